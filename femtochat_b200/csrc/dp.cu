@@ -1,0 +1,105 @@
+// Data-parallel plumbing: one NCCL communicator per handle.  The reference has no distributed
+// path at all (scripts/train.jl:13 "Single-GPU base training"); this layer is new.  NCCL is
+// resolved at run time with dlopen so the library loads (and the layout / host entry points work)
+// on machines without it; a data-parallel call without NCCL fails with a clear error.
+#include <dlfcn.h>
+#include <string.h>
+
+#include "model.cuh"
+
+namespace {
+typedef struct { char internal[128]; } nccl_uid;
+typedef void* nccl_comm;
+typedef int (*fn_get_uid)(nccl_uid*);
+typedef int (*fn_init_rank)(nccl_comm*, int, nccl_uid, int);
+typedef int (*fn_destroy)(nccl_comm);
+typedef int (*fn_allreduce)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
+typedef int (*fn_reduce_scatter)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
+typedef int (*fn_allgather)(const void*, void*, size_t, int, nccl_comm, cudaStream_t);
+typedef const char* (*fn_errstr)(int);
+
+struct Nccl {
+  void* lib = nullptr;
+  fn_get_uid get_uid = nullptr; fn_init_rank init_rank = nullptr; fn_destroy destroy = nullptr;
+  fn_allreduce allreduce = nullptr; fn_reduce_scatter reduce_scatter = nullptr; fn_allgather allgather = nullptr;
+  fn_errstr errstr = nullptr;
+};
+Nccl g_nccl;
+
+int nccl_load() {
+  if (g_nccl.lib) return 0;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    g_nccl.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (g_nccl.lib) break;
+  }
+  if (!g_nccl.lib) return femto_fail(FEMTO_ERR_UNSUPPORTED, "libnccl.so.2 not found: %s", dlerror());
+  g_nccl.get_uid = (fn_get_uid)dlsym(g_nccl.lib, "ncclGetUniqueId");
+  g_nccl.init_rank = (fn_init_rank)dlsym(g_nccl.lib, "ncclCommInitRank");
+  g_nccl.destroy = (fn_destroy)dlsym(g_nccl.lib, "ncclCommDestroy");
+  g_nccl.allreduce = (fn_allreduce)dlsym(g_nccl.lib, "ncclAllReduce");
+  g_nccl.reduce_scatter = (fn_reduce_scatter)dlsym(g_nccl.lib, "ncclReduceScatter");
+  g_nccl.allgather = (fn_allgather)dlsym(g_nccl.lib, "ncclAllGather");
+  g_nccl.errstr = (fn_errstr)dlsym(g_nccl.lib, "ncclGetErrorString");
+  if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.reduce_scatter || !g_nccl.allgather)
+    return femto_fail(FEMTO_ERR_UNSUPPORTED, "libnccl is missing required symbols");
+  return 0;
+}
+// ncclDataType_t / ncclRedOp_t values of the public nccl.h
+constexpr int NCCL_INT8 = 0, NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_SUM = 0;
+int nccl_check(int r, const char* what) {
+  if (r == 0) return 0;
+  return femto_fail(200000 + r, "%s failed: %s", what, g_nccl.errstr ? g_nccl.errstr(r) : "nccl error");
+}
+}  // namespace
+
+struct DpState {
+  nccl_comm comm = nullptr;
+  int rank = 0, world = 1;
+};
+
+int dp_unique_id(void* id128) {
+  FEMTO_TRY(nccl_load());
+  nccl_uid id;
+  FEMTO_TRY(nccl_check(g_nccl.get_uid(&id), "ncclGetUniqueId"));
+  memcpy(id128, &id, 128);
+  return 0;
+}
+
+int dp_create(DpState** out, int rank, int world, const void* id128) {
+  if (world <= 1) { *out = nullptr; return 0; }
+  if (!id128) return femto_fail(FEMTO_ERR_ARG, "world > 1 needs the shared ncclUniqueId");
+  FEMTO_TRY(nccl_load());
+  DpState* d = new DpState();
+  d->rank = rank; d->world = world;
+  nccl_uid id;
+  memcpy(&id, id128, 128);
+  int r = nccl_check(g_nccl.init_rank(&d->comm, world, id, rank), "ncclCommInitRank");
+  if (r) { delete d; return r; }
+  *out = d;
+  return 0;
+}
+
+void dp_destroy(DpState* d) {
+  if (!d) return;
+  if (d->comm && g_nccl.destroy) g_nccl.destroy(d->comm);
+  delete d;
+}
+
+int dp_allreduce_sum_f32(DpState* d, float* buf, long long n, cudaStream_t s) {
+  if (!d) return 0;
+  return nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_FLOAT32, NCCL_SUM, d->comm, s), "ncclAllReduce");
+}
+int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s) {
+  if (!d) return 0;
+  return nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_INT32, NCCL_SUM, d->comm, s), "ncclAllReduce");
+}
+int dp_reduce_scatter_f32(DpState* d, const float* send, float* recv, long long n_per_rank, cudaStream_t s) {
+  if (!d) return 0;
+  return nccl_check(g_nccl.reduce_scatter(send, recv, (size_t)n_per_rank, NCCL_FLOAT32, NCCL_SUM, d->comm, s),
+                    "ncclReduceScatter");
+}
+int dp_allgather_bytes(DpState* d, const void* send, void* recv, long long bytes_per_rank, cudaStream_t s) {
+  if (!d) return 0;
+  return nccl_check(g_nccl.allgather(send, recv, (size_t)bytes_per_rank, NCCL_INT8, d->comm, s), "ncclAllGather");
+}

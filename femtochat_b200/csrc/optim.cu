@@ -1,0 +1,392 @@
+// MuonAdamW (src/optim.jl:318-440): AdamW as one fused pass per flat range (src/optim.jl:33-39,
+// 75-87; GPU form ext/FemtoChatCUDAExt.jl:99-106) and Muon (src/optim.jl:198-248) with the Polar
+// Express chain (src/optim.jl:131-149) run as batched GEMMs on the stacked matrices in their
+// stored [in][out] orientation, so no transposes or gather/scatter copies of Theta are needed.
+#include <math.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "model.cuh"
+#include "streaming.cuh"
+
+struct AdamGroup { long long off, n, moff; float alpha, b1, b2, eps, lam; int t; };
+struct MuonGroup {
+  std::vector<long long> offs;
+  int out = 0, in = 0;          // Julia shape (m, n) = (out, in); stored row-major [in][out]
+  long long moff = 0, voff = 0; // into muon_m / muon_v
+  float alpha, mu, b2, lam;
+  long long* d_offs = nullptr;
+};
+
+struct femto_optimizer {
+  femto_handle* h = nullptr;
+  femto_optimizer_config cfg;
+  std::vector<AdamGroup> adam;
+  std::vector<MuonGroup> muon;
+  float *adam_m = nullptr, *adam_v = nullptr, *muon_m = nullptr, *muon_v = nullptr;
+  char* ws = nullptr;  // X fp32 stack, two compute-type stacks, A, B2, small vectors
+  float* X = nullptr; void *Xa = nullptr, *Xb = nullptr, *A = nullptr, *B2 = nullptr;
+  float *vec = nullptr, *fac = nullptr, *tot = nullptr;
+};
+
+namespace {
+
+__global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const float* __restrict__ delta,
+                                               float* __restrict__ m, float* __restrict__ v, long long n, float alpha,
+                                               float b1, float b2, float eps, float lam, float c1, float c2,
+                                               float inv_nt) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float g = delta[i] * inv_nt;
+    float mm = b1 * m[i] + (1.f - b1) * g;
+    float vv = b2 * v[i] + (1.f - b2) * g * g;
+    m[i] = mm;
+    v[i] = vv;
+    float th = theta[i] * (1.f - alpha * lam);
+    theta[i] = th - alpha * (mm / c1) / (sqrtf(vv / c2) + eps);
+  }
+}
+
+// mom = mu*mom + (1-mu)*g ; X = (1-mu)*g + mu*mom  (src/optim.jl:206-207)
+__global__ void __launch_bounds__(256) k_muon_momentum(const float* __restrict__ delta, const long long* __restrict__ offs,
+                                                       float* __restrict__ mom, float* __restrict__ X, long long per,
+                                                       float mu, float inv_nt) {
+  const int k = blockIdx.y;
+  const float* g = delta + offs[k];
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+    float gv = g[i] * inv_nt;
+    float mm = mu * mom[k * per + i] + (1.f - mu) * gv;
+    mom[k * per + i] = mm;
+    X[k * per + i] = (1.f - mu) * gv + mu * mm;
+  }
+}
+
+// vec[k][o] = sum_i X[k][i][o]^2 (thread per column, rows in order)
+template <typename T>
+__global__ void __launch_bounds__(256) k_sumsq_cols(const T* __restrict__ X, int in, int out, float* __restrict__ vec) {
+  const int k = blockIdx.y;
+  const int o = blockIdx.x * 256 + threadIdx.x;
+  if (o >= out) return;
+  const T* p = X + (long long)k * in * out + o;
+  float acc = 0.f;
+  for (int i = 0; i < in; i++) { float v = to_f<T>(p[(long long)i * out]); acc += v * v; }
+  vec[(long long)k * out + o] = acc;
+}
+// vec[k][i] = sum_o X[k][i][o]^2 (warp per row)
+template <typename T>
+__global__ void __launch_bounds__(256) k_sumsq_rows(const T* __restrict__ X, int in, int out, float* __restrict__ vec) {
+  const int k = blockIdx.y;
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (i >= in) return;
+  const T* p = X + ((long long)k * in + i) * out;
+  float acc = 0.f;
+  for (int o = lane; o < out; o += 32) { float v = to_f<T>(p[o]); acc += v * v; }
+  acc = warp_sum(acc);
+  if (lane == 0) vec[(long long)k * in + i] = acc;
+}
+
+// MuonEq + Polar-Express normalisation factors (src/optim.jl:210-212,135-136), one block per matrix:
+// fac[k][o] = sqrt(old/m)/max(sqrt(row[o]),1e-6) / (1.01*sqrt(sum_o fac0^2*row[o]) + 1e-6)
+__global__ void __launch_bounds__(256) k_muoneq_factors(const float* __restrict__ vec, int out, float* __restrict__ fac) {
+  __shared__ float red[256];
+  const int k = blockIdx.x;
+  const float* row = vec + (long long)k * out;
+  float acc = 0.f;
+  for (int o = threadIdx.x; o < out; o += 256) acc += row[o];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) { if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  const float old = red[0];
+  __syncthreads();
+  const float num = sqrtf(old / (float)out);
+  acc = 0.f;
+  for (int o = threadIdx.x; o < out; o += 256) {
+    float f = num / fmaxf(sqrtf(row[o]), 1e-6f);
+    acc += f * f * row[o];
+  }
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) { if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  const float scale = 1.01f * sqrtf(red[0]) + 1e-6f;
+  for (int o = threadIdx.x; o < out; o += 256) fac[(long long)k * out + o] = num / fmaxf(sqrtf(row[o]), 1e-6f) / scale;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_scale_cols_cast(const float* __restrict__ X, const float* __restrict__ fac,
+                                                         T* __restrict__ Y, long long per, int out) {
+  const int k = blockIdx.y;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x)
+    Y[k * per + i] = from_f<T>(X[k * per + i] * fac[(long long)k * out + (int)(i % out)]);
+}
+
+// Muon+ and NorMuon factors (src/optim.jl:218-233), one block per matrix.  vec = sums of X^2 along
+// the reduced axis (length dim, each over dsize elements); v is the persistent second moment.
+__global__ void __launch_bounds__(256) k_normuon_factors(const float* __restrict__ vec, int dim, int dsize, int rmin,
+                                                         float b2, float* __restrict__ v, float* __restrict__ fac) {
+  __shared__ float red[256];
+  const int k = blockIdx.x;
+  const float* S = vec + (long long)k * dim;
+  float* vv = v + (long long)k * dim;
+  float acc = 0.f;
+  for (int j = threadIdx.x; j < dim; j += 256) acc += S[j];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) { if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  const float old0 = red[0];
+  __syncthreads();
+  const float f1 = sqrtf((float)rmin) / fmaxf(sqrtf(old0), 1e-6f);
+  const float old = f1 * f1 * old0;
+  acc = 0.f;
+  for (int j = threadIdx.x; j < dim; j += 256) {
+    float vm = f1 * f1 * S[j] / (float)dsize;
+    float nv = b2 * vv[j] + (1.f - b2) * vm;
+    vv[j] = nv;
+    float st = rsqrtf(fmaxf(nv, 1e-10f));
+    acc += (float)dsize * vm * st * st;
+  }
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) { if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  const float g = f1 * sqrtf(old) / fmaxf(sqrtf(red[0]), 1e-10f);
+  for (int j = threadIdx.x; j < dim; j += 256) fac[(long long)k * dim + j] = g * rsqrtf(fmaxf(vv[j], 1e-10f));
+}
+
+// theta -= eta*X + eta*lam*theta*[X*theta >= 0]  (src/optim.jl:244-245; ext/FemtoChatCUDAExt.jl:108-119)
+template <typename T>
+__global__ void __launch_bounds__(256) k_muon_update(float* __restrict__ theta, const long long* __restrict__ offs,
+                                                     const T* __restrict__ X, const float* __restrict__ fac,
+                                                     long long per, int out, int by_col, int dim, float eta, float lam) {
+  const int k = blockIdx.y;
+  float* th = theta + offs[k];
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+    int j = by_col ? (int)(i % out) : (int)(i / out);
+    float x = to_f<T>(X[k * per + i]) * fac[(long long)k * dim + j];
+    float t = th[i];
+    th[i] = t - (eta * x + eta * lam * t * ((x * t) >= 0.f ? 1.f : 0.f));
+  }
+}
+
+inline int egrid(long long n) { return (int)std::min<long long>(cdiv(n, 256), 148 * 8); }
+
+}  // namespace
+
+int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
+                 float eps, float lam, int t, float n_tokens, cudaStream_t s) {
+  const float c1 = 1.f - powf(b1, (float)t), c2 = 1.f - powf(b2, (float)t);
+  k_adamw<<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens);
+  KERNEL_CHECK();
+  return 0;
+}
+
+// Polar Express on a stack S[k][in][out] of type T, in place (result left in S).  scratch: S2 like S,
+// A and B2 [k][r][r].
+template <typename T>
+int newton_schulz_t(T* S, T* S2, T* A, T* B2, int k, int in, int out, const float* coeffs, int steps, void* ws,
+                    size_t ws_bytes, unsigned int* status, cudaStream_t s) {
+  const bool tall = out > in;  // Julia m > n: iterate on S as stored (rows = in)
+  const int r = std::min(in, out);
+  const long long per = (long long)in * out, rr = (long long)r * r;
+  T* cur = S;
+  T* nxt = S2;
+  for (int t = 0; t < steps; t++) {
+    const float a = coeffs[3 * t], b = coeffs[3 * t + 1], c = coeffs[3 * t + 2];
+    GemmArgs g;
+    g.ws = ws; g.ws_bytes = ws_bytes; g.status = status; g.batch = k;
+    // A = X X^T
+    g.A = cur; g.B = cur; g.lda = out; g.ldb = out; g.strideA = per; g.strideB = per;
+    g.a_kmajor = tall; g.b_kmajor = tall;
+    g.C = A; g.ldc = r; g.strideC = rr; g.M = r; g.N = r; g.K = tall ? out : in; g.epi = EPI_STORE;
+    FEMTO_TRY(gemm<T>(g, s));
+    // B2 = b A + c A A
+    GemmArgs g2;
+    g2.ws = ws; g2.ws_bytes = ws_bytes; g2.status = status; g2.batch = k;
+    g2.A = A; g2.B = A; g2.lda = r; g2.ldb = r; g2.strideA = rr; g2.strideB = rr; g2.a_kmajor = true; g2.b_kmajor = true;
+    g2.C = B2; g2.ldc = r; g2.strideC = rr; g2.M = r; g2.N = r; g2.K = r;
+    g2.epi = EPI_AXPBY; g2.aux = A; g2.ldaux = r; g2.strideAux = rr; g2.alpha = b; g2.beta = c;
+    FEMTO_TRY(gemm<T>(g2, s));
+    // X' = a X + B2 X   (stored orientation: S' = a S + B2 S when tall, S' = a S + S B2 otherwise)
+    GemmArgs g3;
+    g3.ws = ws; g3.ws_bytes = ws_bytes; g3.status = status; g3.batch = k;
+    if (tall) {
+      g3.A = B2; g3.lda = r; g3.strideA = rr; g3.a_kmajor = true;
+      g3.B = cur; g3.ldb = out; g3.strideB = per; g3.b_kmajor = false;
+      g3.M = r; g3.N = out; g3.K = r;
+    } else {
+      g3.A = cur; g3.lda = out; g3.strideA = per; g3.a_kmajor = true;
+      g3.B = B2; g3.ldb = r; g3.strideB = rr; g3.b_kmajor = true;
+      g3.M = in; g3.N = out; g3.K = r;
+    }
+    g3.C = nxt; g3.ldc = out; g3.strideC = per;
+    g3.epi = EPI_AXPBY; g3.aux = cur; g3.ldaux = out; g3.strideAux = per; g3.alpha = a; g3.beta = 1.f;
+    FEMTO_TRY(gemm<T>(g3, s));
+    std::swap(cur, nxt);
+  }
+  if (cur != S) CUDA_TRY(cudaMemcpyAsync(S, cur, sizeof(T) * per * k, cudaMemcpyDeviceToDevice, s));
+  return 0;
+}
+template int newton_schulz_t<float>(float*, float*, float*, float*, int, int, int, const float*, int, void*, size_t,
+                                    unsigned int*, cudaStream_t);
+template int newton_schulz_t<bf16>(bf16*, bf16*, bf16*, bf16*, int, int, int, const float*, int, void*, size_t,
+                                   unsigned int*, cudaStream_t);
+
+template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& g, float* theta, const float* delta,
+                                                  float alpha, float mu, float lam, float nt, cudaStream_t s) {
+  femto_handle* h = o->h;
+  const int k = (int)g.offs.size(), in = g.in, out = g.out;
+  const long long per = (long long)in * out;
+  float* mom = o->muon_m + g.moff;
+  float* v = o->muon_v + g.voff;
+  dim3 eg(egrid(per), k);
+  k_muon_momentum<<<eg, 256, 0, s>>>(delta, g.d_offs, mom, o->X, per, mu, 1.f / nt);
+  KERNEL_CHECK();
+  k_sumsq_cols<float><<<dim3(cdiv(out, 256), k), 256, 0, s>>>(o->X, in, out, o->vec);
+  KERNEL_CHECK();
+  k_muoneq_factors<<<k, 256, 0, s>>>(o->vec, out, o->fac);
+  KERNEL_CHECK();
+  k_scale_cols_cast<T><<<eg, 256, 0, s>>>(o->X, o->fac, (T*)o->Xa, per, out);
+  KERNEL_CHECK();
+  FEMTO_TRY(newton_schulz_t<T>((T*)o->Xa, (T*)o->Xb, (T*)o->A, (T*)o->B2, k, in, out, o->cfg.ns_coeffs,
+                               o->cfg.ns_steps, h->gemm_ws, h->gemm_ws_bytes, h->status, s));
+  // NorMuon reduces over Julia dim 2 (in) when m >= n, else over dim 1 (out)
+  const bool by_col = out >= in;
+  const int dim = by_col ? out : in, dsize = by_col ? in : out;
+  if (by_col) k_sumsq_cols<T><<<dim3(cdiv(out, 256), k), 256, 0, s>>>((const T*)o->Xa, in, out, o->vec);
+  else k_sumsq_rows<T><<<dim3(cdiv(in, 8), k), 256, 0, s>>>((const T*)o->Xa, in, out, o->vec);
+  KERNEL_CHECK();
+  k_normuon_factors<<<k, 256, 0, s>>>(o->vec, dim, dsize, std::min(in, out), g.b2, v, o->fac);
+  KERNEL_CHECK();
+  const float eta = alpha * sqrtf(std::max(1.f, (float)out / (float)in));
+  k_muon_update<T><<<eg, 256, 0, s>>>(theta, g.d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam);
+  KERNEL_CHECK();
+  return 0;
+}
+
+int optimizer_state_sizes(femto_handle* h, long long* out4) {
+  long long adam = 0, mm = 0, mv = 0;
+  adam += (long long)h->Vp * h->d * 2;
+  for (int i = 0; i < h->L; i++) {
+    if (h->lp[i].ve) adam += (long long)h->Vp * h->kv;
+    adam += 2;
+  }
+  adam += 24 + 1 + 1;
+  const long long d = h->d, kv = h->kv;
+  for (int i = 0; i < h->L; i++) {
+    mm += d * d * 2 + kv * d * 2 + 8 * d * d;
+    mv += std::max(d, d) * 2 + std::max(kv, d) * 2 + 4 * d + 4 * d;  // wq,wo: d; wk,wv: n=d (kv<=d); fc: m=4d; proj: n=4d
+    if (h->lp[i].ve) { mm += h->Hkv * 12; mv += std::max(h->Hkv, 12); }
+  }
+  out4[0] = adam; out4[1] = adam; out4[2] = mm; out4[3] = mv;
+  return 0;
+}
+
+int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* adam_m, float* adam_v, float* muon_m,
+                     float* muon_v, femto_optimizer** out) {
+  if (!h || !cfg || !adam_m || !adam_v || !muon_m || !muon_v || !out) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (cfg->ns_steps < 0 || cfg->ns_steps > 5) return femto_fail(FEMTO_ERR_ARG, "ns_steps must be 0..5");
+  femto_optimizer* o = new femto_optimizer();
+  o->h = h; o->cfg = *cfg; o->adam_m = adam_m; o->adam_v = adam_v; o->muon_m = muon_m; o->muon_v = muon_v;
+  const float scale = sqrtf(768.f / (float)h->d);
+  long long moff = 0;
+  auto add = [&](long long off, long long n, float alpha, float b1, float b2, float lam) {
+    AdamGroup g{off, n, moff, alpha, b1, b2, 1e-10f, lam, 0};
+    moff += n;
+    o->adam.push_back(g);
+  };
+  // group order of src/optim.jl:333-403
+  add(h->off_lm, (long long)h->Vp * h->d, cfg->unembedding_lr * scale, 0.8f, 0.96f, 0.01f);
+  add(h->off_wte, (long long)h->Vp * h->d, cfg->embedding_lr * scale, 0.8f, 0.995f, 0.001f);
+  for (int i = 0; i < h->L; i++) {
+    const LayerP& p = h->lp[i];
+    if (p.ve) add(p.ve_table, (long long)h->Vp * h->kv, 0.5f * cfg->embedding_lr * scale, 0.8f, 0.995f, 0.01f);
+    add(p.lam_b, 1, 0.01f * cfg->scalar_lr, 0.8f, 0.95f, 0.05f);
+    add(p.lam_x0, 1, cfg->scalar_lr, 0.96f, 0.95f, 0.f);
+  }
+  add(h->off_smear, 24, cfg->smear_lr, 0.8f, 0.95f, 0.f);
+  add(h->off_lam_s, 1, cfg->smear_lr, 0.8f, 0.95f, 0.f);
+  add(h->off_lam_y, 1, cfg->smear_lr, 0.8f, 0.95f, 0.f);
+  // Muon groups by shape, in order of first appearance (src/optim.jl:405-425)
+  struct Spec { long long off; int out, in; };
+  std::vector<Spec> specs;
+  for (int i = 0; i < h->L; i++) {
+    const LayerP& p = h->lp[i];
+    specs.push_back({p.wq, h->d, h->d}); specs.push_back({p.wk, h->kv, h->d}); specs.push_back({p.wv, h->kv, h->d});
+    specs.push_back({p.wo, h->d, h->d}); specs.push_back({p.fc, 4 * h->d, h->d}); specs.push_back({p.proj, h->d, 4 * h->d});
+    if (p.ve) specs.push_back({p.ve_gate, h->Hkv, 12});
+  }
+  long long mo = 0, vo = 0;
+  size_t max_stack = 0, max_rr = 0, max_vec = 0;
+  for (const auto& sp : specs) {
+    MuonGroup* g = nullptr;
+    for (auto& e : o->muon) if (e.out == sp.out && e.in == sp.in) g = &e;
+    if (!g) {
+      MuonGroup ng; ng.out = sp.out; ng.in = sp.in; ng.alpha = cfg->matrix_lr; ng.mu = 0.95f; ng.b2 = 0.9f; ng.lam = cfg->weight_decay;
+      o->muon.push_back(ng);
+      g = &o->muon.back();
+    }
+    g->offs.push_back(sp.off);
+  }
+  for (auto& g : o->muon) {
+    const size_t k = g.offs.size();
+    g.moff = mo; g.voff = vo;
+    mo += (long long)k * g.in * g.out;
+    vo += (long long)k * (g.out >= g.in ? g.out : g.in);
+    max_stack = std::max(max_stack, k * (size_t)g.in * g.out);
+    const size_t r = std::min(g.in, g.out);
+    max_rr = std::max(max_rr, k * r * r);
+    max_vec = std::max(max_vec, k * (size_t)std::max(g.in, g.out));
+    CUDA_TRY(cudaMalloc(&g.d_offs, sizeof(long long) * k));
+    CUDA_TRY(cudaMemcpy(g.d_offs, g.offs.data(), sizeof(long long) * k, cudaMemcpyHostToDevice));
+  }
+  const size_t es = cfg->compute_dtype == FEMTO_BF16 ? 2 : 4;
+  auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+  size_t total = al(4 * max_stack) + 2 * al(es * max_stack) + 2 * al(es * max_rr) + 2 * al(4 * max_vec) + 256;
+  CUDA_TRY(cudaMalloc(&o->ws, total));
+  char* p = o->ws;
+  o->X = (float*)p; p += al(4 * max_stack);
+  o->Xa = p; p += al(es * max_stack);
+  o->Xb = p; p += al(es * max_stack);
+  o->A = p; p += al(es * max_rr);
+  o->B2 = p; p += al(es * max_rr);
+  o->vec = (float*)p; p += al(4 * max_vec);
+  o->fac = (float*)p;
+  *out = o;
+  return 0;
+}
+
+int optimizer_destroy(femto_optimizer* o) {
+  if (!o) return 0;
+  for (auto& g : o->muon) cudaFree(g.d_offs);
+  cudaFree(o->ws);
+  delete o;
+  return 0;
+}
+
+int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float eta, int has_mu, float mu,
+                   int has_lambda, float lambda, float n_tokens, cudaStream_t s) {
+  if (!o || !theta || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (!(n_tokens > 0.f)) return femto_fail(FEMTO_ERR_ARG, "n_tokens must be positive");
+  for (auto& g : o->adam) {  // src/optim.jl:431-433
+    g.t += 1;
+    FEMTO_TRY(adamw_launch(theta + g.off, delta + g.off, o->adam_m + g.moff, o->adam_v + g.moff, g.n, eta * g.alpha,
+                           g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, s));
+  }
+  for (auto& g : o->muon) {  // src/optim.jl:434-438
+    const float m_ = has_mu ? mu : g.mu, l_ = has_lambda ? lambda : g.lam;
+    if (o->cfg.compute_dtype == FEMTO_BF16)
+      FEMTO_TRY(muon_group_step<bf16>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s));
+    else
+      FEMTO_TRY(muon_group_step<float>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s));
+  }
+  return model_refresh(o->h, theta, s);
+}
+
+int optimizer_get_t(femto_optimizer* o, int* t, int cap) {
+  int n = (int)o->adam.size();
+  for (int i = 0; i < n && i < cap; i++) t[i] = o->adam[i].t;
+  return n;
+}
+int optimizer_set_t(femto_optimizer* o, const int* t, int count) {
+  if (count != (int)o->adam.size()) return femto_fail(FEMTO_ERR_SHAPE, "expected %d step counters", (int)o->adam.size());
+  for (int i = 0; i < count; i++) o->adam[i].t = t[i];
+  return 0;
+}

@@ -1,0 +1,90 @@
+// lm_head tail: softcap + cross-entropy + its reverse (src/gpt.jl:165-170,172-194;
+// src/kernels.jl:16-28; ext/FemtoChatEnzymeExt.jl:175-189), in token chunks.
+// Tensor-core path (bf16, aligned): pass 1 is a GEMM whose epilogue keeps only per-row
+// (max, sum exp) partials and the target logit; pass 2 recomputes the tile and its epilogue writes
+// d loss/d logit in bf16 for the chunk, which feeds the dX and dW GEMMs.  fp32 / unaligned shapes
+// materialise an fp32 logits chunk instead.
+#include <algorithm>
+
+#include "common.cuh"
+#include "streaming.cuh"
+
+template <typename T> int xent_tail(const XentArgs& x, cudaStream_t s) {
+  const int N = x.N, d = x.D, V = x.V;
+  const long long ld = x.ldw;
+  for (int c0 = 0; c0 < N; c0 += x.chunk) {
+    const int cn = std::min(x.chunk, N - c0);
+    const T* xc = (const T*)x.x + (size_t)c0 * d;
+    GemmArgs g;
+    g.ws = x.ws; g.ws_bytes = x.ws_bytes; g.status = x.status;
+    g.A = xc; g.lda = d; g.B = x.W; g.ldb = ld; g.b_kmajor = false; g.M = cn; g.N = V; g.K = d;
+    g.targets0 = x.targets0 + c0; g.vocab = V;
+    g.epi = EPI_XENT_STATS; g.stats = x.stats; g.tz = x.tz + c0;
+    const bool tc = sizeof(T) == 2 && gemm_tc_supported(g);
+    if (tc) {
+      FEMTO_TRY(gemm_tc_bf16(g, s));
+      FEMTO_TRY(xent_finalize(x.stats, (V + 255) / 256, x.tz + c0, x.targets0 + c0, cn, x.lse_rows + c0,
+                              x.loss_rows + c0, s));
+      if (x.backward) {
+        g.epi = EPI_XENT_DLOGIT; g.C = x.dlogit; g.ldc = ld; g.lse = x.lse_rows + c0;
+        g.xscale = x.scale; g.xscale_dev = x.scale_dev;
+        FEMTO_TRY(gemm_tc_bf16(g, s));
+      }
+    } else {
+      if (!x.logits_f32) return femto_fail(FEMTO_ERR_UNSUPPORTED, "lm_head tail: no fp32 logits workspace for this shape");
+      g.epi = EPI_F32; g.beta = 0.f; g.C = x.logits_f32; g.ldc = ld;
+      FEMTO_TRY(gemm<T>(g, s));
+      FEMTO_TRY(Stream<T>::xent_rows(x.logits_f32, ld, x.targets0 + c0, cn, V, x.scale, x.scale_dev, (T*)x.dlogit, ld,
+                                     x.loss_rows + c0, s));
+    }
+    if (x.backward) {
+      GemmArgs gx;  // dx[cn][d] = dlogit[cn][V] * W[d][V]^T
+      gx.ws = x.ws; gx.ws_bytes = x.ws_bytes; gx.status = x.status;
+      gx.A = x.dlogit; gx.lda = ld; gx.B = x.W; gx.ldb = ld; gx.b_kmajor = true; gx.C = (T*)x.dx + (size_t)c0 * d;
+      gx.ldc = d; gx.M = cn; gx.N = d; gx.K = V;
+      FEMTO_TRY(gemm<T>(gx, s));
+      GemmArgs gw;  // dW[d][ld] += x[cn][d]^T * dlogit[cn][V]
+      gw.ws = x.ws; gw.ws_bytes = x.ws_bytes; gw.status = x.status;
+      gw.A = xc; gw.lda = d; gw.a_kmajor = false; gw.B = x.dlogit; gw.ldb = ld; gw.b_kmajor = false;
+      gw.C = x.dw; gw.ldc = ld; gw.M = d; gw.N = V; gw.K = cn; gw.epi = EPI_F32; gw.beta = 1.f;
+      FEMTO_TRY(gemm<T>(gw, s));
+    }
+  }
+  return 0;
+}
+template int xent_tail<float>(const XentArgs&, cudaStream_t);
+template int xent_tail<bf16>(const XentArgs&, cudaStream_t);
+
+extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W, int64_t ldw, const int32_t* targets0,
+                                    int32_t N, int32_t D, int32_t V, float scale, void* dx, float* dw, float* loss_out,
+                                    int32_t* n_valid_out, void* stream) {
+  if (!x || !W || !targets0 || !loss_out || N <= 0 || D <= 0 || V <= 0 || ldw < V)
+    return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if ((dx == nullptr) != (dw == nullptr)) return femto_fail(FEMTO_ERR_ARG, "dx and dw must both be given or both NULL");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t es = dtype == FEMTO_BF16 ? 2 : 4;
+  const int chunk = std::min(N, 8192);
+  auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+  const size_t wsb = (size_t)160 << 20;
+  const bool need_f32 = dtype != FEMTO_BF16 || (D % 8) != 0 || (ldw % 8) != 0 || N < 128;
+  size_t total = al(need_f32 ? 4 * (size_t)chunk * ldw : 0) + al(sizeof(float2) * (size_t)chunk * ((V + 255) / 256 + 1)) +
+                 3 * al(4 * (size_t)N) + al(es * (size_t)chunk * ldw) + wsb + 1024;
+  char* buf = nullptr;
+  CUDA_TRY(cudaMalloc(&buf, total));
+  char* p = buf;
+  XentArgs a;
+  a.x = x; a.W = W; a.ldw = ldw; a.targets0 = targets0; a.N = N; a.D = D; a.V = V; a.scale = scale;
+  a.backward = dx != nullptr; a.dx = dx; a.dw = dw; a.chunk = chunk;
+  if (need_f32) { a.logits_f32 = (float*)p; p += al(4 * (size_t)chunk * ldw); }
+  a.stats = (float2*)p; p += al(sizeof(float2) * (size_t)chunk * ((V + 255) / 256 + 1));
+  a.tz = (float*)p; p += al(4 * (size_t)N);
+  a.lse_rows = (float*)p; p += al(4 * (size_t)N);
+  a.loss_rows = (float*)p; p += al(4 * (size_t)N);
+  a.dlogit = p; p += al(es * (size_t)chunk * ldw);
+  a.ws = p; a.ws_bytes = wsb;
+  int r = dtype == FEMTO_BF16 ? xent_tail<bf16>(a, s) : xent_tail<float>(a, s);
+  if (!r) r = sum_rows_to_scalar(a.loss_rows, N, loss_out, targets0, n_valid_out, 0.f, s);
+  cudaStreamSynchronize(s);
+  cudaFree(buf);
+  return r;
+}

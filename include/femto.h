@@ -1,0 +1,194 @@
+/* libfemto_sm100a — C ABI of the B200-native femtochat GPT training step.
+ *
+ * Every entry point returns int32: 0 = ok, negative = argument/shape/alignment/state error
+ * detected on the host before any launch, positive = CUDA / NCCL error code or a device status
+ * word.  Nothing throws, exits or aborts (the reference never lets an exception cross a C frame
+ * either: ext/reactant/cuda_call.jl:37-50, deps/reactant/xla_ffi.cpp:21-23).  The text of the last
+ * error is available through femto_last_error().
+ *
+ * Pointers are DEVICE pointers unless the name starts with h_.  The library borrows caller buffers
+ * for the duration of a call; it owns only its workspace arena (allocated once in femto_create) and
+ * its NCCL communicator.  Launch-type calls are asynchronous on the given stream.
+ *
+ * Layout rule: the reference's column-major Julia arrays are byte-identical to the row-major arrays
+ * named here: Julia (d,T,B) == [B][T][d]; a Julia weight (out,in) == [in][out]; (1,T,H,B) == [B][H][T].
+ * Token and target ids are 1-based and the ignore target is -1 (src/gpt.jl:34,172), positions are
+ * 0-based (src/gpt.jl:45), unless index_base says otherwise.
+ */
+#ifndef FEMTO_H
+#define FEMTO_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FEMTO_OK 0
+#define FEMTO_ERR_ARG (-1)
+#define FEMTO_ERR_SHAPE (-2)
+#define FEMTO_ERR_ALIGN (-3)
+#define FEMTO_ERR_STATE (-4)
+#define FEMTO_ERR_UNSUPPORTED (-5)
+#define FEMTO_ERR_NOMEM (-6)
+#define FEMTO_ERR_DEVICE_STATUS 100000 /* + device status word */
+
+#define FEMTO_F32 0
+#define FEMTO_BF16 1
+
+#define FEMTO_REDUCTION_SUM 0  /* reduction=:sum, the training script's call (scripts/train.jl:118) */
+#define FEMTO_REDUCTION_MEAN 1 /* reduction=:mean, the default of the model call (src/gpt.jl:196) */
+
+/* Mirrors GPTConfig (src/parameters.jl:71-80) plus the build options the reference passes as
+ * keyword arguments (compute_type, src/parameters.jl:451) and the four switches on which the
+ * benchmark configurations differ from the reference's defaults. */
+typedef struct femto_config {
+  int32_t sequence_len;
+  int32_t max_document_tokens;
+  int32_t vocab_size;
+  int32_t n_layer;
+  int32_t n_head;
+  int32_t n_kv_head;
+  int32_t n_embed;
+  char window_pattern[32]; /* NUL-terminated, 'S' / 'L' */
+  int32_t short_window;    /* 0 = reference rule min(L, cld(L,512)*128) (src/parameters.jl:204) */
+  int32_t compute_dtype;   /* FEMTO_F32 | FEMTO_BF16: activations and matrix multiplies */
+  int32_t doc_mask;        /* 0 = reference (attention crosses documents); 1 = keys >= document start */
+  int32_t index_base;      /* 1 = reference (1-based tokens/targets); 0 = zero-based wire format */
+  int32_t max_batch;       /* largest B (columns of sequence_len tokens) a call may pass */
+  int32_t pad_vocab_size_to; /* 64 in the reference (src/parameters.jl:221) */
+} femto_config;
+
+typedef struct femto_handle femto_handle;
+
+/* One row of the flat layout (src/parameters.jl:219-337).  `rows`,`cols` are the Julia shape. */
+typedef struct femto_tensor_desc {
+  int32_t kind;  /* 0 wte, 1 wq, 2 wk, 3 wv, 4 wo, 5 ve_gate, 6 fc, 7 proj, 8 ve_table, 9 lam_b, 10 lam_x0,
+                    11 lm_head, 12 smear_gate, 13 lam_s, 14 lam_y */
+  int32_t layer; /* 0-based block index, -1 for global tensors */
+  int64_t offset; /* 0-based element offset into Theta / delta */
+  int64_t rows, cols;
+} femto_tensor_desc;
+
+/* ---- lifetime ------------------------------------------------------------------------------- */
+/* Replaces gradient_state (ext/FemtoChatEnzymeExt.jl:27-36): builds the per-shape state once.
+ * rank/world describe the data-parallel job; h_nccl_id is the 128-byte ncclUniqueId shared by all
+ * ranks (NULL when world == 1). */
+int32_t femto_create(const femto_config* h_cfg, int32_t rank, int32_t world, const void* h_nccl_id,
+                     femto_handle** h_out);
+int32_t femto_destroy(femto_handle* h);
+const char* femto_last_error(femto_handle* h); /* h may be NULL: last error of a failed femto_create */
+int32_t femto_version(void);
+/* Fills the 128-byte ncclUniqueId on the calling rank (rank 0 shares it with the others). */
+int32_t femto_nccl_unique_id(void* h_id128);
+
+/* ---- layout (parameter_layout, src/parameters.jl:219-337) ------------------------------------ */
+int64_t femto_nparams(const femto_config* h_cfg);
+/* Writes up to `capacity` descriptors in flat order; returns the number of tensors (or <0). */
+int32_t femto_layout(const femto_config* h_cfg, femto_tensor_desc* h_out, int32_t capacity);
+/* window_sizes (src/parameters.jl:200-210): left window per layer; has_ve (:197-198) as 0/1. */
+int32_t femto_window_sizes(const femto_config* h_cfg, int32_t* h_left, int32_t* h_has_ve);
+
+/* ---- model ---------------------------------------------------------------------------------- */
+/* Rebuilds the compute-type copy of the weights from Theta (fp32).  The reference casts the fp32
+ * master weights on every Linear call (src/gpt.jl:27); here the cast happens once per update.
+ * Call after any external write to Theta; femto_optimizer_step does it itself. */
+int32_t femto_refresh_weights(femto_handle* h, const float* theta, void* stream);
+
+/* loss_and_gradient! (ext/FemtoChatEnzymeExt.jl:38-44) with the training script's accumulation
+ * (scripts/train.jl:117-131): delta = (accumulate ? delta : 0) + d loss / d Theta.
+ * tokens/targets/positions are int32 [B][T] device arrays (positions may be NULL = 0..T-1).
+ * loss_out (float) and n_valid_out (int32) are device scalars written on the stream. */
+int32_t femto_loss_and_gradient(femto_handle* h, const float* theta, float* delta, const int32_t* tokens,
+                                const int32_t* targets, const int32_t* positions, int32_t B,
+                                int32_t reduction, int32_t accumulate, float* loss_out,
+                                int32_t* n_valid_out, void* stream);
+/* The model call without the reverse pass (src/gpt.jl:196-199). */
+int32_t femto_forward_loss(femto_handle* h, const float* theta, const int32_t* tokens,
+                           const int32_t* targets, const int32_t* positions, int32_t B, int32_t reduction,
+                           float* loss_out, int32_t* n_valid_out, void* stream);
+/* Host-buffer convenience used by the end-to-end path: copies the three int32 [B][T] host arrays to
+ * the device, runs femto_loss_and_gradient, reads loss and n_valid back and synchronises. */
+int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float* delta,
+                                     const int32_t* h_tokens, const int32_t* h_targets,
+                                     const int32_t* h_positions, int32_t B, int32_t reduction,
+                                     int32_t accumulate, float* h_loss, int32_t* h_n_valid, void* stream);
+
+/* ---- data parallel (new; the reference is single-GPU, scripts/train.jl:13) ------------------- */
+/* Sums delta, loss and n_valid over ranks (in place).  No-op when world == 1. */
+int32_t femto_grad_sync(femto_handle* h, float* delta, float* loss_inout, int32_t* n_valid_inout,
+                        void* stream);
+
+/* ---- optimiser: MuonAdamW (src/optim.jl:318-440) ---------------------------------------------- */
+typedef struct femto_optimizer_config {
+  float unembedding_lr, embedding_lr, matrix_lr, weight_decay, scalar_lr, smear_lr; /* :321-326 */
+  int32_t ns_steps;       /* 5 (:421) */
+  float ns_coeffs[15];    /* 5 x (a,b,c): the reference's rho_t table (:90-96) unless overridden */
+  int32_t compute_dtype;  /* dtype of the Polar-Express chain (:327): FEMTO_F32 | FEMTO_BF16 */
+} femto_optimizer_config;
+typedef struct femto_optimizer femto_optimizer;
+
+/* Sizes (in floats) of the four caller-owned state buffers, in the reference's group order:
+ * adam moments m,v over all AdamW groups (:333-403), Muon momentum over all Muon groups (:412-425)
+ * and the NorMuon second moments. h_out[0..3] = adam_m, adam_v (equal), muon_m, muon_v. */
+int32_t femto_optimizer_state_sizes(femto_handle* h, int64_t* h_out4);
+int32_t femto_optimizer_create(femto_handle* h, const femto_optimizer_config* h_cfg, float* adam_m,
+                               float* adam_v, float* muon_m, float* muon_v, femto_optimizer** h_out);
+int32_t femto_optimizer_destroy(femto_optimizer* o);
+/* One update `ω(; η, μ, λ, Nₜ)` (:430-440): has_mu/has_lambda == 0 keeps the groups' own values.
+ * Reads delta, updates Theta and the moments, then refreshes the compute-type weights. */
+int32_t femto_optimizer_step(femto_optimizer* o, float* theta, const float* delta, float eta, int32_t has_mu,
+                             float mu, int32_t has_lambda, float lambda, float n_tokens, void* stream);
+/* Step counters t of the AdamW groups (:17,35), for checkpoints (src/checkpoints.jl:9-12). */
+int32_t femto_optimizer_get_t(femto_optimizer* o, int32_t* h_t, int32_t capacity);
+int32_t femto_optimizer_set_t(femto_optimizer* o, const int32_t* h_t, int32_t count);
+
+/* ---- kernel-level seams (ext/FemtoChatCUDAExt.jl:3-5,161-163) --------------------------------- */
+/* attention!(A,O,l,m,Q,K,V,window) (ext/FemtoChatCUDAExt.jl:1242).  Q,O: [B][T][H][hd]; K,V:
+ * [B][T][Hkv][hd]; l,m: fp32 [B][H][T] (row sum and row max in natural-log units; either may be
+ * NULL); lse: fp32 [B][H][T] = m + log l (may be NULL).  doc_start: int32 [B][T] or NULL. */
+int32_t femto_attention_fwd(int32_t dtype, void* O, float* l, float* m, float* lse, const void* Q,
+                            const void* K, const void* V, int32_t B, int32_t T, int32_t H, int32_t Hkv,
+                            int32_t hd, int32_t window_left, const int32_t* doc_start, void* stream);
+/* Δattention!(A,dQ,dK,dV,dO,Q,K,V,O,l,m,window; accumulate=false) (ext/FemtoChatCUDAExt.jl:1771). */
+int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const void* dO, const void* Q,
+                            const void* K, const void* V, const void* O, const float* lse, int32_t B,
+                            int32_t T, int32_t H, int32_t Hkv, int32_t hd, int32_t window_left,
+                            const int32_t* doc_start, void* stream);
+/* C[M][N] = A[M][K] * B[K][N] in bf16 with fp32 accumulation on the tcgen05 path; each operand may be
+ * stored K-contiguous (kmajor=1) or M/N-contiguous (kmajor=0); replaces the cuBLAS calls behind the
+ * generic `W*X` (src/gpt.jl:28) and batched_mul! (ext/FemtoChatCUDAExt.jl:121-125).  out_f32=1 writes
+ * fp32, accumulate=1 adds to C (fp32 only). */
+int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void* B, int32_t b_kmajor,
+                        int64_t ldb, void* C, int64_t ldc, int32_t M, int32_t N, int32_t K, int32_t batch,
+                        int64_t strideA, int64_t strideB, int64_t strideC, int32_t out_f32,
+                        int32_t accumulate, void* stream);
+/* embedding_gradient!(δ,dy,tokens) (src/kernels.jl:8-14): δ[tokens[n]] += dy[n], deterministic
+ * (fixed summation order), tokens 0-based int32 [N], dy [N][D] of `dtype`, δ fp32 [rows][D]. */
+int32_t femto_embedding_gradient(int32_t dtype, float* delta_table, const void* dy, const int32_t* tokens0,
+                                 int32_t N, int32_t D, int32_t rows, void* stream);
+/* Fused lm_head tail (src/gpt.jl:165-170,172-194; src/kernels.jl:16-28): loss = sum over valid
+ * targets of logsumexp(z) - z[target], z = 15 tanh(x W / 15); dX and dW (+=) of that loss.
+ * x: [N][D] dtype, W: [D][ldw] dtype (first V columns used), targets0: 0-based or -1,
+ * dx: [N][D] dtype, dw: fp32 [D][ldw]. */
+int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W, int64_t ldw, const int32_t* targets0,
+                         int32_t N, int32_t D, int32_t V, float scale, void* dx, float* dw,
+                         float* loss_out, int32_t* n_valid_out, void* stream);
+/* Polar Express / Newton-Schulz (src/optim.jl:131-149) on a stack of k row-major [rows][cols]
+ * bf16 or fp32 matrices, in place; coeffs = steps x (a,b,c). */
+int32_t femto_newton_schulz(int32_t dtype, void* X, int32_t k, int32_t rows, int32_t cols,
+                            const float* h_coeffs, int32_t steps, void* stream);
+/* AdamW on one flat range (src/optim.jl:33-39,75-87), one fused pass. */
+int32_t femto_adamw(float* theta, const float* delta, float* m, float* v, int64_t n, float alpha,
+                    float beta1, float beta2, float eps, float lambda, int32_t t, float n_tokens,
+                    void* stream);
+
+/* ---- status --------------------------------------------------------------------------------- */
+/* Device status word (0 = ok): bounded waits that ran out, out-of-range token ids, ... */
+int32_t femto_status_word(femto_handle* h, int32_t* h_out);
+int32_t femto_sync(femto_handle* h, void* stream);
+/* Number of kernels launched by this handle since creation (host counter). */
+int64_t femto_launch_count(femto_handle* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
