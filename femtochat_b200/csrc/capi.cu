@@ -221,7 +221,8 @@ int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void
   g.A = A; g.B = B; g.C = C; g.lda = lda; g.ldb = ldb; g.ldc = ldc; g.a_kmajor = a_kmajor != 0; g.b_kmajor = b_kmajor != 0;
   g.M = M; g.N = N; g.K = K; g.batch = batch < 1 ? 1 : batch; g.strideA = strideA; g.strideB = strideB; g.strideC = strideC;
   g.epi = out_f32 ? EPI_F32 : EPI_STORE; g.beta = accumulate ? 1.f : 0.f;
-  void* ws = nullptr;
+  if (!out_f32) return gemm<bf16>(g, (cudaStream_t)stream);  // asynchronous, no scratch
+  void* ws = nullptr;  // split-K partials of the fp32 form
   const size_t wsb = (size_t)160 << 20;
   CUDA_TRY(cudaMalloc(&ws, wsb));
   g.ws = ws; g.ws_bytes = wsb;

@@ -1,3 +1,464 @@
-#include "common.cuh"
-bool gemm_tc_supported(const GemmArgs&) { return false; }
-int gemm_tc_bf16(const GemmArgs&, cudaStream_t) { return femto_fail(FEMTO_ERR_UNSUPPORTED, "tcgen05 GEMM not built"); }
+// bf16 GEMM with fp32 accumulation on the sm_100a tensor cores.
+//
+// One persistent CTA per SM walks a list of (tile, k-range) units.  Warp 0 issues TMA tiled loads
+// (128-byte swizzle) into a 4-stage shared-memory ring, warp 1 issues tcgen05.mma (128x256x16 per
+// instruction) into one of two 256-column TMEM accumulators, warps 2-5 drain the other accumulator
+// with tcgen05.ld and run the epilogue, so the epilogue of unit i overlaps the main loop of unit
+// i+1.  Operands may be K-contiguous or M/N-contiguous in memory (the D x T x B layout of the
+// reference makes the weight of a forward Linear N-contiguous and both operands of a weight
+// gradient M/N-contiguous); the difference is only in the tensor maps and the matrix descriptors.
+// Replaces the library GEMMs behind `W*X` (src/gpt.jl:28), the Linear/MLP reverse rules
+// (ext/FemtoChatEnzymeExt.jl:83-134) and batched_mul! (ext/FemtoChatCUDAExt.jl:121-125).
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "sm100_ptx.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NTHREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct TcParams {
+  GemmArgs g;
+  int tiles_m, tiles_n, kblocks, splits, kb_per_split, total_units;
+  float* partial;  // [unit][8 chunks][128 rows][32 cols] when splits > 1
+};
+
+__device__ __forceinline__ float softcap15(float x) {
+  // 15 * tanh(x/15) with tanh(y) = 1 - 2/(exp(2y)+1)
+  float e = __expf(x * (2.f / 15.f));
+  return 15.f * (1.f - __fdividef(2.f, e + 1.f));
+}
+
+__device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m, int n) {
+  if (g.nseg == 0) return reinterpret_cast<float*>(g.C) + bz * g.strideC + (long long)m * g.ldc + n;
+  for (int s = 0; s < g.nseg; s++)
+    if (n >= g.seg_col0[s] && n < g.seg_col0[s] + g.seg_ncol[s])
+      return g.seg_ptr[s] + (long long)m * g.seg_ld[s] + (n - g.seg_col0[s]);
+  return nullptr;
+}
+
+template <bool A_K, bool B_K>
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                 // [STAGES]
+  uint64_t* empty = bars + STAGES;       // [STAGES]
+  uint64_t* tfull = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const GemmArgs& g = p.g;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto unit_coords = [&](int u, int& bz, int& mt, int& nt, int& kb0, int& kb1) {
+    const int s = u % p.splits;
+    int tile = u / p.splits;
+    nt = tile % p.tiles_n; tile /= p.tiles_n;
+    mt = tile % p.tiles_m; bz = tile / p.tiles_m;
+    kb0 = s * p.kb_per_split;
+    kb1 = min(p.kblocks, kb0 + p.kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      uint32_t issued_mask = 0, last_parity = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        int bz, mt, nt, kb0, kb1;
+        unit_coords(u, bz, mt, nt, kb0, kb1);
+        for (int kb = kb0; kb < kb1; kb++) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, g.status)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          if (A_K) {
+            tma_load_3d(sa, &tmA, &full[stage], kb * BK, mt * BM, bz);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; j++) tma_load_3d(sa + j * 8192, &tmA, &full[stage], mt * BM + j * 64, kb * BK, bz);
+          }
+          if (B_K) {
+            tma_load_3d(sb, &tmB, &full[stage], kb * BK, nt * BN, bz);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++) tma_load_3d(sb + j * 8192, &tmB, &full[stage], nt * BN + j * 64, kb * BK, bz);
+          }
+          issued_mask |= 1u << stage;
+          last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // let loads already in flight land before the CTA exits
+        for (int i = 0; i < STAGES; i++)
+          if (issued_mask & (1u << i))
+            for (uint32_t it = 0; it < WAIT_LIMIT && !mbar_try_wait(&full[i], (last_parity >> i) & 1u); ++it) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(BM, BN, !A_K, !B_K);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        int bz, mt, nt, kb0, kb1;
+        unit_coords(u, bz, mt, nt, kb0, kb1);
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, g.status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; kb++) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, g.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; k++) {
+            // K-major: rows of 128 B, 8-row groups 1024 B apart, 16 k-elements = 32 B along the row.
+            // MN-major: [64 k][64 mn] slabs of 8192 B, 8-k groups 1024 B apart, 16 k = 2048 B.
+            const uint64_t ad = A_K ? smem_desc_sw128(sa + k * 32, 16, 1024) : smem_desc_sw128(sa + k * 2048, 8192, 1024);
+            const uint64_t bd = B_K ? smem_desc_sw128(sb + k * 32, 16, 1024) : smem_desc_sw128(sb + k * 2048, 8192, 1024);
+            mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quad = warp & 3;           // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0; uint32_t acc_phase = 0;
+    for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
+      int bz, mt, nt, kb0, kb1;
+      unit_coords(u, bz, mt, nt, kb0, kb1);
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, g.status)) break;
+      tc_fence_after();
+      const int m = mt * BM + row_in_tile;
+      const int n0 = nt * BN;
+      const bool row_ok = m < g.M;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      // cross-entropy row state
+      float rmax = -INFINITY, rsum = 0.f, lse = 0.f, xw = 0.f;
+      int tgt = -1;
+      if (g.epi == EPI_XENT_STATS || g.epi == EPI_XENT_DLOGIT) {
+        if (row_ok) tgt = g.targets0[m];
+        if (g.epi == EPI_XENT_DLOGIT && row_ok) {
+          lse = g.lse[m];
+          xw = tgt >= 0 ? g.xscale * (g.xscale_dev ? g.xscale_dev[0] : 1.f) : 0.f;
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int nc = n0 + c * 32;
+        if (!row_ok || nc >= g.N) continue;
+        const bool full_chunk = nc + 32 <= g.N;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+        if (p.splits > 1) {
+          float* dst = p.partial + ((long long)u * 8 + c) * (128 * 32) + row_in_tile * 32;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          continue;
+        }
+        switch (g.epi) {
+          case EPI_F32: {
+            if (g.nseg == 0 && full_chunk && (g.ldc & 3) == 0) {
+              float* dst = reinterpret_cast<float*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(g.alpha * v[j], g.alpha * v[j + 1], g.alpha * v[j + 2], g.alpha * v[j + 3]);
+                if (g.beta != 0.f) {
+                  float4 q = *reinterpret_cast<const float4*>(dst + j);
+                  o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && nc + j < g.N; j++) {
+                float* dst = f32_dst(g, bz, m, nc + j);
+                if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * v[j];
+              }
+            }
+          } break;
+          case EPI_XENT_STATS: {
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              v[j] = (nc + j < g.vocab) ? softcap15(v[j]) : -INFINITY;
+              cm = fmaxf(cm, v[j]);
+            }
+            if (tgt >= nc && tgt < nc + 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (nc + j == tgt) g.tz[m] = v[j];
+            }
+            const float nm = fmaxf(rmax, cm);
+            float cs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; j++) cs += __expf(v[j] - nm);
+            rsum = rsum * __expf(rmax - nm) + cs;
+            rmax = nm;
+          } break;
+          default: {
+            // bf16 outputs: STORE, RESID, RELU2, DRELU2, AXPBY, XENT_DLOGIT
+            bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
+            const bf16* aux = g.aux ? reinterpret_cast<const bf16*>(g.aux) + (long long)bz * g.strideAux + (long long)m * g.ldaux + nc : nullptr;
+            const bool need_aux = g.epi == EPI_RESID || g.epi == EPI_DRELU2 || g.epi == EPI_AXPBY;
+            float a[32];
+            const bool vec = full_chunk && (g.ldc & 7) == 0 && (!need_aux || (g.ldaux & 7) == 0);
+            if (need_aux) {
+              if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 q = *reinterpret_cast<const uint4*>(aux + j);
+                  const bf16* hq = reinterpret_cast<const bf16*>(&q);
+#pragma unroll
+                  for (int e = 0; e < 8; e++) a[j + e] = __bfloat162float(hq[e]);
+                }
+              } else {
+                for (int j = 0; j < 32; j++) a[j] = (nc + j < g.N) ? __bfloat162float(aux[j]) : 0.f;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              float x = v[j];
+              switch (g.epi) {
+                case EPI_RESID: x = a[j] + x; break;
+                case EPI_RELU2: x = fmaxf(x, 0.f); x = x * x; break;
+                case EPI_DRELU2: x = x * 2.f * sqrtf(fmaxf(a[j], 0.f)); break;
+                case EPI_AXPBY: x = g.alpha * a[j] + g.beta * x; break;
+                case EPI_XENT_DLOGIT: {
+                  float z = softcap15(x);
+                  float t = z * (1.f / 15.f);
+                  float dz = xw * (__expf(z - lse) - ((nc + j) == tgt ? 1.f : 0.f));
+                  x = (nc + j < g.vocab) ? dz * (1.f - t * t) : 0.f;
+                } break;
+                default: break;
+              }
+              v[j] = x;
+            }
+            if (g.dbg == 1) {
+              float t = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; j++) t += v[j];
+              if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
+            } else if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 q;
+                bf16* hq = reinterpret_cast<bf16*>(&q);
+#pragma unroll
+                for (int e = 0; e < 8; e++) hq[e] = __float2bfloat16_rn(v[j + e]);
+                *reinterpret_cast<uint4*>(C + j) = q;
+              }
+            } else {
+              for (int j = 0; j < 32 && nc + j < g.N; j++) C[j] = __float2bfloat16_rn(v[j]);
+            }
+          } break;
+        }
+      }
+      if (g.epi == EPI_XENT_STATS && row_ok && p.splits == 1) g.stats[(long long)m * p.tiles_n + nt] = make_float2(rmax, rsum);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Sum the split-K partials of every tile in split order and apply the fp32 epilogue.
+__global__ void __launch_bounds__(256) gemm_tc_reduce_kernel(const TcParams p) {
+  const GemmArgs& g = p.g;
+  const int tile = blockIdx.x;
+  int t = tile;
+  const int nt = t % p.tiles_n; t /= p.tiles_n;
+  const int mt = t % p.tiles_m;
+  const int bz = t / p.tiles_m;
+  for (int e = threadIdx.x; e < 128 * 256 / 4; e += 256) {
+    const int c = e / (128 * 8);          // 32-column chunk
+    const int rem = e % (128 * 8);
+    const int row = rem / 8, j4 = (rem % 8) * 4;
+    const int m = mt * BM + row, n = nt * BN + c * 32 + j4;
+    if (m >= g.M || n >= g.N) continue;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < p.splits; s++) {
+      const float4 q = *reinterpret_cast<const float4*>(p.partial + (((long long)tile * p.splits + s) * 8 + c) * (128 * 32) + row * 32 + j4);
+      acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+    }
+    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+    for (int j = 0; j < 4 && n + j < g.N; j++) {
+      float* dst = f32_dst(g, bz, m, n + j);
+      if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * vals[j];
+    }
+  }
+}
+
+}  // namespace
+
+// ---- host ---------------------------------------------------------------------------------------
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled get_encode() {
+  static PFN_encodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && p)
+      fn = reinterpret_cast<PFN_encodeTiled>(p);
+  }
+  return fn;
+}
+
+int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                      uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return femto_fail(FEMTO_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {dim0, dim1, dim2 ? dim2 : 1};
+  cuuint64_t strides[2] = {stride1_elems * 2, (dim2 > 1 ? stride2_elems : stride1_elems * dim1) * 2};
+  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return femto_fail(FEMTO_ERR_ALIGN, "cuTensorMapEncodeTiled failed (%d): dims %llu x %llu x %llu, row stride %llu B",
+                      (int)r, (unsigned long long)dim0, (unsigned long long)dim1, (unsigned long long)dims[2],
+                      (unsigned long long)strides[0]);
+  return 0;
+}
+
+bool gemm_tc_supported(const GemmArgs& g) {
+  if (g.M < BM || g.N < BN || g.K < BK) return false;
+  if ((g.lda & 7) || (g.ldb & 7) || (g.strideA & 7) || (g.strideB & 7)) return false;
+  if (!aligned16(g.A) || !aligned16(g.B)) return false;
+  // the contiguous extent of an M/N-major operand must cover whole 16-byte units
+  if (!g.a_kmajor && (g.M & 7)) return false;
+  if (!g.b_kmajor && (g.N & 7)) return false;
+  if (g.a_kmajor && (g.K & 7)) return false;
+  if (g.b_kmajor && (g.K & 7)) return false;
+  if (g.epi == EPI_F32) {
+    if (!g.ws) return false;
+  } else if (g.epi == EPI_XENT_STATS) {
+    if (!g.stats || !g.tz || !g.targets0) return false;
+  } else {
+    if (!g.C && g.epi != EPI_XENT_STATS) return false;
+  }
+  return true;
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
+  if (!gemm_tc_supported(g)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "gemm_tc: shape/alignment not supported");
+  TcParams p;
+  p.g = g;
+  if (const char* e = getenv("FEMTO_DBG")) p.g.dbg = atoi(e);
+  p.tiles_m = cdiv(g.M, BM);
+  p.tiles_n = cdiv(g.N, BN);
+  p.kblocks = cdiv(g.K, BK);
+  const int tiles = p.tiles_m * p.tiles_n * g.batch;
+  const int sms = num_sms();
+  int splits = 1;
+  if (g.epi == EPI_F32 && tiles < 4 * sms) {
+    // pick the split count that minimises (waves x k-blocks per unit), bounded by the workspace
+    const size_t per_unit = (size_t)BM * BN * 4;
+    long long best = (long long)cdiv(tiles, sms) * p.kblocks;
+    for (int sp = 2; sp <= 32 && sp <= p.kblocks; sp++) {
+      if ((size_t)tiles * sp * per_unit > g.ws_bytes) break;
+      const int kbp = cdiv(p.kblocks, sp);
+      if ((sp - 1) * kbp >= p.kblocks) continue;
+      const long long cost = (long long)cdiv((long long)tiles * sp, sms) * kbp + 4;  // +4: reduce pass
+      if (cost < best) { best = cost; splits = sp; }
+    }
+  }
+  p.splits = splits;
+  p.kb_per_split = cdiv(p.kblocks, splits);
+  p.total_units = tiles * splits;
+  p.partial = reinterpret_cast<float*>(g.ws);
+
+  CUtensorMap tmA, tmB;
+  const int nb = g.batch;
+  if (g.a_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.K, g.M, nb, g.lda, g.strideA, 64, BM));
+  else FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, 64, BK));
+  if (g.b_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.K, g.N, nb, g.ldb, g.strideB, 64, BN));
+  else FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, 64, BK));
+
+  const int grid = std::min(p.total_units, sms);
+  static bool attr_done = false;
+  if (!attr_done) {
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_done = true;
+  }
+  if (g.a_kmajor && g.b_kmajor) gemm_tc_kernel<true, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
+  else if (g.a_kmajor) gemm_tc_kernel<true, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
+  else if (g.b_kmajor) gemm_tc_kernel<false, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
+  else gemm_tc_kernel<false, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
+  KERNEL_CHECK();
+  if (splits > 1) {
+    gemm_tc_reduce_kernel<<<tiles, 256, 0, s>>>(p);
+    KERNEL_CHECK();
+  }
+  return 0;
+}
