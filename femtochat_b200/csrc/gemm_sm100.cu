@@ -45,6 +45,65 @@ __device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m
   return nullptr;
 }
 
+// One 32-column chunk of one output row with a bf16 result: C = f(acc, aux).
+template <int EPI>
+__device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], int bz, int m, int nc, bool full_chunk,
+                                           int tgt, float lse, float xw) {
+  bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
+  constexpr bool need_aux = EPI == EPI_RESID || EPI == EPI_DRELU2 || EPI == EPI_AXPBY;
+  const bool vec = full_chunk && (g.ldc & 7) == 0 && (!need_aux || (g.ldaux & 7) == 0);
+  float a[32];
+  if constexpr (need_aux) {
+    const bf16* aux = reinterpret_cast<const bf16*>(g.aux) + (long long)bz * g.strideAux + (long long)m * g.ldaux + nc;
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 q = *reinterpret_cast<const uint4*>(aux + j);
+        const bf16* hq = reinterpret_cast<const bf16*>(&q);
+#pragma unroll
+        for (int e = 0; e < 8; e++) a[j + e] = __bfloat162float(hq[e]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++) a[j] = (nc + j < g.N) ? __bfloat162float(aux[j]) : 0.f;
+    }
+  }
+  const float alpha = g.alpha, beta = g.beta;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    float x = v[j];
+    if constexpr (EPI == EPI_RESID) x = a[j] + x;
+    if constexpr (EPI == EPI_RELU2) { x = fmaxf(x, 0.f); x = x * x; }
+    if constexpr (EPI == EPI_DRELU2) x = x * 2.f * sqrtf(fmaxf(a[j], 0.f));
+    if constexpr (EPI == EPI_AXPBY) x = alpha * a[j] + beta * x;
+    if constexpr (EPI == EPI_XENT_DLOGIT) {
+      float z = softcap15(x);
+      float t = z * (1.f / 15.f);
+      float dz = xw * (__expf(z - lse) - ((nc + j) == tgt ? 1.f : 0.f));
+      x = (nc + j < g.vocab) ? dz * (1.f - t * t) : 0.f;
+    }
+    v[j] = x;
+  }
+  if (g.dbg == 1) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; j++) t += v[j];
+    if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
+  } else if (vec) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 q;
+      __nv_bfloat162* hq = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; e++) hq[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+      *reinterpret_cast<uint4*>(C + j) = q;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j++) if (nc + j < g.N) C[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+
 template <bool A_K, bool B_K>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
@@ -188,9 +247,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
         __syncwarp();
+        if (g.dbg == 2) continue;
         tmem_ld32(taddr + c * 32, r);
         tmem_ld_wait();
         const int nc = n0 + c * 32;
+        if (g.dbg == 3) { if (r[0] == 0x12345678u && r[31] == 0x1u) reinterpret_cast<bf16*>(g.C)[0] = __float2bfloat16_rn(1.f); continue; }
         if (!row_ok || nc >= g.N) continue;
         const bool full_chunk = nc + 32 <= g.N;
         float v[32];
@@ -216,9 +277,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 *reinterpret_cast<float4*>(dst + j) = o;
               }
             } else {
-              for (int j = 0; j < 32 && nc + j < g.N; j++) {
-                float* dst = f32_dst(g, bz, m, nc + j);
-                if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * v[j];
+#pragma unroll
+              for (int j = 0; j < 32; j++) {
+                if (nc + j < g.N) {
+                  float* dst = f32_dst(g, bz, m, nc + j);
+                  if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * v[j];
+                }
               }
             }
           } break;
@@ -240,62 +304,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             rsum = rsum * __expf(rmax - nm) + cs;
             rmax = nm;
           } break;
-          default: {
-            // bf16 outputs: STORE, RESID, RELU2, DRELU2, AXPBY, XENT_DLOGIT
-            bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
-            const bf16* aux = g.aux ? reinterpret_cast<const bf16*>(g.aux) + (long long)bz * g.strideAux + (long long)m * g.ldaux + nc : nullptr;
-            const bool need_aux = g.epi == EPI_RESID || g.epi == EPI_DRELU2 || g.epi == EPI_AXPBY;
-            float a[32];
-            const bool vec = full_chunk && (g.ldc & 7) == 0 && (!need_aux || (g.ldaux & 7) == 0);
-            if (need_aux) {
-              if (vec) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 q = *reinterpret_cast<const uint4*>(aux + j);
-                  const bf16* hq = reinterpret_cast<const bf16*>(&q);
-#pragma unroll
-                  for (int e = 0; e < 8; e++) a[j + e] = __bfloat162float(hq[e]);
-                }
-              } else {
-                for (int j = 0; j < 32; j++) a[j] = (nc + j < g.N) ? __bfloat162float(aux[j]) : 0.f;
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-              float x = v[j];
-              switch (g.epi) {
-                case EPI_RESID: x = a[j] + x; break;
-                case EPI_RELU2: x = fmaxf(x, 0.f); x = x * x; break;
-                case EPI_DRELU2: x = x * 2.f * sqrtf(fmaxf(a[j], 0.f)); break;
-                case EPI_AXPBY: x = g.alpha * a[j] + g.beta * x; break;
-                case EPI_XENT_DLOGIT: {
-                  float z = softcap15(x);
-                  float t = z * (1.f / 15.f);
-                  float dz = xw * (__expf(z - lse) - ((nc + j) == tgt ? 1.f : 0.f));
-                  x = (nc + j < g.vocab) ? dz * (1.f - t * t) : 0.f;
-                } break;
-                default: break;
-              }
-              v[j] = x;
-            }
-            if (g.dbg == 1) {
-              float t = 0.f;
-#pragma unroll
-              for (int j = 0; j < 32; j++) t += v[j];
-              if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
-            } else if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 q;
-                bf16* hq = reinterpret_cast<bf16*>(&q);
-#pragma unroll
-                for (int e = 0; e < 8; e++) hq[e] = __float2bfloat16_rn(v[j + e]);
-                *reinterpret_cast<uint4*>(C + j) = q;
-              }
-            } else {
-              for (int j = 0; j < 32 && nc + j < g.N; j++) C[j] = __float2bfloat16_rn(v[j]);
-            }
-          } break;
+          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          case EPI_XENT_DLOGIT: bf16_chunk<EPI_XENT_DLOGIT>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          default: break;
         }
       }
       if (g.epi == EPI_XENT_STATS && row_ok && p.splits == 1) g.stats[(long long)m * p.tiles_n + nt] = make_float2(rmax, rsum);

@@ -567,7 +567,7 @@ class Model:
         th = theta.clone().requires_grad_(True)
         loss = self.forward(th, tokens, targets, positions, attention="naive")
         loss.backward()
-        return float(loss), th.grad.detach().to(torch.float32)
+        return float(loss.detach()), th.grad.detach().to(torch.float32)
 
 
 # --------------------------------------------------------------------------------------
