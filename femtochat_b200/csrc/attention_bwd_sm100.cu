@@ -1,0 +1,482 @@
+// Reverse pass of flash attention (head_dim 128, bf16) on the sm_100a tensor cores, after
+// src/kernels.jl:287-379 (P from the saved row statistics, dV += P^T dO, dP = dO V^T,
+// dS = P o (dP - D), dQ += tau dS K, dK += tau dS^T Q).  The reference accumulates dQ with fp32
+// atomics (ext/FemtoChatCUDAExt.jl:2002-2004); here two kernels each own their outputs, so every
+// gradient is summed in a fixed order:
+//   * dQ kernel: one CTA per 128 queries of a head; S = Q K^T and dP = dO V^T go to TMEM, the
+//     row-owning threads turn them into dS (bf16, written over S in TMEM), dQ += dS K stays in TMEM.
+//   * dK/dV kernel: one CTA per 128 keys of a kv head; loops over the heads of the GQA group and
+//     the query tiles that see these keys; S^T = K Q^T and dP^T = V dO^T go to TMEM, threads own
+//     key rows and write P^T and dS^T back to TMEM, dV += P^T dO and dK += dS^T Q stay in TMEM.
+#include <algorithm>
+
+#include "sm100_ptx.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int HD = 128, BT = 128;
+constexpr int TILE_BYTES = BT * HD * 2;  // two [128][64] swizzled slabs
+constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 3 * 128 * 4;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct BwdParams {
+  AttnArgs a;
+  const float* D;  // [B][H][T] rowsum(dO*O)
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// D[b][h][t] = sum_d dO*O, one warp per (token, head) slice of 128 channels.
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D) {
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)a.B * a.T * a.H;
+  if (w >= total) return;
+  const int h = (int)(w % a.H);
+  const long long row = w / a.H;
+  const bf16* o = reinterpret_cast<const bf16*>(a.O) + row * a.o_stride + (long long)h * HD + lane * 4;
+  const bf16* g = reinterpret_cast<const bf16*>(a.dO) + row * a.do_stride + (long long)h * HD + lane * 4;
+  uint2 ov = *reinterpret_cast<const uint2*>(o), gv = *reinterpret_cast<const uint2*>(g);
+  const bf16* oh = reinterpret_cast<const bf16*>(&ov);
+  const bf16* gh = reinterpret_cast<const bf16*>(&gv);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) acc += __bfloat162float(oh[i]) * __bfloat162float(gh[i]);
+  acc = warp_sum(acc);
+  const int b = (int)(row / a.T), t = (int)(row % a.T);
+  if (lane == 0) D[((long long)b * a.H + h) * a.T + t] = acc;
+}
+
+// ------------------------------------------------------------------------------------------------
+// dQ kernel
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + TILE_BYTES;
+  uint8_t* sK = smem + 2 * TILE_BYTES;  // 2 stages
+  uint8_t* sV = smem + 4 * TILE_BYTES;  // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* qdo_full = bars;
+  uint64_t* k_full = bars + 1;     // [2]
+  uint64_t* k_empty = bars + 3;    // [2]
+  uint64_t* v_full = bars + 5;     // [2]
+  uint64_t* v_empty = bars + 7;    // [2]
+  uint64_t* s_full = bars + 9;     // [2]
+  uint64_t* dp_full = bars + 11;   // [1]
+  uint64_t* ds_ready = bars + 12;  // [2]
+  uint64_t* dq_done = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const AttnArgs& a = p.a;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (a.H / a.Hkv);
+  const int q0 = qt * BT;
+  const int jhi = min(q0 + BT - 1, a.T - 1) / BT;
+  const int jlo = max(0, q0 - a.window_left) / BT;
+  const int ntile = jhi - jlo + 1;
+  const long long row0 = (long long)b * a.T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&ds_ready[i], 4);
+    }
+    mbar_init(dp_full, 1);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tdP = tmem_base + 256, tdQ = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+      tma_load_2d(sQ, &tmQ, qdo_full, h * HD, (int)(row0 + q0));
+      tma_load_2d(sQ + TILE_BYTES / 2, &tmQ, qdo_full, h * HD + 64, (int)(row0 + q0));
+      tma_load_2d(sdO, &tmdO, qdo_full, h * HD, (int)(row0 + q0));
+      tma_load_2d(sdO + TILE_BYTES / 2, &tmdO, qdo_full, h * HD + 64, (int)(row0 + q0));
+      for (int i = 0; i < ntile; i++) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int krow = (int)(row0 + (jlo + i) * BT);
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, a.status)) break;
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        tma_load_2d(sK + st * TILE_BYTES, &tmK, &k_full[st], kvh * HD, krow);
+        tma_load_2d(sK + st * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[st], kvh * HD + 64, krow);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, a.status)) break;
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        tma_load_2d(sV + st * TILE_BYTES, &tmV, &v_full[st], kvh * HD, krow);
+        tma_load_2d(sV + st * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[st], kvh * HD + 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = idesc_bf16(BT, BT, false, false);  // both operands K-major
+      constexpr uint32_t idesc_mn = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+      auto issue_s = [&](int i) -> bool {  // S_i = Q K_i^T
+        const int st = i & 1;
+        if (!mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag, a.status)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_kk, k > 0);
+        }
+        tc_commit(&s_full[st]);
+        return true;
+      };
+      auto issue_dp = [&](int i) -> bool {  // dP_i = dO V_i^T
+        const int st = i & 1;
+        if (!mbar_wait(&v_full[st], (i >> 1) & 1, abort_flag, a.status)) return false;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(tdP, smem_desc_sw128(do_addr + off, 16, 1024), smem_desc_sw128(v_addr + off, 16, 1024), idesc_kk, k > 0);
+        }
+        tc_commit(dp_full);
+        tc_commit(&v_empty[st]);
+        return true;
+      };
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, a.status);
+      if (ok) { tc_fence_after(); ok = issue_s(0) && issue_dp(0); }
+      for (int i = 0; i < ntile && ok; i++) {
+        const int st = i & 1;
+        if (i + 1 < ntile && !issue_s(i + 1)) { ok = false; break; }
+        if (!mbar_wait(&ds_ready[st], (i >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
+        tc_fence_after();
+        if (i + 1 < ntile && !issue_dp(i + 1)) { ok = false; break; }
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BT / 16; k++)  // dQ += dS_i K_i : 16 keys = 8 TMEM columns / 2048 B of K rows
+          mma_ts(tdQ, tS[st] + k * 8, smem_desc_sw128(k_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (i > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&k_empty[st]);
+      }
+      if (ok) tc_commit(dq_done);
+    }
+  } else if (warp >= 4) {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int q = q0 + r;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float scale = rsqrtf((float)HD);
+    const float c = scale * LOG2E;
+    int lo = max(0, q - a.window_left);
+    if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
+    const long long si = ((long long)b * a.H + h) * a.T + q;
+    const float lse2 = a.lse[si] * LOG2E;
+    const float Dq = p.D[si];
+    bool ok = true;
+    for (int i = 0; i < ntile; i++) {
+      const int st = i & 1;
+      const int k0 = (jlo + i) * BT;
+      if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
+      if (!mbar_wait(dp_full, i & 1, abort_flag, a.status)) { ok = false; break; }
+      tc_fence_after();
+      const bool need_mask = (k0 + BT - 1 > q) || (k0 < lo);
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t sr[32], dr[32], pk[16];
+        tmem_ld32(tS[st] + lane_off + cc * 32, sr);
+        tmem_ld32(tdP + lane_off + cc * 32, dr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float d2[2];
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const int k = k0 + cc * 32 + j + e;
+            float pv = exp2f(__uint_as_float(sr[j + e]) * c - lse2);
+            if (need_mask && !(k <= q && k >= lo)) pv = 0.f;
+            d2[e] = pv * (__uint_as_float(dr[j + e]) - Dq);
+          }
+          pk[j >> 1] = pack2(d2[0], d2[1]);
+        }
+        tmem_st16(tS[st] + lane_off + cc * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_ready[st]);
+    }
+    if (ok && mbar_wait(dq_done, 0, abort_flag, a.status)) {
+      tc_fence_after();
+      bf16* dq = reinterpret_cast<bf16*>(a.dQ) + (row0 + q) * a.dq_stride + (long long)h * HD;
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t rr[32];
+        tmem_ld32(tdQ + lane_off + cc * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 qv;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&qv);
+#pragma unroll
+          for (int e = 0; e < 4; e++)
+            w[e] = pack2(__uint_as_float(rr[j + 2 * e]) * scale, __uint_as_float(rr[j + 2 * e + 1]) * scale);
+          *reinterpret_cast<uint4*>(dq + cc * 32 + j) = qv;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK / dV kernel
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* sdO = smem + 4 * TILE_BYTES;  // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;   // [2]
+  uint64_t* qdo_empty = bars + 3;  // [2]
+  uint64_t* st_full = bars + 5;    // S^T and dP^T of the current tile are in TMEM
+  uint64_t* pds_ready = bars + 6;  // P^T and dS^T written
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2][3][128]: lse2, D, lo
+
+  const AttnArgs& a = p.a;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int g = a.H / a.Hkv;
+  const int k0 = kt * BT;
+  const int ilo = kt;
+  const int ihi = (int)min((long long)a.T / BT - 1, ((long long)k0 + BT - 1 + a.window_left) / BT);
+  const int nq = ihi - ilo + 1;
+  const int nit = nq * g;
+  const long long row0 = (long long)b * a.T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    mbar_init(st_full, 1);
+    mbar_init(pds_ready, 4);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdK = tmem_base + 256, tdV = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_2d(sK, &tmK, kv_full, kvh * HD, (int)(row0 + k0));
+      tma_load_2d(sK + TILE_BYTES / 2, &tmK, kv_full, kvh * HD + 64, (int)(row0 + k0));
+      tma_load_2d(sV, &tmV, kv_full, kvh * HD, (int)(row0 + k0));
+      tma_load_2d(sV + TILE_BYTES / 2, &tmV, kv_full, kvh * HD + 64, (int)(row0 + k0));
+      for (int it = 0; it < nit; it++) {
+        const int st = it & 1;
+        const int h = kvh * g + it / nq;
+        const int qrow = (int)(row0 + (ilo + it % nq) * BT);
+        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, a.status)) break;
+        mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES);
+        tma_load_2d(sQ + st * TILE_BYTES, &tmQ, &qdo_full[st], h * HD, qrow);
+        tma_load_2d(sQ + st * TILE_BYTES + TILE_BYTES / 2, &tmQ, &qdo_full[st], h * HD + 64, qrow);
+        tma_load_2d(sdO + st * TILE_BYTES, &tmdO, &qdo_full[st], h * HD, qrow);
+        tma_load_2d(sdO + st * TILE_BYTES + TILE_BYTES / 2, &tmdO, &qdo_full[st], h * HD + 64, qrow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = idesc_bf16(BT, BT, false, false);
+      constexpr uint32_t idesc_mn = idesc_bf16(BT, HD, false, true);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      auto issue_in = [&](int it) -> bool {  // S^T = K Q^T, dP^T = V dO^T
+        const int st = it & 1;
+        if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES), do_addr = smem_u32(sdO + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(tS, smem_desc_sw128(k_addr + off, 16, 1024), smem_desc_sw128(q_addr + off, 16, 1024), idesc_kk, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(tdP, smem_desc_sw128(v_addr + off, 16, 1024), smem_desc_sw128(do_addr + off, 16, 1024), idesc_kk, k > 0);
+        }
+        tc_commit(st_full);
+        return true;
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, a.status);
+      if (ok) { tc_fence_after(); ok = issue_in(0); }
+      for (int it = 0; it < nit && ok; it++) {
+        const int st = it & 1;
+        if (!mbar_wait(pds_ready, it & 1, abort_flag, a.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES), do_addr = smem_u32(sdO + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BT / 16; k++)  // dV += P^T dO
+          mma_ts(tdV, tS + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q
+          mma_ts(tdK, tdP + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (it > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&qdo_empty[st]);
+        if (it + 1 < nit && !issue_in(it + 1)) { ok = false; break; }
+      }
+      if (ok) tc_commit(acc_done);
+    }
+  } else if (warp >= 4) {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int key = k0 + r;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float scale = rsqrtf((float)HD);
+    const float c = scale * LOG2E;
+    bool ok = true;
+    for (int it = 0; it < nit; it++) {
+      const int h = kvh * g + it / nq;
+      const int qi0 = (ilo + it % nq) * BT;
+      float* sl = stats + (it & 1) * 384;
+      {
+        const int q = qi0 + r;
+        const long long si = ((long long)b * a.H + h) * a.T + q;
+        sl[r] = a.lse[si] * LOG2E;
+        sl[128 + r] = p.D[si];
+        int lo = max(0, q - a.window_left);
+        if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
+        sl[256 + r] = __int_as_float(lo);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(st_full, it & 1, abort_flag, a.status)) { ok = false; break; }
+      tc_fence_after();
+      // tile-level mask test: any (key, q) pair of this row outside key <= q, key >= lo[q]?
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t sr[32], dr[32], pp[16], pd[16];
+        tmem_ld32(tS + lane_off + cc * 32, sr);
+        tmem_ld32(tdP + lane_off + cc * 32, dr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p2[2], d2[2];
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const int qq = cc * 32 + j + e;
+            const int q = qi0 + qq;
+            const int lo = __float_as_int(sl[256 + qq]);
+            float pv = exp2f(__uint_as_float(sr[j + e]) * c - sl[qq]);
+            if (!(key <= q && key >= lo)) pv = 0.f;
+            p2[e] = pv;
+            d2[e] = pv * (__uint_as_float(dr[j + e]) - sl[128 + qq]);
+          }
+          pp[j >> 1] = pack2(p2[0], p2[1]);
+          pd[j >> 1] = pack2(d2[0], d2[1]);
+        }
+        tmem_st16(tS + lane_off + cc * 16, pp);
+        tmem_st16(tdP + lane_off + cc * 16, pd);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+    }
+    if (ok && mbar_wait(acc_done, 0, abort_flag, a.status)) {
+      tc_fence_after();
+      bf16* dk = reinterpret_cast<bf16*>(a.dK) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
+      bf16* dv = reinterpret_cast<bf16*>(a.dV) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t rk[32], rv[32];
+        tmem_ld32(tdK + lane_off + cc * 32, rk);
+        tmem_ld32(tdV + lane_off + cc * 32, rv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 qk, qv;
+          uint32_t* wk = reinterpret_cast<uint32_t*>(&qk);
+          uint32_t* wv = reinterpret_cast<uint32_t*>(&qv);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            wk[e] = pack2(__uint_as_float(rk[j + 2 * e]) * scale, __uint_as_float(rk[j + 2 * e + 1]) * scale);
+            wv[e] = pack2(__uint_as_float(rv[j + 2 * e]), __uint_as_float(rv[j + 2 * e + 1]));
+          }
+          *reinterpret_cast<uint4*>(dk + cc * 32 + j) = qk;
+          *reinterpret_cast<uint4*>(dv + cc * 32 + j) = qv;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+}  // namespace
+
+size_t attention_bwd_tc_ws_bytes(int B, int T, int H, int) { return sizeof(float) * (size_t)B * H * T; }
+
+int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
+  if (!attention_tc_supported(a)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "attention_bwd_tc: unsupported shape");
+  if ((a.do_stride & 7) || (a.dq_stride & 7) || (a.dkv_stride & 7) || !aligned16(a.dO) || !aligned16(a.dQ) ||
+      !aligned16(a.dK) || !aligned16(a.dV))
+    return femto_fail(FEMTO_ERR_ALIGN, "attention_bwd_tc: gradient buffers must be 16-byte aligned");
+  const size_t need = attention_bwd_tc_ws_bytes(a.B, a.T, a.H, a.hd);
+  if (!a.ws || a.ws_bytes < need) return femto_fail(FEMTO_ERR_ARG, "attention_bwd_tc: workspace too small");
+  const long long N = (long long)a.B * a.T;
+  BwdParams p;
+  p.a = a;
+  p.D = reinterpret_cast<const float*>(a.ws);
+  attn_bwd_prep_kernel<<<cdiv(N * a.H, 8), 256, 0, s>>>(a, reinterpret_cast<float*>(a.ws));
+  KERNEL_CHECK();
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  FEMTO_TRY(make_tmap_2d_bf16(&tmQ, a.Q, (uint64_t)a.H * HD, N, a.q_stride, 64, BT));
+  FEMTO_TRY(make_tmap_2d_bf16(&tmK, a.K, (uint64_t)a.Hkv * HD, N, a.kv_stride, 64, BT));
+  FEMTO_TRY(make_tmap_2d_bf16(&tmV, a.V, (uint64_t)a.Hkv * HD, N, a.kv_stride, 64, BT));
+  FEMTO_TRY(make_tmap_2d_bf16(&tmdO, a.dO, (uint64_t)a.H * HD, N, a.do_stride, 64, BT));
+  static bool attr_done = false;
+  if (!attr_done) {
+    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
+    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
+    attr_done = true;
+  }
+  dim3 gq(a.T / BT, a.H, a.B);
+  attn_bwd_dq_kernel<<<gq, 256, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  KERNEL_CHECK();
+  dim3 gk(a.T / BT, a.Hkv, a.B);
+  attn_bwd_dkv_kernel<<<gk, 256, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  KERNEL_CHECK();
+  return 0;
+}

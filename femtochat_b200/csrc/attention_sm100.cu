@@ -1,5 +1,298 @@
-#include "common.cuh"
-bool attention_tc_supported(const AttnArgs&) { return false; }
-int attention_fwd_tc(const AttnArgs&, cudaStream_t) { return femto_fail(FEMTO_ERR_UNSUPPORTED, "tcgen05 attention not built"); }
-int attention_bwd_tc(const AttnArgs&, cudaStream_t) { return femto_fail(FEMTO_ERR_UNSUPPORTED, "tcgen05 attention not built"); }
-size_t attention_bwd_tc_ws_bytes(int, int, int, int) { return 0; }
+// Flash attention for head_dim 128 in bf16 on the sm_100a tensor cores: causal mask with a
+// sliding window (keys t-left..t) and an optional per-document lower bound, GQA by
+// kv_head = head / (H/Hkv).  Replaces the reference's mma.sync kernels
+// (ext/FemtoChatCUDAExt.jl:1295-1463 forward, :1829-2068 reverse); arithmetic follows
+// src/kernels.jl:131-219 and :287-379 (softmax in base 2, fp32 statistics).
+//
+// Forward: one CTA owns 128 queries of one (batch, head).  Warp 0 streams K/V tiles of 128 keys
+// with TMA (two stages each), warp 1 issues tcgen05.mma: S = Q K^T into one of two 128-column
+// TMEM buffers, then O += P V with P read back from TMEM (P overwrites S in place as bf16).
+// Warps 4-7 own one query row per thread: they read S with tcgen05.ld, keep the running
+// max / sum, rescale the TMEM-resident O only when the max grew by more than 2^8, and write P
+// with tcgen05.st.  S of tile j+1 is computed while the softmax of tile j runs.
+#include <algorithm>
+
+#include "sm100_ptx.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int HD = 128, BQ = 128, BKV = 128;
+constexpr int TILE_BYTES = BQ * HD * 2;  // 32 KB: two [128][64] swizzled slabs
+constexpr int FWD_SMEM = TILE_BYTES * 5 + 1024 + 256;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct FwdParams {
+  AttnArgs a;
+  int q_col0, k_col0, v_col0;  // column offsets (elements) of head 0 inside the Q / K / V tensor maps
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(256, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;       // 2 stages
+  uint8_t* sV = smem + 3 * TILE_BYTES;   // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 5 * TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* p_ready = bars + 11;  // [2]
+  uint64_t* pv_done = bars + 13;  // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const AttnArgs& a = p.a;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) query tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (a.H / a.Hkv);
+  const int q0 = qt * BQ;
+  const int jhi = min(q0 + BQ - 1, a.T - 1) / BKV;
+  int jlo = max(0, q0 - a.window_left) / BKV;
+  const int ntile = jhi - jlo + 1;
+  const long long row0 = (long long)b * a.T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 4);
+    }
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_2d(sQ, &tmQ, q_full, p.q_col0 + h * HD, (int)(row0 + q0));
+      tma_load_2d(sQ + TILE_BYTES / 2, &tmQ, q_full, p.q_col0 + h * HD + 64, (int)(row0 + q0));
+      bool ok = true;
+      for (int i = 0; i < ntile && ok; i++) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int krow = (int)(row0 + (jlo + i) * BKV);
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, a.status)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        tma_load_2d(sK + st * TILE_BYTES, &tmK, &k_full[st], p.k_col0 + kvh * HD, krow);
+        tma_load_2d(sK + st * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[st], p.k_col0 + kvh * HD + 64, krow);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, a.status)) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        tma_load_2d(sV + st * TILE_BYTES, &tmV, &v_full[st], p.v_col0 + kvh * HD, krow);
+        tma_load_2d(sV + st * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[st], p.v_col0 + kvh * HD + 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // S = Q K^T, both K-major
+      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // O = P V, V is N-contiguous
+      const uint32_t q_addr = smem_u32(sQ);
+      auto issue_s = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag, a.status)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0);
+        }
+        tc_commit(&s_full[st]);
+        tc_commit(&k_empty[st]);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
+      if (ok) { tc_fence_after(); ok = issue_s(0); }
+      for (int i = 0; i < ntile && ok; i++) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (i + 1 < ntile && !issue_s(i + 1)) { ok = false; break; }
+        if (!mbar_wait(&p_ready[st], ph, abort_flag, a.status)) { ok = false; break; }
+        if (!mbar_wait(&v_full[st], ph, abort_flag, a.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; k++) {
+          // A: 16 keys of P = 8 TMEM columns; B: 16 key rows of the [128][64] slabs = 2048 B, the two
+          // 64-wide head_dim halves 16 KB apart.
+          mma_ts(tO, tS[st] + k * 8, smem_desc_sw128(v_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(pv_done);
+        tc_commit(&v_empty[st]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- softmax, one query row per thread ----------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int q = q0 + r;
+    const bool row_ok = q < a.T;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float c = rsqrtf((float)HD) * LOG2E;
+    int lo = max(0, q - a.window_left);
+    if (a.doc_start && row_ok) lo = max(lo, a.doc_start[row0 + q]);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < ntile; i++) {
+      const int st = i & 1;
+      const uint32_t ph = (i >> 1) & 1;
+      const int k0 = (jlo + i) * BKV;
+      if (!mbar_wait(&s_full[st], ph, abort_flag, a.status)) { ok = false; break; }
+      tc_fence_after();
+      float x[BKV];
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t rr[32];
+        tmem_ld32(tS[st] + lane_off + cc * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j++) x[cc * 32 + j] = __uint_as_float(rr[j]) * c;
+      }
+      const bool need_mask = (k0 + BKV - 1 > q) || (k0 < lo);
+      float mt = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < BKV; j++) {
+          const int k = k0 + j;
+          x[j] = (k <= q && k >= lo) ? x[j] : -INFINITY;
+          mt = fmaxf(mt, x[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < BKV; j++) mt = fmaxf(mt, x[j]);
+      }
+      const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_used, mt);
+        const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        l *= alpha;
+        m_used = m_new;
+        if (i > 0) {
+          // O lives in TMEM and is being accumulated by the tensor core: wait for tile i-1's P V
+          if (!mbar_wait(pv_done, (i - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < 4; cc++) {
+            uint32_t rr[32];
+            tmem_ld32(tO + lane_off + cc * 32, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j++) rr[j] = __float_as_uint(__uint_as_float(rr[j]) * alpha);
+            tmem_st32(tO + lane_off + cc * 32, rr);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float mm = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const float p0 = exp2f(x[cc * 32 + 2 * j] - mm), p1 = exp2f(x[cc * 32 + 2 * j + 1] - mm);
+          sum += p0 + p1;
+          pk[j] = pack_bf16(p0, p1);
+        }
+        tmem_st16(tS[st] + lane_off + cc * 16, pk);
+      }
+      l += sum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[st]);
+    }
+    if (ok && mbar_wait(pv_done, (ntile - 1) & 1, abort_flag, a.status)) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+      bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+        uint32_t rr[32];
+        tmem_ld32(tO + lane_off + cc * 32, rr);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 qv;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&qv);
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+              w[e] = pack_bf16(__uint_as_float(rr[j + 2 * e]) * inv, __uint_as_float(rr[j + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(o + cc * 32 + j) = qv;
+          }
+        }
+      }
+      if (row_ok) {
+        const long long si = ((long long)b * a.H + h) * a.T + q;
+        const float ln2 = 0.6931471805599453f;
+        if (a.lse) a.lse[si] = (m_used + log2f(l)) * ln2;
+        if (a.l) a.l[si] = l;
+        if (a.m) a.m[si] = m_used * ln2;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+bool attention_tc_supported(const AttnArgs& a) {
+  if (a.hd != HD) return false;
+  if (a.T % BQ != 0) return false;
+  if ((a.q_stride & 7) || (a.kv_stride & 7) || (a.o_stride & 7)) return false;
+  if (!aligned16(a.Q) || !aligned16(a.K) || !aligned16(a.V) || !aligned16(a.O)) return false;
+  if (a.H % a.Hkv != 0) return false;
+  return true;
+}
+
+int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
+  if (!attention_tc_supported(a)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "attention_fwd_tc: unsupported shape");
+  const long long N = (long long)a.B * a.T;
+  CUtensorMap tmQ, tmK, tmV;
+  FEMTO_TRY(make_tmap_2d_bf16(&tmQ, a.Q, (uint64_t)a.H * HD, N, a.q_stride, 64, BQ));
+  FEMTO_TRY(make_tmap_2d_bf16(&tmK, a.K, (uint64_t)a.Hkv * HD, N, a.kv_stride, 64, BKV));
+  FEMTO_TRY(make_tmap_2d_bf16(&tmV, a.V, (uint64_t)a.Hkv * HD, N, a.kv_stride, 64, BKV));
+  FwdParams p;
+  p.a = a;
+  p.q_col0 = 0; p.k_col0 = 0; p.v_col0 = 0;
+  static bool attr_done = false;
+  if (!attr_done) {
+    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
+    attr_done = true;
+  }
+  dim3 grid(a.T / BQ, a.H, a.B);
+  attn_fwd_tc_kernel<<<grid, 256, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
+  KERNEL_CHECK();
+  return 0;
+}
+

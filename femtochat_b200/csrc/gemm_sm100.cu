@@ -392,6 +392,23 @@ int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t dim0, uint64_
   return 0;
 }
 
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_elems,
+                      uint32_t box0, uint32_t box1) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return femto_fail(FEMTO_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {dim0, dim1};
+  cuuint64_t strides[1] = {stride1_elems * 2};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return femto_fail(FEMTO_ERR_ALIGN, "cuTensorMapEncodeTiled (2d) failed (%d): dims %llu x %llu, row stride %llu B", (int)r,
+                      (unsigned long long)dim0, (unsigned long long)dim1, (unsigned long long)strides[0]);
+  return 0;
+}
+
 bool gemm_tc_supported(const GemmArgs& g) {
   if (g.M < BM || g.N < BN || g.K < BK) return false;
   if ((g.lda & 7) || (g.ldb & 7) || (g.strideA & 7) || (g.strideB & 7)) return false;
