@@ -79,6 +79,8 @@ SIGNATURES = {
     "femto_status_word": (I32, [P, C.POINTER(I32)]),
     "femto_sync": (I32, [P, P]),
     "femto_launch_count": (I64, [P]),
+    "femto_profile_gemm": (I32, [I32]),
+    "femto_profile_gemm_report": (I32, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(I32)]),
 }
 
 

@@ -12,6 +12,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <vector>
 
 #include "sm100_ptx.cuh"
 
@@ -439,6 +440,36 @@ static int num_sms() {
   return n;
 }
 
+// Optional per-launch timing of the GEMM kernel (measurement aid, off by default).
+namespace {
+struct GemmProfile {
+  bool on = false;
+  std::vector<cudaEvent_t> ev;
+  double flops = 0.0;
+} g_prof;
+}  // namespace
+
+extern "C" int32_t femto_profile_gemm(int32_t enable) {
+  for (auto e : g_prof.ev) cudaEventDestroy(e);
+  g_prof.ev.clear();
+  g_prof.flops = 0.0;
+  g_prof.on = enable != 0;
+  return 0;
+}
+extern "C" int32_t femto_profile_gemm_report(double* h_ms, double* h_flops, int32_t* h_launches) {
+  double ms = 0.0;
+  for (size_t i = 0; i + 1 < g_prof.ev.size(); i += 2) {
+    cudaEventSynchronize(g_prof.ev[i + 1]);
+    float t = 0.f;
+    cudaEventElapsedTime(&t, g_prof.ev[i], g_prof.ev[i + 1]);
+    ms += t;
+  }
+  if (h_ms) *h_ms = ms;
+  if (h_flops) *h_flops = g_prof.flops;
+  if (h_launches) *h_launches = (int32_t)(g_prof.ev.size() / 2);
+  return 0;
+}
+
 int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   if (!gemm_tc_supported(g)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "gemm_tc: shape/alignment not supported");
   TcParams p;
@@ -483,10 +514,20 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
     CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_done = true;
   }
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (g_prof.on) {
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaEventRecord(e0, s);
+  }
   if (g.a_kmajor && g.b_kmajor) gemm_tc_kernel<true, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
   else if (g.a_kmajor) gemm_tc_kernel<true, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
   else if (g.b_kmajor) gemm_tc_kernel<false, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
   else gemm_tc_kernel<false, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
+  if (g_prof.on) {
+    cudaEventRecord(e1, s);
+    g_prof.ev.push_back(e0); g_prof.ev.push_back(e1);
+    g_prof.flops += 2.0 * g.M * (double)g.N * g.K * g.batch;
+  }
   KERNEL_CHECK();
   if (splits > 1) {
     gemm_tc_reduce_kernel<<<tiles, 256, 0, s>>>(p);

@@ -188,6 +188,12 @@ int32_t femto_sync(femto_handle* h, void* stream);
 /* Number of kernels launched by this handle since creation (host counter). */
 int64_t femto_launch_count(femto_handle* h);
 
+/* Measurement aid (no counterpart in the reference): when enabled, every launch of the tensor-core
+ * GEMM kernel is bracketed by CUDA events on its stream; the report returns the summed kernel time,
+ * the summed 2*M*N*K and the launch count since the last femto_profile_gemm call. */
+int32_t femto_profile_gemm(int32_t enable);
+int32_t femto_profile_gemm_report(double* h_ms, double* h_flops, int32_t* h_launches);
+
 #ifdef __cplusplus
 }
 #endif
