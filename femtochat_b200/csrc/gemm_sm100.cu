@@ -2,7 +2,7 @@
 //
 // One persistent CTA per SM walks a list of (tile, k-range) units.  Warp 0 issues TMA tiled loads
 // (128-byte swizzle) into a 4-stage shared-memory ring, warp 1 issues tcgen05.mma (128x256x16 per
-// instruction) into one of two 256-column TMEM accumulators, warps 2-5 drain the other accumulator
+// instruction) into one of two 256-column TMEM accumulators, warps 2-9 drain the other accumulator
 // with tcgen05.ld and run the epilogue, so the epilogue of unit i overlaps the main loop of unit
 // i+1.  Operands may be K-contiguous or M/N-contiguous in memory (the D x T x B layout of the
 // reference makes the weight of a forward Linear N-contiguous and both operands of a weight
@@ -23,7 +23,7 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int TMEM_COLS = 512;
 
 struct TcParams {
@@ -32,6 +32,11 @@ struct TcParams {
   float* partial;  // [unit][8 chunks][128 rows][32 cols] when splits > 1
 };
 
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float softcap15(float x) {
   // 15 * tanh(x/15) with tanh(y) = 1 - 2/(exp(2y)+1)
   float e = __expf(x * (2.f / 15.f));
@@ -75,7 +80,7 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
     float x = v[j];
     if constexpr (EPI == EPI_RESID) x = a[j] + x;
     if constexpr (EPI == EPI_RELU2) { x = fmaxf(x, 0.f); x = x * x; }
-    if constexpr (EPI == EPI_DRELU2) x = x * 2.f * sqrtf(fmaxf(a[j], 0.f));
+    if constexpr (EPI == EPI_DRELU2) x = x * 2.f * sqrt_approx(fmaxf(a[j], 0.f));
     if constexpr (EPI == EPI_AXPBY) x = alpha * a[j] + beta * x;
     if constexpr (EPI == EPI_XENT_DLOGIT) {
       float z = softcap15(x);
@@ -123,7 +128,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int i = 0; i < 2; i++) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 8); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -221,8 +226,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
+    // ---------------- epilogue (warps 2..9) ----------------
     const int quad = warp & 3;           // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;    // the two warps of a quadrant take alternate 32-column chunks
     const int row_in_tile = quad * 32 + lane;
     int acc = 0; uint32_t acc_phase = 0;
     for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
@@ -245,7 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
+      for (int c = half; c < BN / 32; c += 2) {
         uint32_t r[32];
         __syncwarp();
         if (g.dbg == 2) continue;
@@ -314,7 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           default: break;
         }
       }
-      if (g.epi == EPI_XENT_STATS && row_ok && p.splits == 1) g.stats[(long long)m * p.tiles_n + nt] = make_float2(rmax, rsum);
+      if (g.epi == EPI_XENT_STATS && row_ok && p.splits == 1) g.stats[((long long)m * p.tiles_n + nt) * 2 + half] = make_float2(rmax, rsum);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);

@@ -185,7 +185,7 @@ void carve(femto_handle* h, Bump& b) {
   b.take(h->partial, 4 * (size_t)std::max<size_t>(1024 * 32, (N / 256 + 1) * 12 * h->Hkv));
   const size_t xc = h->xchunk;
   if (!h->bf || 4 * xc * Vp <= ((size_t)512 << 20)) b.take(h->logits_f32, 4 * xc * Vp); else h->logits_f32 = nullptr;
-  b.take(h->xstats, sizeof(float2) * xc * ((h->V + 255) / 256 + 1));
+  b.take(h->xstats, sizeof(float2) * xc * (2 * ((h->V + 255) / 256) + 2));
   b.take(h->tz, 4 * N); b.take(h->lse_rows, 4 * N); b.take(h->loss_rows, 4 * N); b.take(h->inv_nvalid, 256);
   b.take(h->dlogit, es * xc * Vp);
   b.take(h->loss_dev, 256); b.take(h->nvalid_dev, 256);

@@ -23,7 +23,7 @@ template <typename T> int xent_tail(const XentArgs& x, cudaStream_t s) {
     const bool tc = sizeof(T) == 2 && gemm_tc_supported(g);
     if (tc) {
       FEMTO_TRY(gemm_tc_bf16(g, s));
-      FEMTO_TRY(xent_finalize(x.stats, (V + 255) / 256, x.tz + c0, x.targets0 + c0, cn, x.lse_rows + c0,
+      FEMTO_TRY(xent_finalize(x.stats, 2 * ((V + 255) / 256), x.tz + c0, x.targets0 + c0, cn, x.lse_rows + c0,
                               x.loss_rows + c0, s));
       if (x.backward) {
         g.epi = EPI_XENT_DLOGIT; g.C = x.dlogit; g.ldc = ld; g.lse = x.lse_rows + c0;
@@ -67,7 +67,7 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
   const size_t wsb = (size_t)160 << 20;
   const bool need_f32 = dtype != FEMTO_BF16 || (D % 8) != 0 || (ldw % 8) != 0 || N < 128;
-  size_t total = al(need_f32 ? 4 * (size_t)chunk * ldw : 0) + al(sizeof(float2) * (size_t)chunk * ((V + 255) / 256 + 1)) +
+  size_t total = al(need_f32 ? 4 * (size_t)chunk * ldw : 0) + al(sizeof(float2) * (size_t)chunk * (2 * ((V + 255) / 256) + 2)) +
                  3 * al(4 * (size_t)N) + al(es * (size_t)chunk * ldw) + wsb + 1024;
   char* buf = nullptr;
   CUDA_TRY(cudaMalloc(&buf, total));
@@ -76,7 +76,7 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   a.x = x; a.W = W; a.ldw = ldw; a.targets0 = targets0; a.N = N; a.D = D; a.V = V; a.scale = scale;
   a.backward = dx != nullptr; a.dx = dx; a.dw = dw; a.chunk = chunk;
   if (need_f32) { a.logits_f32 = (float*)p; p += al(4 * (size_t)chunk * ldw); }
-  a.stats = (float2*)p; p += al(sizeof(float2) * (size_t)chunk * ((V + 255) / 256 + 1));
+  a.stats = (float2*)p; p += al(sizeof(float2) * (size_t)chunk * (2 * ((V + 255) / 256) + 2));
   a.tz = (float*)p; p += al(4 * (size_t)N);
   a.lse_rows = (float*)p; p += al(4 * (size_t)N);
   a.loss_rows = (float*)p; p += al(4 * (size_t)N);
