@@ -153,6 +153,18 @@ int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const v
                             const void* K, const void* V, const void* O, const float* lse, int32_t B,
                             int32_t T, int32_t H, int32_t Hkv, int32_t hd, int32_t window_left,
                             const int32_t* doc_start, void* stream);
+/* Same computation as femto_attention_bwd for callers that cannot allocate device memory (a host
+ * runtime that owns the whole device pool, or a phase in which cudaMalloc is forbidden or would
+ * stall the device).  No counterpart in the reference.  The scratch (one float per (batch, head,
+ * query)) lives in a 4 MiB array compiled into the library, so the call is limited to
+ * B*H*T <= 1 048 576 and fails with FEMTO_ERR_SHAPE beyond that; it never calls cudaMalloc/cudaFree.
+ * The first call on a device looks up the array's device address (make that call before any stream
+ * capture).  All calls on a device share the array: calls that overlap on the GPU (different
+ * streams) race; calls on one stream are safe.  Asynchronous on `stream`. */
+int32_t femto_attention_bwd_static(int32_t dtype, void* dQ, void* dK, void* dV, const void* dO, const void* Q,
+                                   const void* K, const void* V, const void* O, const float* lse, int32_t B,
+                                   int32_t T, int32_t H, int32_t Hkv, int32_t hd, int32_t window_left,
+                                   const int32_t* doc_start, void* stream);
 /* C[M][N] = A[M][K] * B[K][N] in bf16 with fp32 accumulation on the tcgen05 path; each operand may be
  * stored K-contiguous (kmajor=1) or M/N-contiguous (kmajor=0); replaces the cuBLAS calls behind the
  * generic `W*X` (src/gpt.jl:28) and batched_mul! (ext/FemtoChatCUDAExt.jl:121-125).  out_f32=1 writes
