@@ -66,7 +66,13 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   const int chunk = std::min(N, 8192);
   auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
   const size_t wsb = (size_t)160 << 20;
-  const bool need_f32 = dtype != FEMTO_BF16 || (D % 8) != 0 || (ldw % 8) != 0 || N < 128;
+  bool need_f32 = dtype != FEMTO_BF16;
+  if (!need_f32) {  // the fp32 logits chunk is needed whenever the tensor-core GEMM does not take the shape
+    GemmArgs g;
+    g.A = x; g.lda = D; g.B = W; g.ldb = ldw; g.b_kmajor = false; g.M = chunk; g.N = V; g.K = D;
+    g.epi = EPI_XENT_STATS; g.stats = reinterpret_cast<float2*>(1); g.tz = reinterpret_cast<float*>(1); g.targets0 = targets0;
+    need_f32 = !gemm_tc_supported(g);
+  }
   size_t total = al(need_f32 ? 4 * (size_t)chunk * ldw : 0) + al(sizeof(float2) * (size_t)chunk * (2 * ((V + 255) / 256) + 2)) +
                  3 * al(4 * (size_t)N) + al(es * (size_t)chunk * ldw) + wsb + 1024;
   char* buf = nullptr;

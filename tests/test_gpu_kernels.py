@@ -1,0 +1,232 @@
+"""GPU parity of the kernel-level C-ABI entry points against the CPU oracle (oracle/femto_oracle.py)."""
+import ctypes as C
+import math
+import os
+
+import pytest
+import torch
+
+import femtochat_b200 as fb
+from femtochat_b200 import _lib
+from oracle import femto_oracle as fo
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def cosine(a, b):
+    a, b = a.double().flatten().cpu(), b.double().flatten().cpu()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-300))
+
+
+# ---- GEMM -------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("ak", [True, False])
+@pytest.mark.parametrize("bk", [True, False])
+@pytest.mark.parametrize("shape", [(256, 512, 320, 1), (264, 264, 136, 1), (384, 640, 1280, 3)])
+def test_gemm_bf16_all_operand_layouts(ak, bk, shape):
+    """Every combination of K-contiguous / MN-contiguous operands, ragged tails, batches."""
+    M, N, K, batch = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    A = torch.randn(batch, M, K, generator=g, device="cuda").bfloat16()
+    B = torch.randn(batch, K, N, generator=g, device="cuda").bfloat16()
+    As = A.contiguous() if ak else A.transpose(1, 2).contiguous()
+    Bs = B.transpose(1, 2).contiguous() if bk else B.contiguous()
+    Cc = torch.empty(batch, M, N, device="cuda", dtype=torch.bfloat16)
+    _lib.check(_lib.lib().femto_gemm_bf16(_lib.ptr(As), int(ak), K if ak else M, _lib.ptr(Bs), int(bk), K if bk else N,
+                                          _lib.ptr(Cc), N, M, N, K, batch, M * K, K * N, M * N, 0, 0, None))
+    torch.cuda.synchronize()
+    ref = torch.bmm(A.double().cpu(), B.double().cpu())      # exact products of the bf16 inputs
+    err = (Cc.double().cpu() - ref).abs().max()
+    assert err <= 2.0 ** -8 * ref.abs().max()               # one bf16 rounding of the result
+
+
+def test_gemm_split_k_fp32_accumulate_is_deterministic():
+    """Weight-gradient form: both operands MN-contiguous, K = tokens, fp32 C += ; split-K reduce in fixed order."""
+    M, N, K = 1280, 1280, 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A = torch.randn(K, M, generator=g, device="cuda").bfloat16()
+    B = torch.randn(K, N, generator=g, device="cuda").bfloat16()
+    outs = []
+    for _ in range(2):
+        Cc = torch.ones(M, N, device="cuda")
+        _lib.check(_lib.lib().femto_gemm_bf16(_lib.ptr(A), 0, M, _lib.ptr(B), 0, N, _lib.ptr(Cc), N, M, N, K, 1, 0, 0, 0,
+                                              1, 1, None))
+        torch.cuda.synchronize()
+        outs.append(Cc.cpu())
+    ref = 1.0 + A.double().cpu().T @ B.double().cpu()
+    assert (outs[0].double() - ref).abs().max() <= 1e-5 * ref.abs().max()
+    assert torch.equal(outs[0], outs[1])
+
+
+# ---- attention ----------------------------------------------------------------------------------------
+def _attn_inputs(dtype, B, T, H, Hkv, hd, seed, docs):
+    g = torch.Generator().manual_seed(seed)
+    td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
+    mk = lambda *s: torch.randn(*s, generator=g).to(td)
+    Q, K, V, dO = mk(B, T, H, hd), mk(B, T, Hkv, hd), mk(B, T, Hkv, hd), mk(B, T, H, hd)
+    ds = None
+    if docs:
+        pos = (torch.arange(T)[None, :].repeat(B, 1) + 7 * torch.arange(B)[:, None]) % 61
+        ds = fo.document_starts(pos).int().contiguous()
+    return Q, K, V, dO, ds
+
+
+@pytest.mark.parametrize("dtype,B,T,H,Hkv,hd,left,docs", [
+    (_lib.F32, 2, 40, 4, 2, 16, 40, False), (_lib.F32, 2, 40, 4, 1, 16, 7, True), (_lib.F32, 1, 33, 2, 2, 64, 33, False),
+    (_lib.BF16, 2, 256, 4, 2, 128, 256, False), (_lib.BF16, 2, 512, 4, 2, 128, 100, True),
+    (_lib.BF16, 1, 1024, 10, 5, 128, 300, True), (_lib.BF16, 2, 96, 2, 1, 64, 30, False)])
+def test_attention_forward_and_reverse(dtype, B, T, H, Hkv, hd, left, docs):
+    """attention! / Δattention! against naive_attention (src/kernels.jl:59-96) and the blockwise reverse."""
+    Q, K, V, dO, ds = _attn_inputs(dtype, B, T, H, Hkv, hd, seed=T + hd, docs=docs)
+    Qd, Kd, Vd, dOd = (x.double() for x in (Q, K, V, dO))
+    O_ref = fo.naive_attention(Qd, Kd, Vd, (left, 0), ds.long() if ds is not None else None)
+    _, l_ref, m_ref = fo.flash_attention_forward(Qd, Kd, Vd, (left, 0), ds.long() if ds is not None else None)
+    dq_ref, dk_ref, dv_ref = fo.flash_attention_backward(dOd, Qd, Kd, Vd, O_ref, l_ref, m_ref, (left, 0),
+                                                         ds.long() if ds is not None else None)
+    dev = [x.cuda() for x in (Q, K, V, dO)]
+    dsd = ds.cuda() if ds is not None else None
+    O = torch.zeros_like(dev[0])
+    lse, l, m = (torch.zeros(B, H, T, device="cuda") for _ in range(3))
+    L = _lib.lib()
+    _lib.check(L.femto_attention_fwd(dtype, _lib.ptr(O), _lib.ptr(l), _lib.ptr(m), _lib.ptr(lse), _lib.ptr(dev[0]),
+                                     _lib.ptr(dev[1]), _lib.ptr(dev[2]), B, T, H, Hkv, hd, left, _lib.ptr(dsd), None))
+    dQ, dK, dV = torch.zeros_like(dev[0]), torch.zeros_like(dev[1]), torch.zeros_like(dev[2])
+    _lib.check(L.femto_attention_bwd(dtype, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dev[3]), _lib.ptr(dev[0]),
+                                     _lib.ptr(dev[1]), _lib.ptr(dev[2]), _lib.ptr(O), _lib.ptr(lse), B, T, H, Hkv, hd, left,
+                                     _lib.ptr(dsd), None))
+    torch.cuda.synchronize()
+    tol = 2e-2 if dtype == _lib.BF16 else 2e-5
+    assert (O.double().cpu() - O_ref).abs().max() <= tol
+    lse_ref = m_ref + torch.log(l_ref)
+    assert (lse.double().cpu() - lse_ref).abs().max() <= (1e-3 if dtype == _lib.BF16 else 1e-5)
+    assert ((m + torch.log(l)).double().cpu() - lse_ref).abs().max() <= (1e-3 if dtype == _lib.BF16 else 1e-5)
+    for got, ref in ((dQ, dq_ref), (dK, dk_ref), (dV, dv_ref)):
+        rel = (got.double().cpu() - ref).norm() / ref.norm()
+        assert rel <= (1e-2 if dtype == _lib.BF16 else 1e-5), rel
+
+
+# ---- embedding gradient ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [_lib.F32, _lib.BF16])
+def test_embedding_gradient_segmented_scatter(dtype):
+    """embedding_gradient! (src/kernels.jl:8-14) with a Zipf-like token list (one id 3000 times, BOS
+    runs, unseen rows): fixed summation order -> repeatable bit for bit; unseen rows untouched."""
+    N, D, rows = 8192, 256, 4096
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, rows, (N,), generator=g, dtype=torch.int32)
+    tok[:3000] = 17
+    tok[3000:3100] = rows - 1
+    tok = tok[torch.randperm(N, generator=g)]
+    td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
+    dy = torch.randn(N, D, generator=g).to(td)
+    ref = torch.full((rows, D), 0.5, dtype=torch.float64)
+    ref.index_add_(0, tok.long(), dy.double())
+    outs = []
+    for _ in range(2):
+        table = torch.full((rows, D), 0.5, device="cuda")
+        dyd, tokd = dy.cuda(), tok.cuda()          # keep the device copies alive across the call
+        _lib.check(_lib.lib().femto_embedding_gradient(dtype, _lib.ptr(table), _lib.ptr(dyd), _lib.ptr(tokd), N, D, rows,
+                                                       None))
+        outs.append(table.cpu())
+    assert (outs[0].double() - ref).abs().max() <= 1e-3
+    assert torch.equal(outs[0], outs[1])
+    unseen = torch.ones(rows, dtype=torch.bool)
+    unseen[tok.long()] = False
+    assert torch.equal(outs[0][unseen], torch.full_like(outs[0][unseen], 0.5))
+
+
+# ---- lm_head tail -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,N,D,V,ldw", [(_lib.F32, 70, 32, 50, 64), (_lib.BF16, 512, 256, 1000, 1024),
+                                              (_lib.BF16, 300, 64, 100, 128)])
+def test_xent_fused_tail(dtype, N, D, V, ldw):
+    g = torch.Generator().manual_seed(9)
+    td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
+    x = fo.norm(torch.randn(N, D, generator=g), 1e-6).to(td)
+    W = (torch.randn(D, ldw, generator=g) * 0.5).to(td)
+    tgt = torch.randint(0, V, (N,), generator=g, dtype=torch.int32)
+    tgt[::13] = -1
+    xd, Wd = x.double().requires_grad_(True), W.double().requires_grad_(True)
+    z = fo.SOFTCAP * torch.tanh(xd @ Wd[:, :V] / fo.SOFTCAP)
+    valid = tgt >= 0
+    losses = torch.logsumexp(z, -1) - z.gather(1, tgt.clamp(min=0).long()[:, None])[:, 0]
+    loss_ref = losses[valid].sum()
+    loss_ref.backward()
+    dx = torch.zeros(N, D, device="cuda", dtype=td)
+    dw = torch.ones(D, ldw, device="cuda")
+    loss = torch.zeros(1, device="cuda")
+    nv = torch.zeros(1, device="cuda", dtype=torch.int32)
+    xg, Wg, tg = x.cuda(), W.cuda(), tgt.cuda()   # keep the device copies alive across the call
+    _lib.check(_lib.lib().femto_xent_fused(dtype, _lib.ptr(xg), _lib.ptr(Wg), ldw, _lib.ptr(tg), N, D, V, 1.0, _lib.ptr(dx),
+                                           _lib.ptr(dw), _lib.ptr(loss), _lib.ptr(nv), None))
+    torch.cuda.synchronize()
+    assert int(nv.item()) == int(valid.sum())
+    tol = 1e-2 if dtype == _lib.BF16 else 1e-5
+    assert abs(float(loss.item()) - float(loss_ref.detach())) <= tol * abs(float(loss_ref.detach()))
+    assert cosine(dx, xd.grad) >= (0.999 if dtype == _lib.BF16 else 0.999999)
+    assert cosine(dw[:, :V] - 1.0, Wd.grad[:, :V]) >= (0.999 if dtype == _lib.BF16 else 0.999999)
+    assert torch.equal(dw[:, V:].cpu(), torch.ones(D, ldw - V))      # padded vocabulary columns untouched
+
+
+# ---- optimiser ------------------------------------------------------------------------------------------------
+def test_adamw_matches_oracle_three_steps():
+    n = 10007
+    g = torch.Generator().manual_seed(2)
+    theta = torch.randn(n, generator=g)
+    spec = fo.Spec(0, (n,))
+    st = fo.AdamWState(spec, 0.03, 0.8, 0.95, 1e-10, 0.05)
+    th_ref = theta.clone()
+    th, m, v = theta.cuda(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    for t in range(1, 4):
+        d = torch.randn(n, generator=g) * 4
+        gg = d / 64.0
+        st.t += 1
+        st.m.mul_(st.b1).add_((1 - st.b1) * gg)
+        st.v.mul_(st.b2).add_((1 - st.b2) * gg * gg)
+        th_ref = th_ref * (1 - st.alpha * st.lam) - st.alpha * (st.m / (1 - st.b1 ** st.t)) / (
+            torch.sqrt(st.v / (1 - st.b2 ** st.t)) + st.eps)
+        dd = d.cuda()
+        _lib.check(_lib.lib().femto_adamw(_lib.ptr(th), _lib.ptr(dd), _lib.ptr(m), _lib.ptr(v), n, 0.03, 0.8, 0.95, 1e-10,
+                                          0.05, t, 64.0, None))
+        torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    assert (th.cpu() - th_ref).abs().max() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype,k,rows,cols", [(_lib.F32, 3, 24, 48), (_lib.F32, 2, 48, 24), (_lib.F32, 2, 32, 32),
+                                                (_lib.BF16, 2, 256, 512), (_lib.BF16, 2, 512, 256)])
+def test_newton_schulz_matches_polar_express(dtype, k, rows, cols):
+    """polar_express! (src/optim.jl:131-149) with the reference's five coefficient triples."""
+    g = torch.Generator().manual_seed(rows + cols)
+    G = torch.randn(k, rows, cols, generator=g)
+    ref = fo.polar_express(G.double())
+    X = G / (1.01 * G.pow(2).sum(dim=(1, 2), keepdim=True).sqrt() + 1e-6)
+    td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
+    Xd = X.to(td).cuda().contiguous()
+    coeffs = (C.c_float * 15)(*[c for abc in fo.POLAR_EXPRESS_COEFFS for c in abc])
+    _lib.check(_lib.lib().femto_newton_schulz(dtype, _lib.ptr(Xd), k, rows, cols, coeffs, 5, None))
+    torch.cuda.synchronize()
+    if dtype == _lib.F32:
+        assert (Xd.double().cpu() - ref).abs().max() <= 1e-4
+    else:
+        assert cosine(Xd, ref) >= 0.995
+
+
+def test_muon_adamw_three_steps_against_golden():
+    """The whole MuonAdamW step (group order, MuonEq, Polar Express, Muon+, NorMuon, cautious decay)
+    in fp32 against the oracle fixture."""
+    gold = torch.load(os.path.join(GOLD, "optimizer_small.pt"))
+    kw = dict(sequence_len=32, max_document_tokens=64, vocab_size=96, n_layer=2, n_head=4, n_kv_head=2, n_embed=64,
+              window_pattern="SL")
+    cfg = fb.GPTConfig(**kw)
+    lay = fb.parameter_layout(cfg)
+    params = fb.Params(gold["theta0"].clone().cuda())
+    st = fb.GradientState(cfg, max_batch=2)
+    st.refresh_weights(params.theta)
+    opt = fb.MuonAdamW(params, lay, st, weight_decay=0.1)
+    assert len(opt.adamw) == 10 and [len(g.specs) for g in opt.muon] == [4, 4, 2, 2, 1]
+    for i, d in enumerate(gold["deltas"]):
+        params.delta.copy_(d.cuda())
+        opt.step(eta=0.5 + 0.25 * i, mu=0.9, lam=0.05, Nt=64.0)
+        err = (params.theta.cpu() - gold["thetas"][i]).abs().max()
+        assert err <= 2e-4, (i, float(err))
+    assert opt.get_t() == [3] * 10
+    assert float(opt.adamw[0].m.abs().max()) > 0 and float(opt.muon[0].m.abs().max()) > 0
