@@ -4,7 +4,7 @@
 // atomics (ext/FemtoChatCUDAExt.jl:2002-2004); here two kernels each own their outputs, so every
 // gradient is summed in a fixed order:
 //   * dQ kernel: one CTA per 128 queries of a head; S = Q K^T and dP = dO V^T go to TMEM, the
-//     row-owning threads turn them into dS (bf16, written over S in TMEM), dQ += dS K stays in TMEM.
+//     row-owning threads (two per row, each half of the keys) turn them into dS (bf16, written over S in TMEM), dQ += dS K stays in TMEM.
 //   * dK/dV kernel: one CTA per 128 keys of a kv head; loops over the heads of the GQA group and
 //     the query tiles that see these keys; S^T = K Q^T and dP^T = V dO^T go to TMEM, threads own
 //     key rows and write P^T and dS^T back to TMEM, dV += P^T dO and dK += dS^T Q stay in TMEM.
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D
 // ------------------------------------------------------------------------------------------------
 // dQ kernel
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const BwdParams p) {
@@ -93,7 +93,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(qdo_full, 1);
     for (int i = 0; i < 2; i++) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&ds_ready[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&ds_ready[i], 8);
     }
     mbar_init(dp_full, 1);
     mbar_init(dq_done, 1);
@@ -179,6 +179,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp >= 4) {
     const int quad = warp & 3;
+    const int halfsel = (warp - 4) >> 2;  // warps 4-7 take key chunks 0,1 of each tile, warps 8-11 chunks 2,3
     const int r = quad * 32 + lane;
     const int q = q0 + r;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -193,13 +194,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < ntile; i++) {
       const int st = i & 1;
       const int k0 = (jlo + i) * BT;
-      if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
-      if (!mbar_wait(dp_full, i & 1, abort_flag, a.status)) { ok = false; break; }
+      // After a timed-out wait the warp keeps walking the loop (skipping the work) so that it still
+      // meets its partner warp at every pair barrier.
+      if (ok && !mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, a.status)) ok = false;
+      if (ok && !mbar_wait(dp_full, i & 1, abort_flag, a.status)) ok = false;
+      if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
       const bool need_mask = (k0 + BT - 1 > q) || (k0 < lo);
+      // The two threads of a row each take two 32-key chunks.  dS (bf16) is written over the first 64
+      // columns of S, which the partner thread may still be reading: results are kept in registers
+      // until both have read all of S and dP (pair barrier), then stored.
+      uint32_t pk[2][16];
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
-        uint32_t sr[32], dr[32], pk[16];
+      for (int u = 0; u < 2; u++) {
+        const int cc = 2 * halfsel + u;
+        uint32_t sr[32], dr[32];
         tmem_ld32(tS[st] + lane_off + cc * 32, sr);
         tmem_ld32(tdP + lane_off + cc * 32, dr);
         tmem_ld_wait();
@@ -213,10 +222,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (need_mask && !(k <= q && k >= lo)) pv = 0.f;
             d2[e] = pv * (__uint_as_float(dr[j + e]) - Dq);
           }
-          pk[j >> 1] = pack2(d2[0], d2[1]);
+          pk[u][j >> 1] = pack2(d2[0], d2[1]);
         }
-        tmem_st16(tS[st] + lane_off + cc * 16, pk);
       }
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+#pragma unroll
+      for (int u = 0; u < 2; u++) tmem_st16(tS[st] + lane_off + (2 * halfsel + u) * 16, pk[u]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -226,7 +237,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       bf16* dq = reinterpret_cast<bf16*>(a.dQ) + (row0 + q) * a.dq_stride + (long long)h * HD;
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+      for (int cc = 2 * halfsel; cc < 2 * halfsel + 2; cc++) {
         uint32_t rr[32];
         tmem_ld32(tdQ + lane_off + cc * 32, rr);
         tmem_ld_wait();
@@ -250,7 +261,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // ------------------------------------------------------------------------------------------------
 // dK / dV kernel
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const BwdParams p) {
@@ -286,7 +297,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     mbar_init(st_full, 1);
-    mbar_init(pds_ready, 4);
+    mbar_init(pds_ready, 8);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -360,6 +371,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp >= 4) {
     const int quad = warp & 3;
+    const int halfsel = (warp - 4) >> 2;  // which two of the four 32-query chunks of a tile this thread handles
     const int r = quad * 32 + lane;
     const int key = k0 + r;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -370,7 +382,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int h = kvh * g + it / nq;
       const int qi0 = (ilo + it % nq) * BT;
       float* sl = stats + (it & 1) * 384;
-      {
+      if (halfsel == 0) {
         const int q = qi0 + r;
         const long long si = ((long long)b * a.H + h) * a.T + q;
         sl[r] = a.lse[si] * LOG2E;
@@ -379,34 +391,43 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
         sl[256 + r] = __int_as_float(lo);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(st_full, it & 1, abort_flag, a.status)) { ok = false; break; }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (ok && !mbar_wait(st_full, it & 1, abort_flag, a.status)) ok = false;
+      if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
-      // tile-level mask test: any (key, q) pair of this row outside key <= q, key >= lo[q]?
+      uint32_t pp[2][16], pd[2][16];   // kept in registers until the partner thread has read S^T / dP^T
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
-        uint32_t sr[32], dr[32], pp[16], pd[16];
+      for (int u = 0; u < 2; u++) {
+        const int cc = 2 * halfsel + u;
+        uint32_t sr[32], dr[32];
         tmem_ld32(tS + lane_off + cc * 32, sr);
         tmem_ld32(tdP + lane_off + cc * 32, dr);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p2[2], d2[2];
+        for (int j = 0; j < 32; j += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(sl + cc * 32 + j);
+          const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cc * 32 + j);
+          const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cc * 32 + j);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+          const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
+          float p4[4], s4[4];
 #pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const int qq = cc * 32 + j + e;
-            const int q = qi0 + qq;
-            const int lo = __float_as_int(sl[256 + qq]);
-            float pv = exp2f(__uint_as_float(sr[j + e]) * c - sl[qq]);
-            if (!(key <= q && key >= lo)) pv = 0.f;
-            p2[e] = pv;
-            d2[e] = pv * (__uint_as_float(dr[j + e]) - sl[128 + qq]);
+          for (int e = 0; e < 4; e++) {
+            const int q = qi0 + cc * 32 + j + e;
+            float pv = exp2f(__uint_as_float(sr[j + e]) * c - ls[e]);
+            if (!(key <= q && key >= los[e])) pv = 0.f;
+            p4[e] = pv;
+            s4[e] = pv * (__uint_as_float(dr[j + e]) - dd[e]);
           }
-          pp[j >> 1] = pack2(p2[0], p2[1]);
-          pd[j >> 1] = pack2(d2[0], d2[1]);
+          pp[u][j >> 1] = pack2(p4[0], p4[1]); pp[u][(j >> 1) + 1] = pack2(p4[2], p4[3]);
+          pd[u][j >> 1] = pack2(s4[0], s4[1]); pd[u][(j >> 1) + 1] = pack2(s4[2], s4[3]);
         }
-        tmem_st16(tS + lane_off + cc * 16, pp);
-        tmem_st16(tdP + lane_off + cc * 16, pd);
+      }
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        tmem_st16(tS + lane_off + (2 * halfsel + u) * 16, pp[u]);
+        tmem_st16(tdP + lane_off + (2 * halfsel + u) * 16, pd[u]);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -418,7 +439,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bf16* dk = reinterpret_cast<bf16*>(a.dK) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
       bf16* dv = reinterpret_cast<bf16*>(a.dV) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+      for (int cc = 2 * halfsel; cc < 2 * halfsel + 2; cc++) {
         uint32_t rk[32], rv[32];
         tmem_ld32(tdK + lane_off + cc * 32, rk);
         tmem_ld32(tdV + lane_off + cc * 32, rv);
@@ -473,10 +494,10 @@ int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
     attr_done = true;
   }
   dim3 gq(a.T / BT, a.H, a.B);
-  attn_bwd_dq_kernel<<<gq, 256, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  attn_bwd_dq_kernel<<<gq, 384, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
   KERNEL_CHECK();
   dim3 gk(a.T / BT, a.Hkv, a.B);
-  attn_bwd_dkv_kernel<<<gk, 256, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  attn_bwd_dkv_kernel<<<gk, 384, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
   KERNEL_CHECK();
   return 0;
 }

@@ -7,7 +7,7 @@
 // Forward: one CTA owns 128 queries of one (batch, head).  Warp 0 streams K/V tiles of 128 keys
 // with TMA (two stages each), warp 1 issues tcgen05.mma: S = Q K^T into one of two 128-column
 // TMEM buffers, then O += P V with P read back from TMEM (P overwrites S in place as bf16).
-// Warps 4-7 own one query row per thread: they read S with tcgen05.ld, keep the running
+// Warps 4-11 own the query rows, two threads per row (64 keys each): they read S with tcgen05.ld, keep the running
 // max / sum, rescale the TMEM-resident O only when the max grew by more than 2^8, and write P
 // with tcgen05.st.  S of tile j+1 is computed while the softmax of tile j runs.
 #include <algorithm>
@@ -20,7 +20,7 @@ namespace {
 
 constexpr int HD = 128, BQ = 128, BKV = 128;
 constexpr int TILE_BYTES = BQ * HD * 2;  // 32 KB: two [128][64] swizzled slabs
-constexpr int FWD_SMEM = TILE_BYTES * 5 + 1024 + 256;
+constexpr int FWD_SMEM = TILE_BYTES * 5 + 1024 + 256 + 3 * 1024;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct FwdParams {
@@ -33,7 +33,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -52,6 +52,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* pv_done = bars + 13;  // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xmax = reinterpret_cast<float*>(smem + 5 * TILE_BYTES + 256);  // [2 parities][2 halves][128 rows]
+  float* xl = xmax + 512;                                               // [2 halves][128 rows]
 
   const AttnArgs& a = p.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -68,7 +70,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; i++) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8);
     }
     mbar_init(pv_done, 1);
     *abort_flag = 0;
@@ -145,8 +147,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else if (warp >= 4) {
-    // ---------------- softmax, one query row per thread ----------------
+    // ---------------- softmax: two threads per query row, each owns 64 of the 128 keys of a tile ----------------
     const int quad = warp & 3;
+    const int hs = (warp - 4) >> 2;        // 0: keys 0..63 of each tile, 1: keys 64..127
     const int r = quad * 32 + lane;
     const int q = q0 + r;
     const bool row_ok = q < a.T;
@@ -154,36 +157,44 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float c = rsqrtf((float)HD) * LOG2E;
     int lo = max(0, q - a.window_left);
     if (a.doc_start && row_ok) lo = max(lo, a.doc_start[row0 + q]);
-    float m_used = -INFINITY, l = 0.f;
+    float m_used = -INFINITY, l = 0.f;   // l: this thread's share of the row sum (same m_used in both threads)
     bool ok = true;
     for (int i = 0; i < ntile; i++) {
       const int st = i & 1;
       const uint32_t ph = (i >> 1) & 1;
-      const int k0 = (jlo + i) * BKV;
-      if (!mbar_wait(&s_full[st], ph, abort_flag, a.status)) { ok = false; break; }
+      const int k0 = (jlo + i) * BKV + hs * 64;
+      // After a timed-out wait the warp keeps walking the loop (skipping the work) so that it still
+      // meets its partner warp at every pair barrier.
+      if (ok && !mbar_wait(&s_full[st], ph, abort_flag, a.status)) ok = false;
+      if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
-      float x[BKV];
+      float x[64];
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+      for (int u = 0; u < 2; u++) {
         uint32_t rr[32];
-        tmem_ld32(tS[st] + lane_off + cc * 32, rr);
+        tmem_ld32(tS[st] + lane_off + (2 * hs + u) * 32, rr);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; j++) x[cc * 32 + j] = __uint_as_float(rr[j]) * c;
+        for (int j = 0; j < 32; j++) x[u * 32 + j] = __uint_as_float(rr[j]) * c;
       }
-      const bool need_mask = (k0 + BKV - 1 > q) || (k0 < lo);
+      const bool need_mask = (k0 + 63 > q) || (k0 < lo);
       float mt = -INFINITY;
       if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < BKV; j++) {
+        for (int j = 0; j < 64; j++) {
           const int k = k0 + j;
           x[j] = (k <= q && k >= lo) ? x[j] : -INFINITY;
           mt = fmaxf(mt, x[j]);
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < BKV; j++) mt = fmaxf(mt, x[j]);
+        for (int j = 0; j < 64; j++) mt = fmaxf(mt, x[j]);
       }
+      // combine the two half-row maxima; after this barrier both threads hold all of S in registers,
+      // so P may overwrite S in TMEM
+      xmax[(i & 1) * 256 + hs * 128 + r] = mt;
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+      mt = fmaxf(mt, xmax[(i & 1) * 256 + (hs ^ 1) * 128 + r]);
       const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_used, mt);
@@ -192,16 +203,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         m_used = m_new;
         if (i > 0) {
           // O lives in TMEM and is being accumulated by the tensor core: wait for tile i-1's P V
-          if (!mbar_wait(pv_done, (i - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+          if (!mbar_wait(pv_done, (i - 1) & 1, abort_flag, a.status)) { ok = false; continue; }
           tc_fence_after();
 #pragma unroll
-          for (int cc = 0; cc < 4; cc++) {
+          for (int u = 0; u < 2; u++) {
             uint32_t rr[32];
-            tmem_ld32(tO + lane_off + cc * 32, rr);
+            tmem_ld32(tO + lane_off + (2 * hs + u) * 32, rr);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; j++) rr[j] = __float_as_uint(__uint_as_float(rr[j]) * alpha);
-            tmem_st32(tO + lane_off + cc * 32, rr);
+            tmem_st32(tO + lane_off + (2 * hs + u) * 32, rr);
           }
           tmem_st_wait();
         }
@@ -209,15 +220,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float mm = (m_used == -INFINITY) ? 0.f : m_used;
       float sum = 0.f;
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+      for (int u = 0; u < 2; u++) {
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-          const float p0 = exp2f(x[cc * 32 + 2 * j] - mm), p1 = exp2f(x[cc * 32 + 2 * j + 1] - mm);
+          const float p0 = exp2f(x[u * 32 + 2 * j] - mm), p1 = exp2f(x[u * 32 + 2 * j + 1] - mm);
           sum += p0 + p1;
           pk[j] = pack_bf16(p0, p1);
         }
-        tmem_st16(tS[st] + lane_off + cc * 16, pk);
+        tmem_st16(tS[st] + lane_off + (2 * hs + u) * 16, pk);
       }
       l += sum;
       tmem_st_wait();
@@ -225,12 +236,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[st]);
     }
+    xl[hs * 128 + r] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+    l += xl[(hs ^ 1) * 128 + r];
     if (ok && mbar_wait(pv_done, (ntile - 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
       const float inv = 1.f / l;
       bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+      for (int u = 0; u < 2; u++) {
+        const int cc = 2 * hs + u;
         uint32_t rr[32];
         tmem_ld32(tO + lane_off + cc * 32, rr);
         tmem_ld_wait();
@@ -246,7 +261,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-      if (row_ok) {
+      if (row_ok && hs == 0) {
         const long long si = ((long long)b * a.H + h) * a.T + q;
         const float ln2 = 0.6931471805599453f;
         if (a.lse) a.lse[si] = (m_used + log2f(l)) * ln2;
@@ -291,7 +306,7 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
     attr_done = true;
   }
   dim3 grid(a.T / BQ, a.H, a.B);
-  attn_fwd_tc_kernel<<<grid, 256, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
+  attn_fwd_tc_kernel<<<grid, 384, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
   KERNEL_CHECK();
   return 0;
 }
