@@ -244,7 +244,7 @@ def run_ours(args):
     barrier()
     ms = e0.elapsed_time(e1)
     launches = st.launch_count() - l0
-    final_loss = float(losses[-1].item()) / (B * T)
+    final_loss = float(losses[-1].item()) / (B * T * world)   # the loss sum is all-reduced by femto_grad_sync
     clk = clocks.stop() if rank == 0 else None
 
     # ---- end to end: host buffers through the public call, H2D and D2H inside the timed region ----
@@ -296,7 +296,7 @@ def run_ours(args):
         )
         if args.cpu_baseline:
             try:
-                c = cpu_step_sample(args.config, 256)
+                c = cpu_step_sample(args.config, 1024)
                 line["cpu_baseline"] = dict(value=c["tokens_per_s"], unit="tokens/s", cores=c["cores"], kind="port",
                                             sample=c["sample"])
             except Exception as e:  # the GPU number stands even if the host baseline cannot run
