@@ -218,7 +218,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 2; e++) {
             const int k = k0 + cc * 32 + j + e;
-            float pv = exp2f(__uint_as_float(sr[j + e]) * c - lse2);
+            float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - lse2);
             if (need_mask && !(k <= q && k >= lo)) pv = 0.f;
             d2[e] = pv * (__uint_as_float(dr[j + e]) - Dq);
           }
@@ -259,7 +259,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
-// dK / dV kernel
+// dK / dV kernel.  The query tile of an iteration is processed as two halves of 64 queries, so the
+// S^T / dP^T buffers in TMEM (64 columns each) can be double-buffered: the tensor core computes
+// the inputs of half h+1 while the threads turn half h into P^T and dS^T.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(384, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -275,10 +277,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;   // [2]
   uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* st_full = bars + 5;    // S^T and dP^T of the current tile are in TMEM
-  uint64_t* pds_ready = bars + 6;  // P^T and dS^T written
-  uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* st_full = bars + 5;    // [2] S^T and dP^T of a half are in TMEM
+  uint64_t* pds_ready = bars + 7;  // [2] P^T and dS^T of a half are written
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2][3][128]: lse2, D, lo
 
@@ -290,14 +292,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int ilo = kt;
   const int ihi = (int)min((long long)a.T / BT - 1, ((long long)k0 + BT - 1 + a.window_left) / BT);
   const int nq = ihi - ilo + 1;
-  const int nit = nq * g;
+  const int nit = nq * g;      // (head, query tile) pairs
+  const int n2 = nit * 2;      // halves
   const long long row0 = (long long)b * a.T;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
-    mbar_init(st_full, 1);
-    mbar_init(pds_ready, 8);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
+      mbar_init(&st_full[i], 1); mbar_init(&pds_ready[i], 8);
+    }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -307,7 +311,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdK = tmem_base + 256, tdV = tmem_base + 384;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 64};
+  const uint32_t tdP[2] = {tmem_base + 128, tmem_base + 192};
+  const uint32_t tdK = tmem_base + 256, tdV = tmem_base + 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -330,109 +336,115 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_kk = idesc_bf16(BT, BT, false, false);
-      constexpr uint32_t idesc_mn = idesc_bf16(BT, HD, false, true);
+      constexpr uint32_t idesc_in = idesc_bf16(BT, 64, false, false);   // [128 keys] x [64 queries], K = head_dim
+      constexpr uint32_t idesc_out = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous, K = 64 queries
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      auto issue_in = [&](int it) -> bool {  // S^T = K Q^T, dP^T = V dO^T
-        const int st = it & 1;
-        if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) return false;
+      auto issue_in = [&](int h2) -> bool {  // S^T = K Q^T, dP^T = V dO^T for 64 queries
+        const int it = h2 >> 1, hf = h2 & 1, st = it & 1, bf = h2 & 1;
+        if (hf == 0 && !mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES), do_addr = smem_u32(sdO + st * TILE_BYTES);
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES) + hf * 8192, do_addr = smem_u32(sdO + st * TILE_BYTES) + hf * 8192;
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
           const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tS, smem_desc_sw128(k_addr + off, 16, 1024), smem_desc_sw128(q_addr + off, 16, 1024), idesc_kk, k > 0);
+          mma_ss(tS[bf], smem_desc_sw128(k_addr + off, 16, 1024), smem_desc_sw128(q_addr + off, 16, 1024), idesc_in, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
           const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tdP, smem_desc_sw128(v_addr + off, 16, 1024), smem_desc_sw128(do_addr + off, 16, 1024), idesc_kk, k > 0);
+          mma_ss(tdP[bf], smem_desc_sw128(v_addr + off, 16, 1024), smem_desc_sw128(do_addr + off, 16, 1024), idesc_in, k > 0);
         }
-        tc_commit(st_full);
+        tc_commit(&st_full[bf]);
         return true;
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, a.status);
       if (ok) { tc_fence_after(); ok = issue_in(0); }
-      for (int it = 0; it < nit && ok; it++) {
-        const int st = it & 1;
-        if (!mbar_wait(pds_ready, it & 1, abort_flag, a.status)) { ok = false; break; }
+      for (int h2 = 0; h2 < n2 && ok; h2++) {
+        const int it = h2 >> 1, hf = h2 & 1, st = it & 1, bf = h2 & 1;
+        if (h2 + 1 < n2 && !issue_in(h2 + 1)) { ok = false; break; }
+        if (!mbar_wait(&pds_ready[bf], (h2 >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES), do_addr = smem_u32(sdO + st * TILE_BYTES);
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES) + hf * 8192, do_addr = smem_u32(sdO + st * TILE_BYTES) + hf * 8192;
 #pragma unroll
-        for (int k = 0; k < BT / 16; k++)  // dV += P^T dO
-          mma_ts(tdV, tS + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (it > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; k++)  // dV += P^T dO over 64 queries
+          mma_ts(tdV, tS[bf] + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q
-          mma_ts(tdK, tdP + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (it > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&qdo_empty[st]);
-        if (it + 1 < nit && !issue_in(it + 1)) { ok = false; break; }
+        for (int k = 0; k < 4; k++)  // dK += dS^T Q
+          mma_ts(tdK, tdP[bf] + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
+        if (hf == 1) tc_commit(&qdo_empty[st]);
       }
       if (ok) tc_commit(acc_done);
     }
   } else if (warp >= 4) {
     const int quad = warp & 3;
-    const int halfsel = (warp - 4) >> 2;  // which two of the four 32-query chunks of a tile this thread handles
+    const int halfsel = (warp - 4) >> 2;  // which 32 of the 64 queries of a half this thread handles
     const int r = quad * 32 + lane;
     const int key = k0 + r;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float scale = rsqrtf((float)HD);
     const float c = scale * LOG2E;
     bool ok = true;
-    for (int it = 0; it < nit; it++) {
+    // statistics of the queries of a tile (one per thread of warps 4-7), fetched one tile ahead
+    float n_lse = 0.f, n_D = 0.f;
+    int n_lo = 0;
+    auto fetch_stats = [&](int it) {
       const int h = kvh * g + it / nq;
-      const int qi0 = (ilo + it % nq) * BT;
+      const int q = (ilo + it % nq) * BT + r;
+      const long long si = ((long long)b * a.H + h) * a.T + q;
+      n_lse = a.lse[si] * LOG2E;
+      n_D = p.D[si];
+      n_lo = max(0, q - a.window_left);
+      if (a.doc_start) n_lo = max(n_lo, a.doc_start[row0 + q]);
+    };
+    if (halfsel == 0) fetch_stats(0);
+    for (int h2 = 0; h2 < n2; h2++) {
+      const int it = h2 >> 1, hf = h2 & 1, bf = h2 & 1;
+      const int qi0 = (ilo + it % nq) * BT + hf * 64;
       float* sl = stats + (it & 1) * 384;
-      if (halfsel == 0) {
-        const int q = qi0 + r;
-        const long long si = ((long long)b * a.H + h) * a.T + q;
-        sl[r] = a.lse[si] * LOG2E;
-        sl[128 + r] = p.D[si];
-        int lo = max(0, q - a.window_left);
-        if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
-        sl[256 + r] = __int_as_float(lo);
+      if (hf == 0) {
+        if (halfsel == 0) {
+          sl[r] = n_lse; sl[128 + r] = n_D; sl[256 + r] = __int_as_float(n_lo);
+          if (it + 1 < nit) fetch_stats(it + 1);
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (ok && !mbar_wait(st_full, it & 1, abort_flag, a.status)) ok = false;
+      if (ok && !mbar_wait(&st_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
-      uint32_t pp[2][16], pd[2][16];   // kept in registers until the partner thread has read S^T / dP^T
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int cc = 2 * halfsel + u;
+      uint32_t pp[16], pd[16];   // kept in registers until the partner thread has read S^T / dP^T
+      {
+        const int cq = hf * 64 + halfsel * 32;   // first query (within the tile) of this thread's chunk
         uint32_t sr[32], dr[32];
-        tmem_ld32(tS + lane_off + cc * 32, sr);
-        tmem_ld32(tdP + lane_off + cc * 32, dr);
+        tmem_ld32(tS[bf] + lane_off + halfsel * 32, sr);
+        tmem_ld32(tdP[bf] + lane_off + halfsel * 32, dr);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(sl + cc * 32 + j);
-          const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cc * 32 + j);
-          const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cc * 32 + j);
+          const float4 l4 = *reinterpret_cast<const float4*>(sl + cq + j);
+          const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cq + j);
+          const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cq + j);
           const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
           const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
           float p4[4], s4[4];
 #pragma unroll
           for (int e = 0; e < 4; e++) {
-            const int q = qi0 + cc * 32 + j + e;
-            float pv = exp2f(__uint_as_float(sr[j + e]) * c - ls[e]);
+            const int q = qi0 + halfsel * 32 + j + e;
+            float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - ls[e]);
             if (!(key <= q && key >= los[e])) pv = 0.f;
             p4[e] = pv;
             s4[e] = pv * (__uint_as_float(dr[j + e]) - dd[e]);
           }
-          pp[u][j >> 1] = pack2(p4[0], p4[1]); pp[u][(j >> 1) + 1] = pack2(p4[2], p4[3]);
-          pd[u][j >> 1] = pack2(s4[0], s4[1]); pd[u][(j >> 1) + 1] = pack2(s4[2], s4[3]);
+          pp[j >> 1] = pack2(p4[0], p4[1]); pp[(j >> 1) + 1] = pack2(p4[2], p4[3]);
+          pd[j >> 1] = pack2(s4[0], s4[1]); pd[(j >> 1) + 1] = pack2(s4[2], s4[3]);
         }
       }
       asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        tmem_st16(tS + lane_off + (2 * halfsel + u) * 16, pp[u]);
-        tmem_st16(tdP + lane_off + (2 * halfsel + u) * 16, pd[u]);
-      }
+      tmem_st16(tS[bf] + lane_off + halfsel * 16, pp);
+      tmem_st16(tdP[bf] + lane_off + halfsel * 16, pd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_ready);
+      if (lane == 0) mbar_arrive(&pds_ready[bf]);
     }
     if (ok && mbar_wait(acc_done, 0, abort_flag, a.status)) {
       tc_fence_after();

@@ -198,7 +198,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_used, mt);
-        const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
         l *= alpha;
         m_used = m_new;
         if (i > 0) {
@@ -224,7 +224,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-          const float p0 = exp2f(x[u * 32 + 2 * j] - mm), p1 = exp2f(x[u * 32 + 2 * j + 1] - mm);
+          const float p0 = fast_exp2(x[u * 32 + 2 * j] - mm), p1 = fast_exp2(x[u * 32 + 2 * j + 1] - mm);
           sum += p0 + p1;
           pk[j] = pack_bf16(p0, p1);
         }

@@ -32,6 +32,20 @@ struct TcParams {
   float* partial;  // [unit][8 chunks][128 rows][32 cols] when splits > 1
 };
 
+// Tile rasterisation: groups of GROUP_M row-tiles are walked column by column, so one wave of CTAs
+// covers a roughly square patch of the output (16 x 9 tiles) and re-reads neither operand from HBM.
+constexpr int GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(const TcParams& p, int t, int& bz, int& mt, int& nt) {
+  const int per = p.tiles_m * p.tiles_n;
+  bz = t / per;
+  const int pid = t % per;
+  const int width = GROUP_M * p.tiles_n;
+  const int first_m = (pid / width) * GROUP_M;
+  const int gsz = min(p.tiles_m - first_m, GROUP_M);
+  mt = first_m + (pid % width) % gsz;
+  nt = (pid % width) / gsz;
+}
+
 __device__ __forceinline__ float sqrt_approx(float x) {
   float y;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -144,10 +158,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   auto unit_coords = [&](int u, int& bz, int& mt, int& nt, int& kb0, int& kb1) {
-    const int s = u % p.splits;
-    int tile = u / p.splits;
-    nt = tile % p.tiles_n; tile /= p.tiles_n;
-    mt = tile % p.tiles_m; bz = tile / p.tiles_m;
+    // split-major: all tiles of one k-range run together, so the 148 CTAs stream the same rows of
+    // both operands through L2 at the same time
+    const int ntile = p.tiles_m * p.tiles_n * p.g.batch;
+    const int s = u / ntile;
+    tile_coords(p, u % ntile, bz, mt, nt);
     kb0 = s * p.kb_per_split;
     kb1 = min(p.kblocks, kb0 + p.kb_per_split);
   };
@@ -272,8 +287,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         switch (g.epi) {
           case EPI_F32: {
-            if (g.nseg == 0 && full_chunk && (g.ldc & 3) == 0) {
-              float* dst = reinterpret_cast<float*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
+            float* dst = reinterpret_cast<float*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
+            if (g.nseg == 0 && full_chunk && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 float4 o = make_float4(g.alpha * v[j], g.alpha * v[j + 1], g.alpha * v[j + 2], g.alpha * v[j + 3]);
@@ -337,29 +352,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
-// Sum the split-K partials of every tile in split order and apply the fp32 epilogue.
+// Sum the split-K partials in split order and apply the fp32 epilogue.  One block per
+// (tile, 32-column chunk): 128 rows x 32 columns, one float4 column group per thread and row slice.
 __global__ void __launch_bounds__(256) gemm_tc_reduce_kernel(const TcParams p) {
   const GemmArgs& g = p.g;
-  const int tile = blockIdx.x;
-  int t = tile;
-  const int nt = t % p.tiles_n; t /= p.tiles_n;
-  const int mt = t % p.tiles_m;
-  const int bz = t / p.tiles_m;
-  for (int e = threadIdx.x; e < 128 * 256 / 4; e += 256) {
-    const int c = e / (128 * 8);          // 32-column chunk
-    const int rem = e % (128 * 8);
-    const int row = rem / 8, j4 = (rem % 8) * 4;
+  const int tile = blockIdx.x >> 3, c = blockIdx.x & 7;
+  const int ntile = p.tiles_m * p.tiles_n * g.batch;
+  int bz, mt, nt;
+  tile_coords(p, tile, bz, mt, nt);
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    const int e = it * 256 + threadIdx.x;     // 0..1023 float4 groups of this chunk
+    const int row = e >> 3, j4 = (e & 7) * 4;
     const int m = mt * BM + row, n = nt * BN + c * 32 + j4;
     if (m >= g.M || n >= g.N) continue;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* src = p.partial + ((long long)tile * 8 + c) * (128 * 32) + row * 32 + j4;
+    const long long sstride = (long long)ntile * 8 * (128 * 32);
     for (int s = 0; s < p.splits; s++) {
-      const float4 q = *reinterpret_cast<const float4*>(p.partial + (((long long)tile * p.splits + s) * 8 + c) * (128 * 32) + row * 32 + j4);
+      const float4 q = *reinterpret_cast<const float4*>(src + s * sstride);
       acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
     }
-    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-    for (int j = 0; j < 4 && n + j < g.N; j++) {
-      float* dst = f32_dst(g, bz, m, n + j);
-      if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * vals[j];
+    float* dst4 = reinterpret_cast<float*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + n;
+    // delta ranges start at arbitrary element offsets: vector access only when the address is 16-byte aligned
+    if (g.nseg == 0 && n + 3 < g.N && (reinterpret_cast<uintptr_t>(dst4) & 15) == 0) {
+      float* dst = dst4;
+      float4 o = make_float4(g.alpha * acc.x, g.alpha * acc.y, g.alpha * acc.z, g.alpha * acc.w);
+      if (g.beta != 0.f) {
+        const float4 q = *reinterpret_cast<const float4*>(dst);
+        o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w;
+      }
+      *reinterpret_cast<float4*>(dst) = o;
+    } else {
+      const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        if (n + j < g.N) {
+          float* dst = f32_dst(g, bz, m, n + j);
+          if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * vals[j];
+        }
+      }
     }
   }
 }
@@ -536,7 +568,7 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   }
   KERNEL_CHECK();
   if (splits > 1) {
-    gemm_tc_reduce_kernel<<<tiles, 256, 0, s>>>(p);
+    gemm_tc_reduce_kernel<<<tiles * 8, 256, 0, s>>>(p);
     KERNEL_CHECK();
   }
   return 0;
