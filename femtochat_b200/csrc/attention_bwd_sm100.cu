@@ -85,9 +85,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int kvh = h / (a.H / a.Hkv);
   const int q0 = qt * BT;
   const int jhi = min(q0 + BT - 1, a.T - 1) / BT;
-  const int jlo = max(0, q0 - a.window_left) / BT;
-  const int ntile = jhi - jlo + 1;
+  int jlo = max(0, q0 - a.window_left) / BT;
   const long long row0 = (long long)b * a.T;
+  if (a.doc_start) {
+    // key tiles that lie before the earliest document start of these 128 queries are fully masked
+    __shared__ int s_ds_min[4];
+    if (threadIdx.x < 128) {
+      const int v = __reduce_min_sync(0xffffffffu, a.doc_start[row0 + q0 + threadIdx.x]);
+      if ((threadIdx.x & 31) == 0) s_ds_min[threadIdx.x >> 5] = v;
+    }
+    __syncthreads();
+    jlo = max(jlo, min(min(s_ds_min[0], s_ds_min[1]), min(s_ds_min[2], s_ds_min[3])) / BT);
+  }
+  const int ntile = jhi - jlo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -291,10 +301,34 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int k0 = kt * BT;
   const int ilo = kt;
   const int ihi = (int)min((long long)a.T / BT - 1, ((long long)k0 + BT - 1 + a.window_left) / BT);
-  const int nq = ihi - ilo + 1;
+  const long long row0 = (long long)b * a.T;
+  // query tiles whose earliest document start lies after this key tile are fully masked: keep a
+  // compact list of the visible ones (document starts need not be monotone for arbitrary positions)
+  __shared__ int s_qlist[64];
+  __shared__ int s_tmin[64];
+  __shared__ int s_nq;
+  {
+    const int cand = ihi - ilo + 1;
+    if (a.doc_start) {
+      for (int c = threadIdx.x >> 5; c < cand; c += 12) {
+        const int base = (ilo + c) * BT + (threadIdx.x & 31) * 4;
+        const int4 v = *reinterpret_cast<const int4*>(a.doc_start + row0 + base);
+        const int m = __reduce_min_sync(0xffffffffu, min(min(v.x, v.y), min(v.z, v.w)));
+        if ((threadIdx.x & 31) == 0) s_tmin[c] = m;
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      int n = 0;
+      for (int c = 0; c < cand; c++)
+        if (!a.doc_start || s_tmin[c] <= k0 + BT - 1) s_qlist[n++] = ilo + c;
+      s_nq = n;
+    }
+    __syncthreads();
+  }
+  const int nq = s_nq;         // >= 1: the diagonal tile always sees its own keys
   const int nit = nq * g;      // (head, query tile) pairs
   const int n2 = nit * 2;      // halves
-  const long long row0 = (long long)b * a.T;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -325,7 +359,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int it = 0; it < nit; it++) {
         const int st = it & 1;
         const int h = kvh * g + it / nq;
-        const int qrow = (int)(row0 + (ilo + it % nq) * BT);
+        const int qrow = (int)(row0 + s_qlist[it % nq] * BT);
         if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, a.status)) break;
         mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES);
         tma_load_2d(sQ + st * TILE_BYTES, &tmQ, &qdo_full[st], h * HD, qrow);
@@ -389,7 +423,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     int n_lo = 0;
     auto fetch_stats = [&](int it) {
       const int h = kvh * g + it / nq;
-      const int q = (ilo + it % nq) * BT + r;
+      const int q = s_qlist[it % nq] * BT + r;
       const long long si = ((long long)b * a.H + h) * a.T + q;
       n_lse = a.lse[si] * LOG2E;
       n_D = p.D[si];
@@ -399,7 +433,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (halfsel == 0) fetch_stats(0);
     for (int h2 = 0; h2 < n2; h2++) {
       const int it = h2 >> 1, hf = h2 & 1, bf = h2 & 1;
-      const int qi0 = (ilo + it % nq) * BT + hf * 64;
+      const int qi0 = s_qlist[it % nq] * BT + hf * 64;
       float* sl = stats + (it & 1) * 384;
       if (hf == 0) {
         if (halfsel == 0) {

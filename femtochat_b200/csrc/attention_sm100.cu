@@ -63,8 +63,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int q0 = qt * BQ;
   const int jhi = min(q0 + BQ - 1, a.T - 1) / BKV;
   int jlo = max(0, q0 - a.window_left) / BKV;
-  const int ntile = jhi - jlo + 1;
   const long long row0 = (long long)b * a.T;
+  if (a.doc_start) {
+    // key tiles that lie before the earliest document start of these 128 queries are fully masked
+    __shared__ int s_ds_min[4];
+    if (threadIdx.x < 128) {
+      const int qq = min(q0 + (int)threadIdx.x, a.T - 1);
+      const int v = __reduce_min_sync(0xffffffffu, a.doc_start[row0 + qq]);
+      if ((threadIdx.x & 31) == 0) s_ds_min[threadIdx.x >> 5] = v;
+    }
+    __syncthreads();
+    jlo = max(jlo, min(min(s_ds_min[0], s_ds_min[1]), min(s_ds_min[2], s_ds_min[3])) / BKV);
+  }
+  const int ntile = jhi - jlo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -283,10 +294,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 bool attention_tc_supported(const AttnArgs& a) {
   if (a.hd != HD) return false;
-  if (a.T % BQ != 0) return false;
+  if (a.T % BQ != 0 || a.T > 8192) return false;  // the dK/dV kernel lists at most 64 query tiles
   if ((a.q_stride & 7) || (a.kv_stride & 7) || (a.o_stride & 7)) return false;
   if (!aligned16(a.Q) || !aligned16(a.K) || !aligned16(a.V) || !aligned16(a.O)) return false;
   if (a.H % a.Hkv != 0) return false;
+  if (a.doc_start && !aligned16(a.doc_start)) return false;
   return true;
 }
 
