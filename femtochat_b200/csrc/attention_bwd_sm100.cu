@@ -31,25 +31,26 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// D[b][h][t] = sum_d dO*O, one warp per (token, head) slice of 128 channels.
+// D[b][h][t] = sum_d dO*O: 16 lanes per (token, head) slice of 128 channels, 16-byte loads.
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D) {
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
   const long long total = (long long)a.B * a.T * a.H;
-  if (w >= total) return;
+  const long long w0 = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const long long w = w0 < total ? w0 : total - 1;   // surplus half-warps recompute the last slice
+  const int sub = threadIdx.x & 15;
   const int h = (int)(w % a.H);
   const long long row = w / a.H;
-  const bf16* o = reinterpret_cast<const bf16*>(a.O) + row * a.o_stride + (long long)h * HD + lane * 4;
-  const bf16* g = reinterpret_cast<const bf16*>(a.dO) + row * a.do_stride + (long long)h * HD + lane * 4;
-  uint2 ov = *reinterpret_cast<const uint2*>(o), gv = *reinterpret_cast<const uint2*>(g);
+  const bf16* o = reinterpret_cast<const bf16*>(a.O) + row * a.o_stride + (long long)h * HD + sub * 8;
+  const bf16* g = reinterpret_cast<const bf16*>(a.dO) + row * a.do_stride + (long long)h * HD + sub * 8;
+  const uint4 ov = *reinterpret_cast<const uint4*>(o), gv = *reinterpret_cast<const uint4*>(g);
   const bf16* oh = reinterpret_cast<const bf16*>(&ov);
   const bf16* gh = reinterpret_cast<const bf16*>(&gv);
   float acc = 0.f;
 #pragma unroll
-  for (int i = 0; i < 4; i++) acc += __bfloat162float(oh[i]) * __bfloat162float(gh[i]);
-  acc = warp_sum(acc);
+  for (int i = 0; i < 8; i++) acc += __bfloat162float(oh[i]) * __bfloat162float(gh[i]);
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   const int b = (int)(row / a.T), t = (int)(row % a.T);
-  if (lane == 0) D[((long long)b * a.H + h) * a.T + t] = acc;
+  if (sub == 0 && w0 < total) D[((long long)b * a.H + h) * a.T + t] = acc;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -526,7 +527,7 @@ int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
   BwdParams p;
   p.a = a;
   p.D = reinterpret_cast<const float*>(a.ws);
-  attn_bwd_prep_kernel<<<cdiv(N * a.H, 8), 256, 0, s>>>(a, reinterpret_cast<float*>(a.ws));
+  attn_bwd_prep_kernel<<<cdiv(N * a.H, 16), 256, 0, s>>>(a, reinterpret_cast<float*>(a.ws));
   KERNEL_CHECK();
   CUtensorMap tmQ, tmK, tmV, tmdO;
   FEMTO_TRY(make_tmap_2d_bf16(&tmQ, a.Q, (uint64_t)a.H * HD, N, a.q_stride, 64, BT));

@@ -52,9 +52,11 @@ __device__ __forceinline__ float sqrt_approx(float x) {
   return y;
 }
 __device__ __forceinline__ float softcap15(float x) {
-  // 15 * tanh(x/15) with tanh(y) = 1 - 2/(exp(2y)+1)
-  float e = __expf(x * (2.f / 15.f));
-  return 15.f * (1.f - __fdividef(2.f, e + 1.f));
+  // 15 * tanh(x/15) on the special-function unit (tanh.approx: relative error about 2^-11, below the
+  // bf16 rounding of the logits that feed it)
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x * (1.f / 15.f)));
+  return 15.f * t;
 }
 
 __device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m, int n) {
@@ -68,7 +70,7 @@ __device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m
 // One 32-column chunk of one output row with a bf16 result: C = f(acc, aux).
 template <int EPI>
 __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], int bz, int m, int nc, bool full_chunk,
-                                           int tgt, float lse, float xw) {
+                                           int tgt, float lse, float xw, const uint4 (&pre)[4], bool use_pre) {
   bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
   constexpr bool need_aux = EPI == EPI_RESID || EPI == EPI_DRELU2 || EPI == EPI_AXPBY;
   const bool vec = full_chunk && (g.ldc & 7) == 0 && (!need_aux || (g.ldaux & 7) == 0);
@@ -78,7 +80,8 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
     if (vec) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
-        uint4 q = *reinterpret_cast<const uint4*>(aux + j);
+        // `pre` was loaded one chunk ahead (while the previous chunk was being processed)
+        uint4 q = use_pre ? pre[j >> 3] : *reinterpret_cast<const uint4*>(aux + j);
         const bf16* hq = reinterpret_cast<const bf16*>(&q);
 #pragma unroll
         for (int e = 0; e < 8; e++) a[j + e] = __bfloat162float(hq[e]);
@@ -265,12 +268,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           xw = tgt >= 0 ? g.xscale * (g.xscale_dev ? g.xscale_dev[0] : 1.f) : 0.f;
         }
       }
+      // operands of the residual / relu^2-reverse / axpby epilogues are fetched one chunk ahead
+      const bool aux_epi = p.splits == 1 && (g.epi == EPI_RESID || g.epi == EPI_DRELU2 || g.epi == EPI_AXPBY) &&
+                           (g.ldaux & 7) == 0 && (g.ldc & 7) == 0 && row_ok;
+      const bf16* aux_row = aux_epi ? reinterpret_cast<const bf16*>(g.aux) + (long long)bz * g.strideAux + (long long)m * g.ldaux : nullptr;
+      uint4 auxq[4], auxn[4];
+      bool pre_ok = false, next_ok = aux_epi && n0 + half * 32 + 32 <= g.N;
+      if (next_ok) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) auxn[j] = *reinterpret_cast<const uint4*>(aux_row + n0 + half * 32 + j * 8);
+      }
 #pragma unroll 1
       for (int c = half; c < BN / 32; c += 2) {
         uint32_t r[32];
         __syncwarp();
         if (g.dbg == 2) continue;
         tmem_ld32(taddr + c * 32, r);
+        pre_ok = next_ok;
+#pragma unroll
+        for (int j = 0; j < 4; j++) auxq[j] = auxn[j];
+        next_ok = aux_epi && c + 2 < BN / 32 && n0 + (c + 2) * 32 + 32 <= g.N;
+        if (next_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) auxn[j] = *reinterpret_cast<const uint4*>(aux_row + n0 + (c + 2) * 32 + j * 8);
+        }
         tmem_ld_wait();
         const int nc = n0 + c * 32;
         if (g.dbg == 3) { if (r[0] == 0x12345678u && r[31] == 0x1u) reinterpret_cast<bf16*>(g.C)[0] = __float2bfloat16_rn(1.f); continue; }
@@ -326,12 +347,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             rsum = rsum * __expf(rmax - nm) + cs;
             rmax = nm;
           } break;
-          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
-          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
-          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
-          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
-          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
-          case EPI_XENT_DLOGIT: bf16_chunk<EPI_XENT_DLOGIT>(g, v, bz, m, nc, full_chunk, tgt, lse, xw); break;
+          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
+          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
+          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
+          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
+          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
+          case EPI_XENT_DLOGIT: bf16_chunk<EPI_XENT_DLOGIT>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
           default: break;
         }
       }
