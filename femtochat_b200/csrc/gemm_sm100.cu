@@ -22,7 +22,8 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int STORE_STAGE_BYTES = 8 * 2 * 2048;  // 8 epilogue warps x 2 buffers x [32 rows][32 bf16]
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int TMEM_COLS = 512;
 
@@ -30,6 +31,7 @@ struct TcParams {
   GemmArgs g;
   int tiles_m, tiles_n, kblocks, splits, kb_per_split, total_units;
   float* partial;  // [unit][8 chunks][128 rows][32 cols] when splits > 1
+  int tma_store;   // bf16 results leave through shared memory and TMA tiled stores
 };
 
 // Tile rasterisation: groups of GROUP_M row-tiles are walked column by column, so one wave of CTAs
@@ -70,14 +72,18 @@ __device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m
 // One 32-column chunk of one output row with a bf16 result: C = f(acc, aux).
 template <int EPI>
 __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], int bz, int m, int nc, bool full_chunk,
-                                           int tgt, float lse, float xw, const uint4 (&pre)[4], bool use_pre) {
+                                           int tgt, float lse, float xw, const uint4 (&pre)[4], bool use_pre, bool row_ok,
+                                           uint8_t* stage_buf, const CUtensorMap* tmC, int m_warp0, int lane) {
   bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
   constexpr bool need_aux = EPI == EPI_RESID || EPI == EPI_DRELU2 || EPI == EPI_AXPBY;
   const bool vec = full_chunk && (g.ldc & 7) == 0 && (!need_aux || (g.ldaux & 7) == 0);
   float a[32];
   if constexpr (need_aux) {
     const bf16* aux = reinterpret_cast<const bf16*>(g.aux) + (long long)bz * g.strideAux + (long long)m * g.ldaux + nc;
-    if (vec) {
+    if (!row_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) a[j] = 0.f;
+    } else if (vec) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
         // `pre` was loaded one chunk ahead (while the previous chunk was being processed)
@@ -112,6 +118,28 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
 #pragma unroll
     for (int j = 0; j < 32; j++) t += v[j];
     if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
+  } else if (stage_buf != nullptr) {
+    // Coalesced path: the warp's 32 x 32 block goes to shared memory (64-byte swizzle, so the
+    // 16-byte stores of a quarter warp hit distinct banks) and leaves as one TMA tiled store, which
+    // also clips rows >= M and columns >= N.
+    if (lane == 0) bulk_wait_read<1>();   // the store that last used this buffer has read it
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      uint4 q;
+      __nv_bfloat162* hq = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; e++) hq[e] = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+      *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = q;
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(tmC, stage_buf, nc, m_warp0, bz);
+      bulk_commit();
+    }
+  } else if (!row_ok) {
+    // nothing to store for rows past M
   } else if (vec) {
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
@@ -129,10 +157,12 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
 
 template <bool A_K, bool B_K>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* store_stage = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + STORE_STAGE_BYTES);
   uint64_t* full = bars;                 // [STAGES]
   uint64_t* empty = bars + STAGES;       // [STAGES]
   uint64_t* tfull = bars + 2 * STAGES;   // [2]
@@ -295,7 +325,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int nc = n0 + c * 32;
         if (g.dbg == 3) { if (r[0] == 0x12345678u && r[31] == 0x1u) reinterpret_cast<bf16*>(g.C)[0] = __float2bfloat16_rn(1.f); continue; }
-        if (!row_ok || nc >= g.N) continue;
+        const bool tma_out = p.tma_store != 0 && p.splits == 1 && g.epi != EPI_F32 && g.epi != EPI_XENT_STATS;
+        if (nc >= g.N || (!row_ok && !tma_out)) continue;   // on the TMA path the whole warp stays together
+        uint8_t* sbuf = tma_out ? store_stage + ((warp - 2) * 2 + ((c >> 1) & 1)) * 2048 : nullptr;
         const bool full_chunk = nc + 32 <= g.N;
         float v[32];
 #pragma unroll
@@ -347,12 +379,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             rsum = rsum * __expf(rmax - nm) + cs;
             rmax = nm;
           } break;
-          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
-          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
-          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
-          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
-          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
-          case EPI_XENT_DLOGIT: bf16_chunk<EPI_XENT_DLOGIT>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok); break;
+          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_XENT_DLOGIT: bf16_chunk<EPI_XENT_DLOGIT>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
           default: break;
         }
       }
@@ -365,6 +397,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
 
+  if (warp >= 2 && lane == 0) bulk_wait_all();   // every TMA store of this warp has landed
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -436,14 +469,21 @@ static PFN_encodeTiled get_encode() {
 
 int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
                       uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1) {
+  return make_tmap_3d_bf16_sw(out, base, dim0, dim1, dim2, stride1_elems, stride2_elems, box0, box1, 3);
+}
+
+int make_tmap_3d_bf16_sw(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                         uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1, int swizzle) {
   PFN_encodeTiled enc = get_encode();
   if (!enc) return femto_fail(FEMTO_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[3] = {dim0, dim1, dim2 ? dim2 : 1};
   cuuint64_t strides[2] = {stride1_elems * 2, (dim2 > 1 ? stride2_elems : stride1_elems * dim1) * 2};
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapSwizzle sw = swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return femto_fail(FEMTO_ERR_ALIGN, "cuTensorMapEncodeTiled failed (%d): dims %llu x %llu x %llu, row stride %llu B",
@@ -564,6 +604,13 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   if (g.b_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.K, g.N, nb, g.ldb, g.strideB, 64, BN));
   else FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, 64, BK));
 
+  CUtensorMap tmC = tmA;
+  p.tma_store = 0;
+  const bool bf16_out = g.epi != EPI_F32 && g.epi != EPI_XENT_STATS;
+  if (bf16_out && splits == 1 && (g.ldc & 7) == 0 && (g.strideC & 7) == 0 && aligned16(g.C)) {
+    FEMTO_TRY(make_tmap_3d_bf16_sw(&tmC, g.C, g.N, g.M, nb, g.ldc, g.strideC, 32, 32, 2));
+    p.tma_store = 1;
+  }
   const int grid = std::min(p.total_units, sms);
   static bool attr_done = false;
   if (!attr_done) {
@@ -578,10 +625,10 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
     cudaEventCreate(&e0); cudaEventCreate(&e1);
     cudaEventRecord(e0, s);
   }
-  if (g.a_kmajor && g.b_kmajor) gemm_tc_kernel<true, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
-  else if (g.a_kmajor) gemm_tc_kernel<true, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
-  else if (g.b_kmajor) gemm_tc_kernel<false, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
-  else gemm_tc_kernel<false, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, p);
+  if (g.a_kmajor && g.b_kmajor) gemm_tc_kernel<true, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  else if (g.a_kmajor) gemm_tc_kernel<true, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  else if (g.b_kmajor) gemm_tc_kernel<false, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  else gemm_tc_kernel<false, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
   if (g_prof.on) {
     cudaEventRecord(e1, s);
     g_prof.ev.push_back(e0); g_prof.ev.push_back(e1);
