@@ -192,6 +192,8 @@ def run_ours(args):
     st = fb.GradientState(cfg, max_batch=B, compute_type="bfloat16", short_window=spec["short_window"], doc_mask=True,
                           rank=rank, world=world, nccl_id=nccl_id)
     st.refresh_weights(params.theta)
+    if world > 1 and args.overlap:
+        _lib.check(_lib.lib().femto_set_overlap(st.h, 1))   # one micro-step per update: reduce delta while the reverse pass runs
     opt = fb.MuonAdamW(params, lay, st, compute_type="bfloat16", weight_decay=0.01)
     total = args.steps + args.warmup
     pk = fb.PackedBatches(cfg.vocab_size, T, B, max_document_tokens=cfg.max_document_tokens, rank=rank)
@@ -316,6 +318,8 @@ def main():
     ap.add_argument("--config", default="d20", choices=sorted(CONFIGS))
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-overlap", dest="overlap", action="store_false",
+                    help="sum delta over ranks after the reverse pass instead of bucket by bucket during it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -63,6 +63,7 @@ SIGNATURES = {
     "femto_forward_loss": (I32, [P, P, P, P, P, I32, I32, P, P, P]),
     "femto_loss_and_gradient_host": (I32, [P, P, P, P, P, P, I32, I32, I32, C.POINTER(F), C.POINTER(I32), P]),
     "femto_grad_sync": (I32, [P, P, P, P, P]),
+    "femto_set_overlap": (I32, [P, I32]),
     "femto_optimizer_state_sizes": (I32, [P, C.POINTER(I64)]),
     "femto_optimizer_create": (I32, [P, C.POINTER(OptimizerConfig), P, P, P, P, C.POINTER(P)]),
     "femto_optimizer_destroy": (I32, [P]),

@@ -141,9 +141,20 @@ int32_t femto_grad_sync(femto_handle* h, float* delta, float* loss_inout, int32_
   if (!h || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   if (h->world <= 1) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  FEMTO_TRY(dp_allreduce_sum_f32(h->dp, delta, h->nparams, s));
+  if (h->delta_synced) {
+    FEMTO_TRY(dp_join(h->dp, s));   // the buckets were queued by the reverse pass
+    h->delta_synced = false;
+  } else {
+    FEMTO_TRY(dp_allreduce_sum_f32(h->dp, delta, h->nparams, s));
+  }
   if (loss_inout) FEMTO_TRY(dp_allreduce_sum_f32(h->dp, loss_inout, 1, s));
   if (n_valid_inout) FEMTO_TRY(dp_allreduce_sum_i32(h->dp, n_valid_inout, 1, s));
+  return 0;
+}
+
+int32_t femto_set_overlap(femto_handle* h, int32_t enable) {
+  if (!h) return femto_fail(FEMTO_ERR_ARG, "NULL handle");
+  h->overlap_sync = enable != 0;
   return 0;
 }
 

@@ -56,6 +56,10 @@ int nccl_check(int r, const char* what) {
 struct DpState {
   nccl_comm comm = nullptr;
   int rank = 0, world = 1;
+  cudaStream_t cs = nullptr;      // communication stream: bucket all-reduces overlap the reverse pass
+  cudaEvent_t ready = nullptr;    // compute -> comm: the bucket's gradients are complete
+  cudaEvent_t done = nullptr;     // comm -> compute: every queued bucket has been reduced
+  bool pending = false;
 };
 
 int dp_unique_id(void* id128) {
@@ -76,13 +80,39 @@ int dp_create(DpState** out, int rank, int world, const void* id128) {
   memcpy(&id, id128, 128);
   int r = nccl_check(g_nccl.init_rank(&d->comm, world, id, rank), "ncclCommInitRank");
   if (r) { delete d; return r; }
+  CUDA_TRY(cudaStreamCreateWithFlags(&d->cs, cudaStreamNonBlocking));
+  CUDA_TRY(cudaEventCreateWithFlags(&d->ready, cudaEventDisableTiming));
+  CUDA_TRY(cudaEventCreateWithFlags(&d->done, cudaEventDisableTiming));
   *out = d;
+  return 0;
+}
+
+// Queue an in-place sum over ranks of buf[0..n) on the communication stream, ordered after
+// everything already enqueued on `compute`.
+int dp_bucket_allreduce(DpState* d, float* buf, long long n, cudaStream_t compute) {
+  if (!d || n <= 0) return 0;
+  CUDA_TRY(cudaEventRecord(d->ready, compute));
+  CUDA_TRY(cudaStreamWaitEvent(d->cs, d->ready, 0));
+  FEMTO_TRY(nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_FLOAT32, NCCL_SUM, d->comm, d->cs), "ncclAllReduce"));
+  d->pending = true;
+  return 0;
+}
+// Make `compute` wait for every queued bucket.
+int dp_join(DpState* d, cudaStream_t compute) {
+  if (!d || !d->pending) return 0;
+  CUDA_TRY(cudaEventRecord(d->done, d->cs));
+  CUDA_TRY(cudaStreamWaitEvent(compute, d->done, 0));
+  d->pending = false;
   return 0;
 }
 
 void dp_destroy(DpState* d) {
   if (!d) return;
+  if (d->cs) cudaStreamSynchronize(d->cs);
   if (d->comm && g_nccl.destroy) g_nccl.destroy(d->comm);
+  if (d->ready) cudaEventDestroy(d->ready);
+  if (d->done) cudaEventDestroy(d->done);
+  if (d->cs) cudaStreamDestroy(d->cs);
   delete d;
 }
 

@@ -360,6 +360,12 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   if (!backward) return 0;
 
   // ---- reverse ----
+  // With overlap_sync each finished range of delta (lm_head, then one transformer block at a time,
+  // then the embeddings) is summed over ranks on the communication stream while the rest of the
+  // reverse pass runs.
+  const bool ov = h->overlap_sync && h->dp != nullptr;
+  h->delta_synced = false;
+  if (ov) FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_lm, (long long)Vp * d, s));
   int nb = 0;
   FEMTO_TRY(scatter_plan_build(h->plan, h->tok0, N, Vp, s));
   FEMTO_TRY(S::head_bwd(dxnf, (const T*)h->xnf, h->rf, xb, (T*)h->dxf, N, d, h->partial, &nb, s));
@@ -409,6 +415,7 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     FEMTO_TRY(S::mix_bwd(dx, dxn, (const T*)l.xn1, l.r1, xin, (const T*)h->x0, theta + p.lam_b, theta + p.lam_x0,
                          (T*)h->dx0, i == L - 1, N, d, h->partial, &nb, s));
     FEMTO_TRY(reduce_partials(h->partial, nb, 2, delta + p.lam_b, nullptr, 1.f, true, s));
+    if (ov) FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + p.wq, p.lam_x0 + 1 - p.wq, s));   // the block's range is contiguous
   }
   FEMTO_TRY(S::add((T*)h->dx0, dx, (long long)N * d, s));
   FEMTO_TRY(S::smear_gate_bwd((const T*)h->dx0, (const T*)h->xe, h->sg, theta + h->off_lam_s, N, Tl, d, h->dpre_s,
@@ -417,6 +424,11 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   FEMTO_TRY(S::embed_bwd((const T*)h->dx0, (const T*)h->sh_wte, h->tok0, (const T*)h->xe, h->sg, h->dpre_s,
                          theta + h->off_smear, theta + h->off_lam_s, N, Tl, d, eps, dxn, s));
   FEMTO_TRY(scatter_rows<T>(h->plan, delta + h->off_wte, dxn, d, d, s));
+  if (ov) {
+    FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_wte, (long long)Vp * d, s));
+    FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_smear, 26, s));   // smear gate (24), lam_s, lam_y
+    h->delta_synced = true;
+  }
   return 0;
 }
 

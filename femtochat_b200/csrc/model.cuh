@@ -58,6 +58,8 @@ struct femto_handle {
   size_t attn_ws_bytes = 0;
   struct ScatterPlan* plan = nullptr;
   DpState* dp = nullptr;
+  bool overlap_sync = false;     // sum delta over ranks in buckets while the reverse pass runs
+  bool delta_synced = false;     // the last step already reduced delta (femto_grad_sync only joins)
   std::string err;
 };
 
@@ -78,3 +80,5 @@ int dp_allreduce_sum_f32(DpState* d, float* buf, long long n, cudaStream_t s);
 int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s);
 int dp_reduce_scatter_f32(DpState* d, const float* send, float* recv, long long n_per_rank, cudaStream_t s);
 int dp_allgather_bytes(DpState* d, const void* send, void* recv, long long bytes_per_rank, cudaStream_t s);
+int dp_bucket_allreduce(DpState* d, float* buf, long long n, cudaStream_t compute);
+int dp_join(DpState* d, cudaStream_t compute);

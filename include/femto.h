@@ -117,6 +117,12 @@ int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float*
 int32_t femto_grad_sync(femto_handle* h, float* delta, float* loss_inout, int32_t* n_valid_inout,
                         void* stream);
 
+/* When enabled (world > 1), femto_loss_and_gradient sums each finished range of delta over ranks on a
+ * communication stream while the rest of the reverse pass runs; femto_grad_sync then only waits for
+ * those reductions.  Enable it for the LAST micro-step of an update only: earlier micro-steps must
+ * leave delta local (scripts/train.jl:117-131 accumulates before the single update). */
+int32_t femto_set_overlap(femto_handle* h, int32_t enable);
+
 /* ---- optimiser: MuonAdamW (src/optim.jl:318-440) ---------------------------------------------- */
 typedef struct femto_optimizer_config {
   float unembedding_lr, embedding_lr, matrix_lr, weight_decay, scalar_lr, smear_lr; /* :321-326 */
