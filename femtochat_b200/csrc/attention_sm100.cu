@@ -179,28 +179,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok && !mbar_wait(&s_full[st], ph, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
+      // x holds the raw scores; the 1/sqrt(hd) * log2(e) factor is folded into the exponent's FMA.
+      // Maxima and sums use four independent accumulators so the chains do not serialise.
       float x[64];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        uint32_t rr[32];
-        tmem_ld32(tS[st] + lane_off + (2 * hs + u) * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; j++) x[u * 32 + j] = __uint_as_float(rr[j]) * c;
-      }
+      tmem_ld32(tS[st] + lane_off + (2 * hs) * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+      tmem_ld32(tS[st] + lane_off + (2 * hs + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+      tmem_ld_wait();
       const bool need_mask = (k0 + 63 > q) || (k0 < lo);
-      float mt = -INFINITY;
       if (need_mask) {
 #pragma unroll
         for (int j = 0; j < 64; j++) {
           const int k = k0 + j;
           x[j] = (k <= q && k >= lo) ? x[j] : -INFINITY;
-          mt = fmaxf(mt, x[j]);
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 64; j++) mt = fmaxf(mt, x[j]);
       }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 64; j += 4) {
+        mx[0] = fmaxf(mx[0], x[j]); mx[1] = fmaxf(mx[1], x[j + 1]);
+        mx[2] = fmaxf(mx[2], x[j + 2]); mx[3] = fmaxf(mx[3], x[j + 3]);
+      }
+      float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;   // scaled units (c > 0 keeps the argmax)
       // combine the two half-row maxima; after this barrier both threads hold all of S in registers,
       // so P may overwrite S in TMEM
       xmax[(i & 1) * 256 + hs * 128 + r] = mt;
@@ -229,18 +228,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       const float mm = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
+      float sm[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int u = 0; u < 2; u++) {
         uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-          const float p0 = fast_exp2(x[u * 32 + 2 * j] - mm), p1 = fast_exp2(x[u * 32 + 2 * j + 1] - mm);
-          sum += p0 + p1;
+        for (int j = 0; j < 16; j += 2) {
+          const float p0 = fast_exp2(fmaf(x[u * 32 + 2 * j], c, -mm)), p1 = fast_exp2(fmaf(x[u * 32 + 2 * j + 1], c, -mm));
+          const float p2 = fast_exp2(fmaf(x[u * 32 + 2 * j + 2], c, -mm)), p3 = fast_exp2(fmaf(x[u * 32 + 2 * j + 3], c, -mm));
+          sm[0] += p0; sm[1] += p1; sm[2] += p2; sm[3] += p3;
           pk[j] = pack_bf16(p0, p1);
+          pk[j + 1] = pack_bf16(p2, p3);
         }
         tmem_st16(tS[st] + lane_off + (2 * hs + u) * 16, pk);
       }
+      const float sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
       l += sum;
       tmem_st_wait();
       tc_fence_before();
