@@ -270,9 +270,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
-// dK / dV kernel.  The query tile of an iteration is processed as two halves of 64 queries, so the
-// S^T / dP^T buffers in TMEM (64 columns each) can be double-buffered: the tensor core computes
-// the inputs of half h+1 while the threads turn half h into P^T and dS^T.
+// dK / dV kernel.  S^T and dP^T of a query tile are computed with full 128-wide instructions; the
+// threads then convert the tile in two halves of 64 queries, so dV / dK of the first half run on the
+// tensor core while the second half is being converted.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(384, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -371,42 +371,50 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_in = idesc_bf16(BT, 64, false, false);   // [128 keys] x [64 queries], K = head_dim
+      constexpr uint32_t idesc_in = idesc_bf16(BT, BT, false, false);   // [128 keys] x [128 queries], K = head_dim
       constexpr uint32_t idesc_out = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous, K = 64 queries
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      auto issue_in = [&](int h2) -> bool {  // S^T = K Q^T, dP^T = V dO^T for 64 queries
-        const int it = h2 >> 1, hf = h2 & 1, st = it & 1, bf = h2 & 1;
-        if (hf == 0 && !mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) return false;
+      // S^T = K Q^T and dP^T = V dO^T for a whole query tile (128-wide instructions run at full rate;
+      // 64-wide ones cost the same per instruction)
+      auto issue_in = [&](int it) -> bool {
+        const int st = it & 1;
+        if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES) + hf * 8192, do_addr = smem_u32(sdO + st * TILE_BYTES) + hf * 8192;
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES), do_addr = smem_u32(sdO + st * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
           const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tS[bf], smem_desc_sw128(k_addr + off, 16, 1024), smem_desc_sw128(q_addr + off, 16, 1024), idesc_in, k > 0);
+          mma_ss(tS[0], smem_desc_sw128(k_addr + off, 16, 1024), smem_desc_sw128(q_addr + off, 16, 1024), idesc_in, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
           const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tdP[bf], smem_desc_sw128(v_addr + off, 16, 1024), smem_desc_sw128(do_addr + off, 16, 1024), idesc_in, k > 0);
+          mma_ss(tdP[0], smem_desc_sw128(v_addr + off, 16, 1024), smem_desc_sw128(do_addr + off, 16, 1024), idesc_in, k > 0);
         }
-        tc_commit(&st_full[bf]);
+        tc_commit(&st_full[0]);
         return true;
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, a.status);
       if (ok) { tc_fence_after(); ok = issue_in(0); }
-      for (int h2 = 0; h2 < n2 && ok; h2++) {
-        const int it = h2 >> 1, hf = h2 & 1, st = it & 1, bf = h2 & 1;
-        if (h2 + 1 < n2 && !issue_in(h2 + 1)) { ok = false; break; }
-        if (!mbar_wait(&pds_ready[bf], (h2 >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES) + hf * 8192, do_addr = smem_u32(sdO + st * TILE_BYTES) + hf * 8192;
+      for (int it = 0; it < nit && ok; it++) {
+        const int st = it & 1;
+        const uint32_t q_base = smem_u32(sQ + st * TILE_BYTES), do_base = smem_u32(sdO + st * TILE_BYTES);
+        for (int hf = 0; hf < 2 && ok; hf++) {
+          // the threads finish the first 64 queries of the tile first, so dV/dK of that half run
+          // on the tensor core while they work on the second half
+          if (!mbar_wait(&pds_ready[hf], it & 1, abort_flag, a.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t q_addr = q_base + hf * 8192, do_addr = do_base + hf * 8192;
 #pragma unroll
-        for (int k = 0; k < 4; k++)  // dV += P^T dO over 64 queries
-          mma_ts(tdV, tS[bf] + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; k++)  // dV += P^T dO over 64 queries
+            mma_ts(tdV, tS[hf] + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (it > 0 || hf > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < 4; k++)  // dK += dS^T Q
-          mma_ts(tdK, tdP[bf] + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
-        if (hf == 1) tc_commit(&qdo_empty[st]);
+          for (int k = 0; k < 4; k++)  // dK += dS^T Q
+            mma_ts(tdK, tdP[hf] + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (it > 0 || hf > 0 || k > 0) ? 1u : 0u);
+        }
+        if (!ok) break;
+        tc_commit(&qdo_empty[st]);
+        if (it + 1 < nit && !issue_in(it + 1)) { ok = false; break; }
       }
       if (ok) tc_commit(acc_done);
     }
@@ -443,7 +451,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      if (ok && !mbar_wait(&st_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
+      if (ok && hf == 0 && !mbar_wait(&st_full[0], it & 1, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
       uint32_t pp[16], pd[16];   // kept in registers until the partner thread has read S^T / dP^T
@@ -479,7 +487,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&pds_ready[bf]);
+      if (lane == 0) mbar_arrive(&pds_ready[bf]);   // bf == half index: one phase per query tile
     }
     if (ok && mbar_wait(acc_done, 0, abort_flag, a.status)) {
       tc_fence_after();
