@@ -108,8 +108,8 @@ enum GemmEpi {
   EPI_DRELU2 = 3,   // C_T = acc * 2*sqrt(aux_T)   (aux = relu(u)^2, so 2*sqrt(aux) = 2*max(u,0))
   EPI_AXPBY = 4,    // C_T = alpha*aux_T + beta*acc
   EPI_F32 = 5,      // C_f32 = (beta? C_f32 : 0) + alpha*acc
-  EPI_XENT_STATS = 6,   // tensor-core path only: per-row partial (max, sum exp) of softcapped logits
-  EPI_XENT_DLOGIT = 7,  // tensor-core path only: C_T = d loss / d logit from lse and targets
+  EPI_XENT_STATS = 6,   // tensor-core path only: per-row partial (max, sum exp) of softcapped logits; with C set the
+                        // logits are also stored there as T
 };
 
 struct GemmArgs {
@@ -124,14 +124,11 @@ struct GemmArgs {
   // fp32 split output: up to 3 column segments of C go to different destinations (fused QKV dW).
   int nseg = 0; int seg_col0[3] = {0, 0, 0}; int seg_ncol[3] = {0, 0, 0};
   float* seg_ptr[3] = {nullptr, nullptr, nullptr}; long long seg_ld[3] = {0, 0, 0};
-  // cross-entropy epilogues
+  // cross-entropy statistics epilogue
   const int* targets0 = nullptr;   // [M] 0-based target or -1
-  const float* lse = nullptr;      // [M]
-  float2* stats = nullptr;         // [M][ntiles_n] partial (max, sumexp)
+  float2* stats = nullptr;         // [M][2 * ntiles_n] partial (max, sumexp)
   float* tz = nullptr;             // [M] softcapped target logit
-  float xscale = 1.f;              // weight of each valid row in dlogit
-  const float* xscale_dev = nullptr;  // optional device factor multiplied into xscale (1/n_valid)
-  int vocab = 0;                   // columns >= vocab are ignored by the xent epilogues
+  int vocab = 0;                   // columns >= vocab are ignored
   // tensor-core path scratch
   void* ws = nullptr; size_t ws_bytes = 0;  // stream-K partials
   unsigned int* status = nullptr;

@@ -69,10 +69,33 @@ __device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m
   return nullptr;
 }
 
+// The warp's 32 x 32 block of bf16 results goes to shared memory (64-byte swizzle, so the 16-byte
+// stores of a quarter warp hit distinct banks) and leaves as one TMA tiled store, which also clips
+// rows >= M and columns >= N.
+__device__ __forceinline__ void stage_store_bf16(const float (&v)[32], uint8_t* stage_buf, const CUtensorMap* tmC, int nc,
+                                                 int m_warp0, int bz, int lane) {
+  if (lane == 0) bulk_wait_read<1>();   // the store that last used this buffer has read it
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    uint4 q;
+    __nv_bfloat162* hq = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int e = 0; e < 4; e++) hq[e] = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+    *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = q;
+  }
+  fence_proxy_async();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_3d(tmC, stage_buf, nc, m_warp0, bz);
+    bulk_commit();
+  }
+}
+
 // One 32-column chunk of one output row with a bf16 result: C = f(acc, aux).
 template <int EPI>
 __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], int bz, int m, int nc, bool full_chunk,
-                                           int tgt, float lse, float xw, const uint4 (&pre)[4], bool use_pre, bool row_ok,
+                                           const uint4 (&pre)[4], bool use_pre, bool row_ok,
                                            uint8_t* stage_buf, const CUtensorMap* tmC, int m_warp0, int lane) {
   bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
   constexpr bool need_aux = EPI == EPI_RESID || EPI == EPI_DRELU2 || EPI == EPI_AXPBY;
@@ -105,12 +128,6 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
     if constexpr (EPI == EPI_RELU2) { x = fmaxf(x, 0.f); x = x * x; }
     if constexpr (EPI == EPI_DRELU2) x = x * 2.f * sqrt_approx(fmaxf(a[j], 0.f));
     if constexpr (EPI == EPI_AXPBY) x = alpha * a[j] + beta * x;
-    if constexpr (EPI == EPI_XENT_DLOGIT) {
-      float z = softcap15(x);
-      float t = z * (1.f / 15.f);
-      float dz = xw * (__expf(z - lse) - ((nc + j) == tgt ? 1.f : 0.f));
-      x = (nc + j < g.vocab) ? dz * (1.f - t * t) : 0.f;
-    }
     v[j] = x;
   }
   if (g.dbg == 1) {
@@ -119,25 +136,7 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
     for (int j = 0; j < 32; j++) t += v[j];
     if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
   } else if (stage_buf != nullptr) {
-    // Coalesced path: the warp's 32 x 32 block goes to shared memory (64-byte swizzle, so the
-    // 16-byte stores of a quarter warp hit distinct banks) and leaves as one TMA tiled store, which
-    // also clips rows >= M and columns >= N.
-    if (lane == 0) bulk_wait_read<1>();   // the store that last used this buffer has read it
-    __syncwarp();
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      uint4 q;
-      __nv_bfloat162* hq = reinterpret_cast<__nv_bfloat162*>(&q);
-#pragma unroll
-      for (int e = 0; e < 4; e++) hq[e] = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
-      *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = q;
-    }
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_3d(tmC, stage_buf, nc, m_warp0, bz);
-      bulk_commit();
-    }
+    stage_store_bf16(v, stage_buf, tmC, nc, m_warp0, bz, lane);
   } else if (!row_ok) {
     // nothing to store for rows past M
   } else if (vec) {
@@ -289,15 +288,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool row_ok = m < g.M;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
       // cross-entropy row state
-      float rmax = -INFINITY, rsum = 0.f, lse = 0.f, xw = 0.f;
+      float rmax = -INFINITY, rsum = 0.f;
       int tgt = -1;
-      if (g.epi == EPI_XENT_STATS || g.epi == EPI_XENT_DLOGIT) {
-        if (row_ok) tgt = g.targets0[m];
-        if (g.epi == EPI_XENT_DLOGIT && row_ok) {
-          lse = g.lse[m];
-          xw = tgt >= 0 ? g.xscale * (g.xscale_dev ? g.xscale_dev[0] : 1.f) : 0.f;
-        }
-      }
+      if (g.epi == EPI_XENT_STATS && row_ok) tgt = g.targets0[m];
       // operands of the residual / relu^2-reverse / axpby epilogues are fetched one chunk ahead
       const bool aux_epi = p.splits == 1 && (g.epi == EPI_RESID || g.epi == EPI_DRELU2 || g.epi == EPI_AXPBY) &&
                            (g.ldaux & 7) == 0 && (g.ldc & 7) == 0 && row_ok;
@@ -325,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int nc = n0 + c * 32;
         if (g.dbg == 3) { if (r[0] == 0x12345678u && r[31] == 0x1u) reinterpret_cast<bf16*>(g.C)[0] = __float2bfloat16_rn(1.f); continue; }
-        const bool tma_out = p.tma_store != 0 && p.splits == 1 && g.epi != EPI_F32 && g.epi != EPI_XENT_STATS;
+        const bool tma_out = p.tma_store != 0 && p.splits == 1 && g.epi != EPI_F32;
         if (nc >= g.N || (!row_ok && !tma_out)) continue;   // on the TMA path the whole warp stays together
         uint8_t* sbuf = tma_out ? store_stage + ((warp - 2) * 2 + ((c >> 1) & 1)) * 2048 : nullptr;
         const bool full_chunk = nc + 32 <= g.N;
@@ -362,6 +355,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           } break;
           case EPI_XENT_STATS: {
+            // with a destination the raw logits are kept in bf16 (as the reference materialises them) and
+            // the statistics are taken from the rounded values, so a later pass over the stored chunk agrees
+            if (tma_out) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+              stage_store_bf16(v, sbuf, &tmC, nc, mt * BM + quad * 32, bz, lane);
+            }
             float cm = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; j++) {
@@ -379,12 +379,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             rsum = rsum * __expf(rmax - nm) + cs;
             rmax = nm;
           } break;
-          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_XENT_DLOGIT: bf16_chunk<EPI_XENT_DLOGIT>(g, v, bz, m, nc, full_chunk, tgt, lse, xw, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
           default: break;
         }
       }
@@ -522,6 +521,7 @@ bool gemm_tc_supported(const GemmArgs& g) {
     if (!g.ws) return false;
   } else if (g.epi == EPI_XENT_STATS) {
     if (!g.stats || !g.tz || !g.targets0) return false;
+    if (g.C && ((g.ldc & 7) || (g.strideC & 7) || !aligned16(g.C))) return false;  // kept logits leave by TMA only
   } else {
     if (!g.C && g.epi != EPI_XENT_STATS) return false;
   }
@@ -606,7 +606,7 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
 
   CUtensorMap tmC = tmA;
   p.tma_store = 0;
-  const bool bf16_out = g.epi != EPI_F32 && g.epi != EPI_XENT_STATS;
+  const bool bf16_out = g.epi != EPI_F32 && (g.epi != EPI_XENT_STATS || g.C != nullptr);
   if (bf16_out && splits == 1 && (g.ldc & 7) == 0 && (g.strideC & 7) == 0 && aligned16(g.C)) {
     FEMTO_TRY(make_tmap_3d_bf16_sw(&tmC, g.C, g.N, g.M, nb, g.ldc, g.strideC, 32, 32, 2));
     p.tma_store = 1;

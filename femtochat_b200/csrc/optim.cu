@@ -36,14 +36,28 @@ __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const 
                                                float* __restrict__ m, float* __restrict__ v, long long n, float alpha,
                                                float b1, float b2, float eps, float lam, float c1, float c2,
                                                float inv_nt) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    float g = delta[i] * inv_nt;
-    float mm = b1 * m[i] + (1.f - b1) * g;
-    float vv = b2 * v[i] + (1.f - b2) * g * g;
-    m[i] = mm;
-    v[i] = vv;
-    float th = theta[i] * (1.f - alpha * lam);
-    theta[i] = th - alpha * (mm / c1) / (sqrtf(vv / c2) + eps);
+  // four elements per thread, a block apart: the sixteen loads are issued before the arithmetic, which is what
+  // keeps enough bytes in flight (group offsets are arbitrary, so no wider-than-4-byte access is assumed)
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n; i0 += 4 * stride) {
+    float g[4], mo[4], vo[4], th[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const long long i = i0 + u * stride;
+      if (i < n) { g[u] = delta[i]; mo[u] = m[i]; vo[u] = v[i]; th[u] = theta[i]; }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const long long i = i0 + u * stride;
+      if (i >= n) continue;
+      const float gg = g[u] * inv_nt;
+      const float mm = b1 * mo[u] + (1.f - b1) * gg;
+      const float vv = b2 * vo[u] + (1.f - b2) * gg * gg;
+      m[i] = mm;
+      v[i] = vv;
+      const float t = th[u] * (1.f - alpha * lam);
+      theta[i] = t - alpha * (mm / c1) / (sqrtf(vv / c2) + eps);
+    }
   }
 }
 
@@ -68,9 +82,18 @@ __global__ void __launch_bounds__(256) k_sumsq_cols(const T* __restrict__ X, int
   const int o = blockIdx.x * 256 + threadIdx.x;
   if (o >= out) return;
   const T* p = X + (long long)k * in * out + o;
-  float acc = 0.f;
-  for (int i = 0; i < in; i++) { float v = to_f<T>(p[(long long)i * out]); acc += v * v; }
-  vec[(long long)k * out + o] = acc;
+  // eight independent partial sums (rows i mod 8), combined in a fixed order: eight loads in flight per thread
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int i = 0;
+  for (; i + 8 <= in; i += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) v[u] = to_f<T>(p[(long long)(i + u) * out]);
+#pragma unroll
+    for (int u = 0; u < 8; u++) a[u] += v[u] * v[u];
+  }
+  for (; i < in; i++) { float v = to_f<T>(p[(long long)i * out]); a[i & 7] += v * v; }
+  vec[(long long)k * out + o] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
 }
 // vec[k][i] = sum_o X[k][i][o]^2 (warp per row)
 template <typename T>

@@ -787,21 +787,63 @@ __global__ void __launch_bounds__(256) k_reduce_partials(const float* __restrict
   out[j] = (accumulate ? out[j] : 0.f) + acc;
 }
 
+// One warp per row: merge the row's (max, sum exp) partials into its logsumexp.
 __global__ void __launch_bounds__(256) k_xent_finalize(const float2* __restrict__ stats, int ntile,
                                                        const float* __restrict__ tz, const int* __restrict__ tgt0,
                                                        int n, float* __restrict__ lse, float* __restrict__ loss_rows) {
-  int row = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= n) return;
+  const float2* st = stats + (long long)row * ntile;
   float m = -INFINITY;
-  for (int i = 0; i < ntile; i++) m = fmaxf(m, stats[(long long)row * ntile + i].x);
+  for (int i = lane; i < ntile; i += 32) m = fmaxf(m, st[i].x);
+  m = warp_max(m);
   float s = 0.f;
-  for (int i = 0; i < ntile; i++) {
-    float2 st = stats[(long long)row * ntile + i];
-    s += st.y * expf(st.x - m);
+  for (int i = lane; i < ntile; i += 32) {
+    const float2 v = st[i];
+    s += v.y * expf(v.x - m);
   }
-  float l = m + logf(s);
-  lse[row] = l;
-  loss_rows[row] = tgt0[row] >= 0 ? l - tz[row] : 0.f;
+  s = warp_sum(s);
+  if (lane == 0) {
+    const float l = m + logf(s);
+    lse[row] = l;
+    loss_rows[row] = tgt0[row] >= 0 ? l - tz[row] : 0.f;
+  }
+}
+
+// In place on a chunk of stored bf16 logits l[row][col]: d loss / d logit = w (softmax(z) - onehot) (1 - tanh^2(l/15)),
+// z = 15 tanh(l/15), with the row's logsumexp from the statistics pass (src/kernels.jl:16-28;
+// ext/FemtoChatEnzymeExt.jl:175-189).  Same tanh.approx / ex2 arithmetic as that pass, so softmax sums to 1 over
+// the stored values.  A thread takes four 8-column groups 2048 columns apart (all four loads in flight before the
+// arithmetic); rows with an ignored target become zero.
+__global__ void __launch_bounds__(256) k_xent_dlogit_inplace(bf16* __restrict__ buf, long long ld,
+                                                             const float* __restrict__ lse_rows,
+                                                             const int* __restrict__ tgt0, int V, float w_host,
+                                                             const float* __restrict__ w_dev) {
+  const long long row = blockIdx.y;
+  const int col0 = blockIdx.x * 8192 + threadIdx.x * 8;
+  const int tg = tgt0[row];
+  const float w = tg >= 0 ? w_host * (w_dev ? w_dev[0] : 1.f) : 0.f;
+  const float lse = lse_rows[row];
+  bf16* base = buf + row * ld;
+  uint4 q[4];
+#pragma unroll
+  for (int u = 0; u < 4; u++)
+    if (col0 + u * 2048 < V) q[u] = *reinterpret_cast<const uint4*>(base + col0 + u * 2048);
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    const int col = col0 + u * 2048;
+    if (col >= V) continue;
+    bf16* h = reinterpret_cast<bf16*>(&q[u]);
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(__bfloat162float(h[e]) * (1.f / 15.f)));
+      const float z = 15.f * t;
+      const float dz = w * (__expf(z - lse) - ((col + e) == tg ? 1.f : 0.f));
+      h[e] = __float2bfloat16_rn(dz * (1.f - t * t));
+    }
+    *reinterpret_cast<uint4*>(base + col) = q[u];
+  }
 }
 
 inline int row_grid(long long N) { return cdiv(N, WPB); }
@@ -981,7 +1023,14 @@ int reduce_partials(const float* partial, int nrow, int ncol, float* out, const 
 }
 int xent_finalize(const float2* stats, int ntile, const float* tz, const int* tgt0, int n, float* lse,
                   float* loss_rows, cudaStream_t s) {
-  k_xent_finalize<<<cdiv(n, 256), 256, 0, s>>>(stats, ntile, tz, tgt0, n, lse, loss_rows);
+  k_xent_finalize<<<cdiv(n, 8), 256, 0, s>>>(stats, ntile, tz, tgt0, n, lse, loss_rows);
+  KERNEL_CHECK();
+  return 0;
+}
+int xent_dlogit_inplace(void* logits_bf16, long long ld, const float* lse_rows, const int* tgt0, int n, int V, float w,
+                        const float* w_dev, cudaStream_t s) {
+  if ((ld & 7) || (V & 7)) return femto_fail(FEMTO_ERR_ALIGN, "xent_dlogit_inplace: row pitch and vocabulary must be multiples of 8");
+  k_xent_dlogit_inplace<<<dim3(cdiv(V, 8192), n), 256, 0, s>>>(reinterpret_cast<bf16*>(logits_bf16), ld, lse_rows, tgt0, V, w, w_dev);
   KERNEL_CHECK();
   return 0;
 }

@@ -1,9 +1,9 @@
 // lm_head tail: softcap + cross-entropy + its reverse (src/gpt.jl:165-170,172-194;
 // src/kernels.jl:16-28; ext/FemtoChatEnzymeExt.jl:175-189), in token chunks.
-// Tensor-core path (bf16, aligned): pass 1 is a GEMM whose epilogue keeps only per-row
-// (max, sum exp) partials and the target logit; pass 2 recomputes the tile and its epilogue writes
-// d loss/d logit in bf16 for the chunk, which feeds the dX and dW GEMMs.  fp32 / unaligned shapes
-// materialise an fp32 logits chunk instead.
+// Tensor-core path (bf16, aligned): pass 1 is a GEMM whose epilogue reduces each row to (max, sum exp)
+// partials and the target logit and, for the reverse pass, stores the chunk's logits in bf16; a
+// streaming pass rewrites that chunk in place as d loss/d logit, which feeds the dX and dW GEMMs
+// (forward-only calls store nothing).  fp32 / unaligned shapes materialise an fp32 logits chunk.
 #include <algorithm>
 
 #include "common.cuh"
@@ -20,16 +20,16 @@ template <typename T> int xent_tail(const XentArgs& x, cudaStream_t s) {
     g.A = xc; g.lda = d; g.B = x.W; g.ldb = ld; g.b_kmajor = false; g.M = cn; g.N = V; g.K = d;
     g.targets0 = x.targets0 + c0; g.vocab = V;
     g.epi = EPI_XENT_STATS; g.stats = x.stats; g.tz = x.tz + c0;
+    // reverse pass: the statistics GEMM also keeps the chunk's logits in bf16 (as the reference materialises
+    // them) and a streaming pass turns them into d loss/d logit in place
+    if (x.backward) { g.C = x.dlogit; g.ldc = ld; }
     const bool tc = sizeof(T) == 2 && gemm_tc_supported(g);
     if (tc) {
       FEMTO_TRY(gemm_tc_bf16(g, s));
       FEMTO_TRY(xent_finalize(x.stats, 2 * ((V + 255) / 256), x.tz + c0, x.targets0 + c0, cn, x.lse_rows + c0,
                               x.loss_rows + c0, s));
-      if (x.backward) {
-        g.epi = EPI_XENT_DLOGIT; g.C = x.dlogit; g.ldc = ld; g.lse = x.lse_rows + c0;
-        g.xscale = x.scale; g.xscale_dev = x.scale_dev;
-        FEMTO_TRY(gemm_tc_bf16(g, s));
-      }
+      if (x.backward)
+        FEMTO_TRY(xent_dlogit_inplace(x.dlogit, ld, x.lse_rows + c0, x.targets0 + c0, cn, V, x.scale, x.scale_dev, s));
     } else {
       if (!x.logits_f32) return femto_fail(FEMTO_ERR_UNSUPPORTED, "lm_head tail: no fp32 logits workspace for this shape");
       g.epi = EPI_F32; g.beta = 0.f; g.C = x.logits_f32; g.ldc = ld;
