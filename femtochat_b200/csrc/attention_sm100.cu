@@ -5,11 +5,13 @@
 // src/kernels.jl:131-219 and :287-379 (softmax in base 2, fp32 statistics).
 //
 // Forward: one CTA owns 128 queries of one (batch, head).  Warp 0 streams K/V tiles of 128 keys
-// with TMA (two stages each), warp 1 issues tcgen05.mma: S = Q K^T into one of two 128-column
-// TMEM buffers, then O += P V with P read back from TMEM (P overwrites S in place as bf16).
-// Warps 4-11 own the query rows, two threads per row (64 keys each): they read S with tcgen05.ld, keep the running
-// max / sum, rescale the TMEM-resident O only when the max grew by more than 2^8, and write P
-// with tcgen05.st.  S of tile j+1 is computed while the softmax of tile j runs.
+// with TMA (two stages each).  Warp 1 issues S = Q K^T into one of two 128-column TMEM buffers and
+// warp 2 issues O += P V with P read back from TMEM (P overwrites S in place as bf16): tcgen05.mma
+// issue blocks while the pipe is busy, so with one issuer per product the barrier waits of one
+// overlap the issue of the other.  Warps 4-11 own the query rows, two threads per row (64 keys
+// each): they read S with tcgen05.ld, keep the running max / sum, rescale the TMEM-resident O only
+// when the max grew by more than 2^8, and write P with tcgen05.st.  S of tile j+1 is computed
+// while the softmax of tile j runs.
 #include <algorithm>
 
 #include "sm100_ptx.cuh"
@@ -44,13 +46,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 5 * TILE_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]
-  uint64_t* p_ready = bars + 11;  // [2]
-  uint64_t* pv_done = bars + 13;  // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;    // [2] S of a tile is in TMEM; also frees the tile's K stage
+  uint64_t* p_ready = bars + 7;   // [2]
+  uint64_t* pv_done = bars + 9;   // [2] P V of a tile has been accumulated; also frees its V stage and its S/P buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xmax = reinterpret_cast<float*>(smem + 5 * TILE_BYTES + 256);  // [2 parities][2 halves][128 rows]
   float* xl = xmax + 512;                                               // [2 halves][128 rows]
@@ -80,10 +80,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; i++) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8);
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8); mbar_init(&pv_done[i], 1);
     }
-    mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -105,13 +104,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       bool ok = true;
       for (int i = 0; i < ntile && ok; i++) {
         const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
+        const uint32_t ph2 = ((i - 2) >> 1) & 1;   // phase of tile i-2, the previous user of this stage
         const int krow = (int)(row0 + (jlo + i) * BKV);
-        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, a.status)) { ok = false; break; }
+        if (i >= 2 && !mbar_wait(&s_full[st], ph2, abort_flag, a.status)) { ok = false; break; }
         mbar_expect_tx(&k_full[st], TILE_BYTES);
         tma_load_2d(sK + st * TILE_BYTES, &tmK, &k_full[st], p.k_col0 + kvh * HD, krow);
         tma_load_2d(sK + st * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[st], p.k_col0 + kvh * HD + 64, krow);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, a.status)) { ok = false; break; }
+        if (i >= 2 && !mbar_wait(&pv_done[st], ph2, abort_flag, a.status)) { ok = false; break; }
         mbar_expect_tx(&v_full[st], TILE_BYTES);
         tma_load_2d(sV + st * TILE_BYTES, &tmV, &v_full[st], p.v_col0 + kvh * HD, krow);
         tma_load_2d(sV + st * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[st], p.v_col0 + kvh * HD + 64, krow);
@@ -119,13 +118,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // S = Q K^T, both K-major
-      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // O = P V, V is N-contiguous
+      // ---------------- S = Q K^T issuer ----------------
+      // The two products of a tile are issued by different threads, so the barrier waits of one overlap
+      // the (blocking) instruction issue of the other and the tensor pipe is fed from whichever is ready.
+      constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // both operands K-major
       const uint32_t q_addr = smem_u32(sQ);
-      auto issue_s = [&](int i) -> bool {
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
+      for (int i = 0; i < ntile && ok; i++) {
         const int st = i & 1;
-        if (!mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag, a.status)) return false;
+        if (!mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag, a.status)) break;
+        // S(i) overwrites the buffer that held P(i-2): its P V must have been executed
+        if (i >= 2 && !mbar_wait(&pv_done[st], ((i - 2) >> 1) & 1, abort_flag, a.status)) break;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
 #pragma unroll
@@ -134,17 +137,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0);
         }
         tc_commit(&s_full[st]);
-        tc_commit(&k_empty[st]);
-        return true;
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
-      if (ok) { tc_fence_after(); ok = issue_s(0); }
-      for (int i = 0; i < ntile && ok; i++) {
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      // ---------------- O += P V issuer ----------------
+      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // V is N-contiguous
+      for (int i = 0; i < ntile; i++) {
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
-        if (i + 1 < ntile && !issue_s(i + 1)) { ok = false; break; }
-        if (!mbar_wait(&p_ready[st], ph, abort_flag, a.status)) { ok = false; break; }
-        if (!mbar_wait(&v_full[st], ph, abort_flag, a.status)) { ok = false; break; }
+        if (!mbar_wait(&p_ready[st], ph, abort_flag, a.status)) break;
+        if (!mbar_wait(&v_full[st], ph, abort_flag, a.status)) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
@@ -153,8 +156,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // 64-wide head_dim halves 16 KB apart.
           mma_ts(tO, tS[st] + k * 8, smem_desc_sw128(v_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(pv_done);
-        tc_commit(&v_empty[st]);
+        tc_commit(&pv_done[st]);
       }
     }
   } else if (warp >= 4) {
@@ -213,7 +215,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         m_used = m_new;
         if (i > 0) {
           // O lives in TMEM and is being accumulated by the tensor core: wait for tile i-1's P V
-          if (!mbar_wait(pv_done, (i - 1) & 1, abort_flag, a.status)) { ok = false; continue; }
+          if (!mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, a.status)) { ok = false; continue; }
           tc_fence_after();
 #pragma unroll
           for (int u = 0; u < 2; u++) {
@@ -252,7 +254,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     xl[hs * 128 + r] = l;
     asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
     l += xl[(hs ^ 1) * 128 + r];
-    if (ok && mbar_wait(pv_done, (ntile - 1) & 1, abort_flag, a.status)) {
+    if (ok && mbar_wait(&pv_done[(ntile - 1) & 1], ((ntile - 1) >> 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
       const float inv = 1.f / l;
       bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
