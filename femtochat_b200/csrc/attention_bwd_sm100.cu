@@ -4,7 +4,8 @@
 // atomics (ext/FemtoChatCUDAExt.jl:2002-2004); here two kernels each own their outputs, so every
 // gradient is summed in a fixed order:
 //   * dQ kernel: one CTA per 128 queries of a head; S = Q K^T and dP = dO V^T go to TMEM, the
-//     row-owning threads (two per row, each half of the keys) turn them into dS (bf16, written over S in TMEM), dQ += dS K stays in TMEM.
+//     row-owning threads (two per row, each half of the keys) turn them into dS (bf16, written
+//     over S in TMEM), dQ += dS K stays in TMEM.
 //   * dK/dV kernel: one CTA per 128 keys of a kv head; loops over the heads of the GQA group and
 //     the query tiles that see these keys; S^T = K Q^T and dP^T = V dO^T go to TMEM, threads own
 //     key rows and write P^T and dS^T back to TMEM, dV += P^T dO and dK += dS^T Q stay in TMEM.
@@ -54,8 +55,15 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D
 }
 
 // ------------------------------------------------------------------------------------------------
-// dQ kernel
+// dQ kernel.  Roles: warp 0 streams K (three stages: a K tile is held until dQ has used it) and V
+// (two stages) with TMA; warp 1 issues S = Q K^T and dP = dO V^T, warp 2 issues dQ += dS K (issue
+// of tcgen05.mma blocks while the pipe is busy, so two issuers keep it fed while one of them waits
+// on a barrier); warps 4-11 own the query rows.  S is double-buffered in TMEM; dP has one buffer,
+// which the threads release as soon as they hold its values in registers, so dP of the next tile
+// is computed while they work on the current one.
 // ------------------------------------------------------------------------------------------------
+constexpr int DQ_SMEM = TILE_BYTES * 7 + 1024 + 256;
+
 __global__ void __launch_bounds__(384, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -64,19 +72,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + TILE_BYTES;
-  uint8_t* sK = smem + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* sV = smem + 4 * TILE_BYTES;  // 2 stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint8_t* sK = smem + 2 * TILE_BYTES;  // 3 stages
+  uint8_t* sV = smem + 5 * TILE_BYTES;  // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * TILE_BYTES);
   uint64_t* qdo_full = bars;
-  uint64_t* k_full = bars + 1;     // [2]
-  uint64_t* k_empty = bars + 3;    // [2]
-  uint64_t* v_full = bars + 5;     // [2]
-  uint64_t* v_empty = bars + 7;    // [2]
+  uint64_t* k_full = bars + 1;     // [3]
+  uint64_t* k_free = bars + 4;     // [3] dQ of the tile in this stage has been executed
+  uint64_t* v_full = bars + 7;     // [2]
   uint64_t* s_full = bars + 9;     // [2]
-  uint64_t* dp_full = bars + 11;   // [1]
-  uint64_t* ds_ready = bars + 12;  // [2]
-  uint64_t* dq_done = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* dp_full = bars + 11;   // [2] indexed by tile parity (one TMEM buffer); also frees the tile's V stage
+  uint64_t* dp_free = bars + 13;   // [1] every thread holds its part of dP in registers
+  uint64_t* ds_ready = bars + 14;  // [2]
+  uint64_t* dq_done = bars + 16;   // [2] dQ of a tile has been executed: its S/dS buffer may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const AttnArgs& a = p.a;
@@ -102,12 +110,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
+    for (int i = 0; i < 3; i++) { mbar_init(&k_full[i], 1); mbar_init(&k_free[i], 1); }
     for (int i = 0; i < 2; i++) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&ds_ready[i], 8);
+      mbar_init(&v_full[i], 1); mbar_init(&s_full[i], 1); mbar_init(&dp_full[i], 1);
+      mbar_init(&ds_ready[i], 8); mbar_init(&dq_done[i], 1);
     }
-    mbar_init(dp_full, 1);
-    mbar_init(dq_done, 1);
+    mbar_init(dp_free, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -127,40 +135,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tma_load_2d(sdO, &tmdO, qdo_full, h * HD, (int)(row0 + q0));
       tma_load_2d(sdO + TILE_BYTES / 2, &tmdO, qdo_full, h * HD + 64, (int)(row0 + q0));
       for (int i = 0; i < ntile; i++) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
+        const int ks = i % 3, vs = i & 1;
         const int krow = (int)(row0 + (jlo + i) * BT);
-        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, a.status)) break;
-        mbar_expect_tx(&k_full[st], TILE_BYTES);
-        tma_load_2d(sK + st * TILE_BYTES, &tmK, &k_full[st], kvh * HD, krow);
-        tma_load_2d(sK + st * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[st], kvh * HD + 64, krow);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, a.status)) break;
-        mbar_expect_tx(&v_full[st], TILE_BYTES);
-        tma_load_2d(sV + st * TILE_BYTES, &tmV, &v_full[st], kvh * HD, krow);
-        tma_load_2d(sV + st * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[st], kvh * HD + 64, krow);
+        if (i >= 3 && !mbar_wait(&k_free[ks], ((i - 3) / 3) & 1, abort_flag, a.status)) break;
+        mbar_expect_tx(&k_full[ks], TILE_BYTES);
+        tma_load_2d(sK + ks * TILE_BYTES, &tmK, &k_full[ks], kvh * HD, krow);
+        tma_load_2d(sK + ks * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[ks], kvh * HD + 64, krow);
+        // the V stage of tile i-2 is free once its dP has been executed
+        if (i >= 2 && !mbar_wait(&dp_full[vs], ((i - 2) >> 1) & 1, abort_flag, a.status)) break;
+        mbar_expect_tx(&v_full[vs], TILE_BYTES);
+        tma_load_2d(sV + vs * TILE_BYTES, &tmV, &v_full[vs], kvh * HD, krow);
+        tma_load_2d(sV + vs * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[vs], kvh * HD + 64, krow);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // ---------------- S = Q K^T and dP = dO V^T ----------------
       constexpr uint32_t idesc_kk = idesc_bf16(BT, BT, false, false);  // both operands K-major
-      constexpr uint32_t idesc_mn = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
-      auto issue_s = [&](int i) -> bool {  // S_i = Q K_i^T
-        const int st = i & 1;
-        if (!mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag, a.status)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < HD / 16; k++) {
-          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_kk, k > 0);
-        }
-        tc_commit(&s_full[st]);
-        return true;
-      };
-      auto issue_dp = [&](int i) -> bool {  // dP_i = dO V_i^T
-        const int st = i & 1;
-        if (!mbar_wait(&v_full[st], (i >> 1) & 1, abort_flag, a.status)) return false;
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, a.status);
+      for (int i = 0; i < ntile && ok; i++) {
+        const int st = i & 1, ks = i % 3;
+        // dP first: its buffer is released early in the threads' work on tile i-1
+        if (!mbar_wait(&v_full[st], (i >> 1) & 1, abort_flag, a.status)) break;
+        if (i >= 1 && !mbar_wait(dp_free, (i - 1) & 1, abort_flag, a.status)) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
@@ -168,25 +166,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
           mma_ss(tdP, smem_desc_sw128(do_addr + off, 16, 1024), smem_desc_sw128(v_addr + off, 16, 1024), idesc_kk, k > 0);
         }
-        tc_commit(dp_full);
-        tc_commit(&v_empty[st]);
-        return true;
-      };
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, a.status);
-      if (ok) { tc_fence_after(); ok = issue_s(0) && issue_dp(0); }
-      for (int i = 0; i < ntile && ok; i++) {
-        const int st = i & 1;
-        if (i + 1 < ntile && !issue_s(i + 1)) { ok = false; break; }
-        if (!mbar_wait(&ds_ready[st], (i >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
+        tc_commit(&dp_full[st]);
+        if (!mbar_wait(&k_full[ks], (i / 3) & 1, abort_flag, a.status)) break;
+        // S(i) overwrites the buffer that held dS(i-2)
+        if (i >= 2 && !mbar_wait(&dq_done[st], ((i - 2) >> 1) & 1, abort_flag, a.status)) break;
         tc_fence_after();
-        if (i + 1 < ntile && !issue_dp(i + 1)) { ok = false; break; }
-        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(sK + ks * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < BT / 16; k++)  // dQ += dS_i K_i : 16 keys = 8 TMEM columns / 2048 B of K rows
-          mma_ts(tdQ, tS[st] + k * 8, smem_desc_sw128(k_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (i > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&k_empty[st]);
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_kk, k > 0);
+        }
+        tc_commit(&s_full[st]);
       }
-      if (ok) tc_commit(dq_done);
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      // ---------------- dQ += dS K ----------------
+      constexpr uint32_t idesc_mn = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous
+      for (int i = 0; i < ntile; i++) {
+        const int st = i & 1, ks = i % 3;
+        if (!mbar_wait(&ds_ready[st], (i >> 1) & 1, abort_flag, a.status)) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + ks * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BT / 16; k++)  // 16 keys = 8 TMEM columns / 2048 B of K rows
+          mma_ts(tdQ, tS[st] + k * 8, smem_desc_sw128(k_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (i > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&dq_done[st]);
+        tc_commit(&k_free[ks]);
+      }
     }
   } else if (warp >= 4) {
     const int quad = warp & 3;
@@ -207,22 +215,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int k0 = (jlo + i) * BT;
       // After a timed-out wait the warp keeps walking the loop (skipping the work) so that it still
       // meets its partner warp at every pair barrier.
+      if (ok && !mbar_wait(&dp_full[st], (i >> 1) & 1, abort_flag, a.status)) ok = false;
       if (ok && !mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, a.status)) ok = false;
-      if (ok && !mbar_wait(dp_full, i & 1, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
       const bool need_mask = (k0 + BT - 1 > q) || (k0 < lo);
-      // The two threads of a row each take two 32-key chunks.  dS (bf16) is written over the first 64
-      // columns of S, which the partner thread may still be reading: results are kept in registers
-      // until both have read all of S and dP (pair barrier), then stored.
+      // The two threads of a row each take two 32-key chunks.  Both chunks of dP are read first and the
+      // buffer is handed back, so the tensor core can fill it for the next tile meanwhile.  dS (bf16) is
+      // written over the first 64 columns of S, which the partner thread may still be reading: results
+      // stay in registers until both have read all of S (pair barrier), then they are stored.
+      uint32_t dr[2][32];
+      tmem_ld32(tdP + lane_off + (2 * halfsel) * 32, dr[0]);
+      tmem_ld32(tdP + lane_off + (2 * halfsel + 1) * 32, dr[1]);
       uint32_t pk[2][16];
 #pragma unroll
       for (int u = 0; u < 2; u++) {
         const int cc = 2 * halfsel + u;
-        uint32_t sr[32], dr[32];
+        uint32_t sr[32];
         tmem_ld32(tS[st] + lane_off + cc * 32, sr);
-        tmem_ld32(tdP + lane_off + cc * 32, dr);
         tmem_ld_wait();
+        if (u == 0) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dp_free);
+        }
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           float d2[2];
@@ -231,7 +247,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const int k = k0 + cc * 32 + j + e;
             float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - lse2);
             if (need_mask && !(k <= q && k >= lo)) pv = 0.f;
-            d2[e] = pv * (__uint_as_float(dr[j + e]) - Dq);
+            d2[e] = pv * (__uint_as_float(dr[u][j + e]) - Dq);
           }
           pk[u][j >> 1] = pack2(d2[0], d2[1]);
         }
@@ -244,7 +260,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_ready[st]);
     }
-    if (ok && mbar_wait(dq_done, 0, abort_flag, a.status)) {
+    const int last = ntile - 1;
+    if (ok && mbar_wait(&dq_done[last & 1], (last >> 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
       bf16* dq = reinterpret_cast<bf16*>(a.dQ) + (row0 + q) * a.dq_stride + (long long)h * HD;
 #pragma unroll
@@ -544,12 +561,12 @@ int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
   FEMTO_TRY(make_tmap_2d_bf16(&tmdO, a.dO, (uint64_t)a.H * HD, N, a.do_stride, 64, BT));
   static bool attr_done = false;
   if (!attr_done) {
-    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
+    CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
     attr_done = true;
   }
   dim3 gq(a.T / BT, a.H, a.B);
-  attn_bwd_dq_kernel<<<gq, 384, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  attn_bwd_dq_kernel<<<gq, 384, DQ_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
   KERNEL_CHECK();
   dim3 gk(a.T / BT, a.Hkv, a.B);
   attn_bwd_dkv_kernel<<<gk, 384, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
