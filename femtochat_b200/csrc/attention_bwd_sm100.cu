@@ -56,9 +56,9 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D
 
 // ------------------------------------------------------------------------------------------------
 // dQ kernel.  Roles: warp 0 streams K (three stages: a K tile is held until dQ has used it) and V
-// (two stages) with TMA; warp 1 issues S = Q K^T and dP = dO V^T, warp 2 issues dQ += dS K (issue
-// of tcgen05.mma blocks while the pipe is busy, so two issuers keep it fed while one of them waits
-// on a barrier); warps 4-11 own the query rows.  S is double-buffered in TMEM; dP has one buffer,
+// (two stages) with TMA; warps 1, 3 and 2 issue dP = dO V^T, S = Q K^T and dQ += dS K (issue of
+// tcgen05.mma blocks while the pipe is busy, so one issuer per product keeps it fed while another
+// waits on a barrier); warps 4-11 own the query rows.  S is double-buffered in TMEM; dP has one buffer,
 // which the threads release as soon as they hold its values in registers, so dP of the next tile
 // is computed while they work on the current one.
 // ------------------------------------------------------------------------------------------------
@@ -150,14 +150,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // ---------------- S = Q K^T and dP = dO V^T ----------------
+      // ---------------- dP = dO V^T ----------------
       constexpr uint32_t idesc_kk = idesc_bf16(BT, BT, false, false);  // both operands K-major
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+      const uint32_t do_addr = smem_u32(sdO);
       bool ok = mbar_wait(qdo_full, 0, abort_flag, a.status);
       for (int i = 0; i < ntile && ok; i++) {
-        const int st = i & 1, ks = i % 3;
-        // dP first: its buffer is released early in the threads' work on tile i-1
+        const int st = i & 1;
         if (!mbar_wait(&v_full[st], (i >> 1) & 1, abort_flag, a.status)) break;
+        // the single dP buffer is released early in the threads' work on tile i-1
         if (i >= 1 && !mbar_wait(dp_free, (i - 1) & 1, abort_flag, a.status)) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
@@ -167,6 +167,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           mma_ss(tdP, smem_desc_sw128(do_addr + off, 16, 1024), smem_desc_sw128(v_addr + off, 16, 1024), idesc_kk, k > 0);
         }
         tc_commit(&dp_full[st]);
+      }
+    }
+  } else if (warp == 3) {
+    if (lane == 0) {
+      // ---------------- S = Q K^T ----------------
+      constexpr uint32_t idesc_kk = idesc_bf16(BT, BT, false, false);
+      const uint32_t q_addr = smem_u32(sQ);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, a.status);
+      for (int i = 0; i < ntile && ok; i++) {
+        const int st = i & 1, ks = i % 3;
         if (!mbar_wait(&k_full[ks], (i / 3) & 1, abort_flag, a.status)) break;
         // S(i) overwrites the buffer that held dS(i-2)
         if (i >= 2 && !mbar_wait(&dq_done[st], ((i - 2) >> 1) & 1, abort_flag, a.status)) break;
