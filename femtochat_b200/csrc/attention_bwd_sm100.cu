@@ -19,7 +19,7 @@ namespace {
 
 constexpr int HD = 128, BT = 128;
 constexpr int TILE_BYTES = BT * HD * 2;  // two [128][64] swizzled slabs
-constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 3 * 128 * 4;
+constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 3 * 128 * 4 + 64;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -297,9 +297,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
-// dK / dV kernel.  S^T and dP^T of a query tile are computed with full 128-wide instructions; the
-// threads then convert the tile in two halves of 64 queries, so dV / dK of the first half run on the
-// tensor core while the second half is being converted.
+// dK / dV kernel.  A query tile is processed as two halves of 64 queries so that the S^T / dP^T
+// buffers in TMEM (64 columns each) can be double-buffered next to the two 128-column accumulators:
+// the tensor core computes the inputs of half h+1 and the dV / dK update of half h-1 while the
+// threads turn half h into P^T and dS^T.  Warps 1 and 3 issue S^T = K Q^T and dP^T = V dO^T, warp 2
+// issues dV += P^T dO and dK += dS^T Q (one issuer per product: tcgen05.mma issue blocks while the
+// pipe is busy, so the barrier waits of one issuer overlap the issue of another).
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(384, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -315,12 +318,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;   // [2]
   uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* st_full = bars + 5;    // [2] S^T and dP^T of a half are in TMEM
-  uint64_t* pds_ready = bars + 7;  // [2] P^T and dS^T of a half are written
-  uint64_t* acc_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* s_full = bars + 5;     // [2] S^T of a half is in TMEM
+  uint64_t* dp_full = bars + 7;    // [2] dP^T of a half is in TMEM
+  uint64_t* pds_ready = bars + 9;  // [2] P^T and dS^T of a half are written
+  uint64_t* out_done = bars + 11;  // [2] dV / dK of a half have been accumulated: its buffers may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2][3][128]: lse2, D, lo
+  int* lomax = reinterpret_cast<int*>(stats + 2 * 384);                    // [2][4]: largest lower bound of each 32 queries
 
   const AttnArgs& a = p.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -362,9 +367,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; i++) {
       mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
-      mbar_init(&st_full[i], 1); mbar_init(&pds_ready[i], 8);
+      mbar_init(&s_full[i], 1); mbar_init(&dp_full[i], 1); mbar_init(&pds_ready[i], 8); mbar_init(&out_done[i], 1);
     }
-    mbar_init(acc_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -396,54 +400,47 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_2d(sdO + st * TILE_BYTES + TILE_BYTES / 2, &tmdO, &qdo_full[st], h * HD + 64, qrow);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 3) {
     if (lane == 0) {
-      constexpr uint32_t idesc_in = idesc_bf16(BT, BT, false, false);   // [128 keys] x [128 queries], K = head_dim
-      constexpr uint32_t idesc_out = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous, K = 64 queries
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      // S^T = K Q^T and dP^T = V dO^T for a whole query tile (128-wide instructions run at full rate;
-      // 64-wide ones cost the same per instruction)
-      auto issue_in = [&](int it) -> bool {
-        const int st = it & 1;
-        if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) return false;
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES), do_addr = smem_u32(sdO + st * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < HD / 16; k++) {
-          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tS[0], smem_desc_sw128(k_addr + off, 16, 1024), smem_desc_sw128(q_addr + off, 16, 1024), idesc_in, k > 0);
-        }
-#pragma unroll
-        for (int k = 0; k < HD / 16; k++) {
-          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
-          mma_ss(tdP[0], smem_desc_sw128(v_addr + off, 16, 1024), smem_desc_sw128(do_addr + off, 16, 1024), idesc_in, k > 0);
-        }
-        tc_commit(&st_full[0]);
-        return true;
-      };
+      // ---------------- S^T = K Q^T (warp 1) / dP^T = V dO^T (warp 3), 64 queries at a time ----------------
+      constexpr uint32_t idesc_in = idesc_bf16(BT, 64, false, false);   // [128 keys] x [64 queries], K = head_dim
+      const bool is_s = warp == 1;
+      const uint32_t a_addr = smem_u32(is_s ? sK : sV);
       bool ok = mbar_wait(kv_full, 0, abort_flag, a.status);
-      if (ok) { tc_fence_after(); ok = issue_in(0); }
-      for (int it = 0; it < nit && ok; it++) {
-        const int st = it & 1;
-        const uint32_t q_base = smem_u32(sQ + st * TILE_BYTES), do_base = smem_u32(sdO + st * TILE_BYTES);
-        for (int hf = 0; hf < 2 && ok; hf++) {
-          // the threads finish the first 64 queries of the tile first, so dV/dK of that half run
-          // on the tensor core while they work on the second half
-          if (!mbar_wait(&pds_ready[hf], it & 1, abort_flag, a.status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t q_addr = q_base + hf * 8192, do_addr = do_base + hf * 8192;
+      for (int h2 = 0; h2 < n2 && ok; h2++) {
+        const int it = h2 >> 1, hf = h2 & 1, st = it & 1, bf = h2 & 1;
+        if (hf == 0 && !mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag, a.status)) break;
+        // the buffer still holds P^T / dS^T of half h2-2 until its dV / dK update has been executed
+        if (h2 >= 2 && !mbar_wait(&out_done[bf], ((h2 - 2) >> 1) & 1, abort_flag, a.status)) break;
+        tc_fence_after();
+        const uint32_t b_addr = smem_u32((is_s ? sQ : sdO) + st * TILE_BYTES) + hf * 8192;
+        const uint32_t d_tmem = is_s ? tS[bf] : tdP[bf];
 #pragma unroll
-          for (int k = 0; k < 4; k++)  // dV += P^T dO over 64 queries
-            mma_ts(tdV, tS[hf] + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (it > 0 || hf > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-          for (int k = 0; k < 4; k++)  // dK += dS^T Q
-            mma_ts(tdK, tdP[hf] + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (it > 0 || hf > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+          mma_ss(d_tmem, smem_desc_sw128(a_addr + off, 16, 1024), smem_desc_sw128(b_addr + off, 16, 1024), idesc_in, k > 0);
         }
-        if (!ok) break;
-        tc_commit(&qdo_empty[st]);
-        if (it + 1 < nit && !issue_in(it + 1)) { ok = false; break; }
+        tc_commit(is_s ? &s_full[bf] : &dp_full[bf]);
       }
-      if (ok) tc_commit(acc_done);
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      // ---------------- dV += P^T dO, dK += dS^T Q over 64 queries ----------------
+      constexpr uint32_t idesc_out = idesc_bf16(BT, HD, false, true);   // A from TMEM, B N-contiguous, K = 64 queries
+      for (int h2 = 0; h2 < n2; h2++) {
+        const int it = h2 >> 1, hf = h2 & 1, st = it & 1, bf = h2 & 1;
+        if (!mbar_wait(&pds_ready[bf], (h2 >> 1) & 1, abort_flag, a.status)) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES) + hf * 8192, do_addr = smem_u32(sdO + st * TILE_BYTES) + hf * 8192;
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+          mma_ts(tdV, tS[bf] + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+          mma_ts(tdK, tdP[bf] + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&out_done[bf]);
+        if (hf == 1) tc_commit(&qdo_empty[st]);
+      }
     }
   } else if (warp >= 4) {
     const int quad = warp & 3;
@@ -474,38 +471,62 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (hf == 0) {
         if (halfsel == 0) {
           sl[r] = n_lse; sl[128 + r] = n_D; sl[256 + r] = __int_as_float(n_lo);
+          const int wmax = __reduce_max_sync(0xffffffffu, n_lo);
+          if (lane == 0) lomax[(it & 1) * 4 + quad] = wmax;   // queries 32*quad .. 32*quad+31 of the tile
           if (it + 1 < nit) fetch_stats(it + 1);
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      if (ok && hf == 0 && !mbar_wait(&st_full[0], it & 1, abort_flag, a.status)) ok = false;
+      if (ok && !mbar_wait(&s_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
+      if (ok && !mbar_wait(&dp_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
       uint32_t pp[16], pd[16];   // kept in registers until the partner thread has read S^T / dP^T
       {
         const int cq = hf * 64 + halfsel * 32;   // first query (within the tile) of this thread's chunk
+        const int qf = qi0 + halfsel * 32;       // its position in the sequence
         uint32_t sr[32], dr[32];
         tmem_ld32(tS[bf] + lane_off + halfsel * 32, sr);
         tmem_ld32(tdP[bf] + lane_off + halfsel * 32, dr);
+        // the mask matters only when some key of this warp is above the chunk's first query (causal edge)
+        // or below the largest lower bound of its 32 queries (window / document edge)
+        const bool need_mask = __any_sync(0xffffffffu, key > qf || key < lomax[(it & 1) * 4 + (cq >> 5)]);
         tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(sl + cq + j);
-          const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cq + j);
-          const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cq + j);
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-          const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
-          float p4[4], s4[4];
+          for (int j = 0; j < 32; j += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(sl + cq + j);
+            const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cq + j);
+            const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cq + j);
+            const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+            const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
+            float p4[4], s4[4];
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int q = qi0 + halfsel * 32 + j + e;
-            float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - ls[e]);
-            if (!(key <= q && key >= los[e])) pv = 0.f;
-            p4[e] = pv;
-            s4[e] = pv * (__uint_as_float(dr[j + e]) - dd[e]);
+            for (int e = 0; e < 4; e++) {
+              const int q = qf + j + e;
+              float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - ls[e]);
+              if (!(key <= q && key >= los[e])) pv = 0.f;
+              p4[e] = pv;
+              s4[e] = pv * (__uint_as_float(dr[j + e]) - dd[e]);
+            }
+            pp[j >> 1] = pack2(p4[0], p4[1]); pp[(j >> 1) + 1] = pack2(p4[2], p4[3]);
+            pd[j >> 1] = pack2(s4[0], s4[1]); pd[(j >> 1) + 1] = pack2(s4[2], s4[3]);
           }
-          pp[j >> 1] = pack2(p4[0], p4[1]); pp[(j >> 1) + 1] = pack2(p4[2], p4[3]);
-          pd[j >> 1] = pack2(s4[0], s4[1]); pd[(j >> 1) + 1] = pack2(s4[2], s4[3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(sl + cq + j);
+            const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cq + j);
+            const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+            float p4[4], s4[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              p4[e] = fast_exp2(__uint_as_float(sr[j + e]) * c - ls[e]);
+              s4[e] = p4[e] * (__uint_as_float(dr[j + e]) - dd[e]);
+            }
+            pp[j >> 1] = pack2(p4[0], p4[1]); pp[(j >> 1) + 1] = pack2(p4[2], p4[3]);
+            pd[j >> 1] = pack2(s4[0], s4[1]); pd[(j >> 1) + 1] = pack2(s4[2], s4[3]);
+          }
         }
       }
       asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
@@ -514,9 +535,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&pds_ready[bf]);   // bf == half index: one phase per query tile
+      if (lane == 0) mbar_arrive(&pds_ready[bf]);
     }
-    if (ok && mbar_wait(acc_done, 0, abort_flag, a.status)) {
+    const int lasth = n2 - 1;   // the dV / dK issuer's last commit covers every earlier instruction
+    if (ok && mbar_wait(&out_done[lasth & 1], (lasth >> 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
       bf16* dk = reinterpret_cast<bf16*>(a.dK) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
       bf16* dv = reinterpret_cast<bf16*>(a.dV) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
