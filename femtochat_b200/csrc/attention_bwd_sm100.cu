@@ -19,12 +19,13 @@ namespace {
 
 constexpr int HD = 128, BT = 128;
 constexpr int TILE_BYTES = BT * HD * 2;  // two [128][64] swizzled slabs
-constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 3 * 128 * 4 + 64;
+constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 2 * 128 * 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
   AttnArgs a;
-  const float* D;  // [B][H][T] rowsum(dO*O)
+  const float* D;   // [B][H][T] rowsum(dO*O)
+  const float* L2;  // [B][H][T] lse * log2(e)
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -32,8 +33,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// D[b][h][t] = sum_d dO*O: 16 lanes per (token, head) slice of 128 channels, 16-byte loads.
-__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D) {
+// D[b][h][t] = sum_d dO*O and L2 = lse * log2(e): 16 lanes per (token, head) slice of 128 channels, 16-byte loads.
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D, float* L2) {
   const long long total = (long long)a.B * a.T * a.H;
   const long long w0 = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
   const long long w = w0 < total ? w0 : total - 1;   // surplus half-warps recompute the last slice
@@ -51,7 +52,11 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D
 #pragma unroll
   for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   const int b = (int)(row / a.T), t = (int)(row % a.T);
-  if (sub == 0 && w0 < total) D[((long long)b * a.H + h) * a.T + t] = acc;
+  if (sub == 0 && w0 < total) {
+    const long long si = ((long long)b * a.H + h) * a.T + t;
+    D[si] = acc;
+    L2[si] = a.lse[si] * LOG2E;   // the exponent's offset in base 2, so P = exp2(S c - L2) is one FMA + ex2
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -217,7 +222,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     int lo = max(0, q - a.window_left);
     if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
     const long long si = ((long long)b * a.H + h) * a.T + q;
-    const float lse2 = a.lse[si] * LOG2E;
+    const float lse2 = p.L2[si];
     const float Dq = p.D[si];
     bool ok = true;
     for (int i = 0; i < ntile; i++) {
@@ -324,8 +329,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* out_done = bars + 11;  // [2] dV / dK of a half have been accumulated: its buffers may be overwritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2][3][128]: lse2, D, lo
-  int* lomax = reinterpret_cast<int*>(stats + 2 * 384);                    // [2][4]: largest lower bound of each 32 queries
+  float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2 stages][2][128]: lse * log2(e) and D of the tile's queries
 
   const AttnArgs& a = p.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -339,6 +343,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // compact list of the visible ones (document starts need not be monotone for arbitrary positions)
   __shared__ int s_qlist[64];
   __shared__ int s_tmin[64];
+  __shared__ int s_dsmax[64][4];   // per candidate tile: largest document start of each 32 queries
   __shared__ int s_nq;
   {
     const int cand = ihi - ilo + 1;
@@ -347,7 +352,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int base = (ilo + c) * BT + (threadIdx.x & 31) * 4;
         const int4 v = *reinterpret_cast<const int4*>(a.doc_start + row0 + base);
         const int m = __reduce_min_sync(0xffffffffu, min(min(v.x, v.y), min(v.z, v.w)));
+        int mx = max(max(v.x, v.y), max(v.z, v.w));   // 8 lanes hold 32 consecutive queries
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
         if ((threadIdx.x & 31) == 0) s_tmin[c] = m;
+        if ((threadIdx.x & 7) == 0) s_dsmax[c][(threadIdx.x & 31) >> 3] = mx;
       }
       __syncthreads();
     }
@@ -393,7 +403,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int h = kvh * g + it / nq;
         const int qrow = (int)(row0 + s_qlist[it % nq] * BT);
         if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, a.status)) break;
-        mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES);
+        mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES + 1024);
+        const long long srow = ((long long)b * a.H + h) * a.T + s_qlist[it % nq] * BT;
+        bulk_load_1d(stats + st * 256, p.L2 + srow, 512, &qdo_full[st]);
+        bulk_load_1d(stats + st * 256 + 128, p.D + srow, 512, &qdo_full[st]);
         tma_load_2d(sQ + st * TILE_BYTES, &tmQ, &qdo_full[st], h * HD, qrow);
         tma_load_2d(sQ + st * TILE_BYTES + TILE_BYTES / 2, &tmQ, &qdo_full[st], h * HD + 64, qrow);
         tma_load_2d(sdO + st * TILE_BYTES, &tmdO, &qdo_full[st], h * HD, qrow);
@@ -451,32 +464,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float scale = rsqrtf((float)HD);
     const float c = scale * LOG2E;
     bool ok = true;
-    // statistics of the queries of a tile (one per thread of warps 4-7), fetched one tile ahead
-    float n_lse = 0.f, n_D = 0.f;
-    int n_lo = 0;
-    auto fetch_stats = [&](int it) {
-      const int h = kvh * g + it / nq;
-      const int q = s_qlist[it % nq] * BT + r;
-      const long long si = ((long long)b * a.H + h) * a.T + q;
-      n_lse = a.lse[si] * LOG2E;
-      n_D = p.D[si];
-      n_lo = max(0, q - a.window_left);
-      if (a.doc_start) n_lo = max(n_lo, a.doc_start[row0 + q]);
-    };
-    if (halfsel == 0) fetch_stats(0);
     for (int h2 = 0; h2 < n2; h2++) {
       const int it = h2 >> 1, hf = h2 & 1, bf = h2 & 1;
       const int qi0 = s_qlist[it % nq] * BT + hf * 64;
-      float* sl = stats + (it & 1) * 384;
-      if (hf == 0) {
-        if (halfsel == 0) {
-          sl[r] = n_lse; sl[128 + r] = n_D; sl[256 + r] = __int_as_float(n_lo);
-          const int wmax = __reduce_max_sync(0xffffffffu, n_lo);
-          if (lane == 0) lomax[(it & 1) * 4 + quad] = wmax;   // queries 32*quad .. 32*quad+31 of the tile
-          if (it + 1 < nit) fetch_stats(it + 1);
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-      }
+      const float* sl = stats + (it & 1) * 256;
+      const int qtile = s_qlist[it % nq];
+      // the tile's statistics rows arrive with its Q / dO (already complete here: S^T was computed from them)
+      if (ok && hf == 0 && !mbar_wait(&qdo_full[it & 1], (it >> 1) & 1, abort_flag, a.status)) ok = false;
       if (ok && !mbar_wait(&s_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
       if (ok && !mbar_wait(&dp_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
@@ -490,22 +484,26 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(tdP[bf] + lane_off + halfsel * 32, dr);
         // the mask matters only when some key of this warp is above the chunk's first query (causal edge)
         // or below the largest lower bound of its 32 queries (window / document edge)
-        const bool need_mask = __any_sync(0xffffffffu, key > qf || key < lomax[(it & 1) * 4 + (cq >> 5)]);
+        const int lo_max = max(max(0, qf + 31 - a.window_left), a.doc_start ? s_dsmax[qtile - ilo][cq >> 5] : 0);
+        const bool need_mask = __any_sync(0xffffffffu, key > qf || key < lo_max);
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             const float4 l4 = *reinterpret_cast<const float4*>(sl + cq + j);
             const float4 d4 = *reinterpret_cast<const float4*>(sl + 128 + cq + j);
-            const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cq + j);
             const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-            const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
+            int los[4] = {0, 0, 0, 0};
+            if (a.doc_start) {
+              const int4 lo4 = *reinterpret_cast<const int4*>(a.doc_start + row0 + qf + j);
+              los[0] = lo4.x; los[1] = lo4.y; los[2] = lo4.z; los[3] = lo4.w;
+            }
             float p4[4], s4[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const int q = qf + j + e;
               float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - ls[e]);
-              if (!(key <= q && key >= los[e])) pv = 0.f;
+              if (!(key <= q && key >= max(los[e], q - a.window_left))) pv = 0.f;
               p4[e] = pv;
               s4[e] = pv * (__uint_as_float(dr[j + e]) - dd[e]);
             }
@@ -571,7 +569,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 }  // namespace
 
-size_t attention_bwd_tc_ws_bytes(int B, int T, int H, int) { return sizeof(float) * (size_t)B * H * T; }
+size_t attention_bwd_tc_ws_bytes(int B, int T, int H, int) { return 2 * sizeof(float) * (size_t)B * H * T; }
 
 int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
   if (!attention_tc_supported(a)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "attention_bwd_tc: unsupported shape");
@@ -584,7 +582,8 @@ int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
   BwdParams p;
   p.a = a;
   p.D = reinterpret_cast<const float*>(a.ws);
-  attn_bwd_prep_kernel<<<cdiv(N * a.H, 16), 256, 0, s>>>(a, reinterpret_cast<float*>(a.ws));
+  p.L2 = p.D + (size_t)a.B * a.H * a.T;
+  attn_bwd_prep_kernel<<<cdiv(N * a.H, 16), 256, 0, s>>>(a, reinterpret_cast<float*>(a.ws), reinterpret_cast<float*>(a.ws) + (size_t)a.B * a.H * a.T);
   KERNEL_CHECK();
   CUtensorMap tmQ, tmK, tmV, tmdO;
   FEMTO_TRY(make_tmap_2d_bf16(&tmQ, a.Q, (uint64_t)a.H * HD, N, a.q_stride, 64, BT));

@@ -1,16 +1,16 @@
 // Attention reverse pass for callers that must not allocate device memory.
 //
-// femto_attention_bwd takes its scratch (the per-row term D = rowsum(dO * O), one float per
-// (batch, head, query)) from cudaMalloc on every call.  Some callers cannot do that: a host runtime
+// femto_attention_bwd takes its scratch (the per-row terms D = rowsum(dO * O) and lse * log2(e), two
+// floats per (batch, head, query)) from cudaMalloc on every call.  Some callers cannot do that: a host runtime
 // that has handed all device memory to its own pool (XLA-style allocators, a Julia session with a
 // capped CUDA.jl pool), or code that runs while allocation is forbidden or would synchronise the
 // device.  For them the scratch below is compiled into the library image: every GPU that loads the
-// library holds these 4 MiB until the process exits, and the entry point never allocates or frees.
+// library holds these 8 MiB until the process exits, and the entry point never allocates or frees.
 #include "common.cuh"
 
 namespace {
 
-constexpr long long STATIC_SCRATCH_FLOATS = 1ll << 20;  // B*H*T <= 1 048 576 (e.g. 32 x 16 x 2048)
+constexpr long long STATIC_SCRATCH_FLOATS = 2ll << 20;  // two floats per row: B*H*T <= 1 048 576 (e.g. 32 x 16 x 2048)
 static __device__ __align__(256) float g_attn_bwd_scratch[STATIC_SCRATCH_FLOATS];
 
 constexpr int MAX_DEVICES = 64;
@@ -40,11 +40,11 @@ extern "C" int32_t femto_attention_bwd_static(int32_t dtype, void* dQ, void* dK,
   if (!dQ || !dK || !dV || !dO || !Q || !K || !V || !O || !lse) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   if (B <= 0 || T <= 0 || H <= 0 || Hkv <= 0 || hd <= 0 || H % Hkv != 0) return femto_fail(FEMTO_ERR_SHAPE, "bad attention shape");
   if (dtype != FEMTO_F32 && dtype != FEMTO_BF16) return femto_fail(FEMTO_ERR_ARG, "dtype must be FEMTO_F32 or FEMTO_BF16");
-  const long long need = (long long)B * H * T;
+  const long long need = 2ll * B * H * T;
   if (need > STATIC_SCRATCH_FLOATS)
     return femto_fail(FEMTO_ERR_SHAPE,
-                      "femto_attention_bwd_static: B*H*T = %lld exceeds the built-in scratch of %lld floats; "
-                      "use femto_attention_bwd, which allocates", need, STATIC_SCRATCH_FLOATS);
+                      "femto_attention_bwd_static: B*H*T = %lld exceeds the built-in scratch of %lld rows; "
+                      "use femto_attention_bwd, which allocates", need / 2, STATIC_SCRATCH_FLOATS / 2);
   float* scratch = nullptr;
   FEMTO_TRY(scratch_for_current_device(&scratch));
   AttnArgs a;
@@ -54,7 +54,7 @@ extern "C" int32_t femto_attention_bwd_static(int32_t dtype, void* dQ, void* dK,
   a.window_left = window_left < 0 ? T : window_left; a.doc_start = doc_start;
   a.lse = const_cast<float*>(lse); a.dO = dO; a.dQ = dQ; a.dK = dK; a.dV = dV;
   a.do_stride = a.q_stride; a.dq_stride = a.q_stride; a.dkv_stride = a.kv_stride;
-  // Every element of D that the kernels read is written first by the same call, so nothing in
+  // Every element of the scratch that the kernels read is written first by the same call, so nothing in
   // the shared array needs clearing between calls.
   a.ws = scratch; a.ws_bytes = sizeof(float) * (size_t)STATIC_SCRATCH_FLOATS;
   return dtype == FEMTO_BF16 ? attention_bwd<bf16>(a, (cudaStream_t)stream) : attention_bwd<float>(a, (cudaStream_t)stream);

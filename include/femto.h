@@ -161,8 +161,8 @@ int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const v
                             const int32_t* doc_start, void* stream);
 /* Same computation as femto_attention_bwd for callers that cannot allocate device memory (a host
  * runtime that owns the whole device pool, or a phase in which cudaMalloc is forbidden or would
- * stall the device).  No counterpart in the reference.  The scratch (one float per (batch, head,
- * query)) lives in a 4 MiB array compiled into the library, so the call is limited to
+ * stall the device).  No counterpart in the reference.  The scratch (two floats per (batch, head,
+ * query)) lives in an 8 MiB array compiled into the library, so the call is limited to
  * B*H*T <= 1 048 576 and fails with FEMTO_ERR_SHAPE beyond that; it never calls cudaMalloc/cudaFree.
  * The first call on a device looks up the array's device address (make that call before any stream
  * capture).  All calls on a device share the array: calls that overlap on the GPU (different
