@@ -19,7 +19,7 @@ namespace {
 
 constexpr int HD = 128, BT = 128;
 constexpr int TILE_BYTES = BT * HD * 2;  // two [128][64] swizzled slabs
-constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 2 * 128 * 4;
+constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256 + 2 * 3 * 128 * 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -329,7 +329,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* out_done = bars + 11;  // [2] dV / dK of a half have been accumulated: its buffers may be overwritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2 stages][2][128]: lse * log2(e) and D of the tile's queries
+  float* stats = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2 stages][3][128]: lse * log2(e), D and document start of the tile's queries
 
   const AttnArgs& a = p.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -403,10 +403,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int h = kvh * g + it / nq;
         const int qrow = (int)(row0 + s_qlist[it % nq] * BT);
         if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, a.status)) break;
-        mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES + 1024);
+        mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES + 1024 + (a.doc_start ? 512 : 0));
         const long long srow = ((long long)b * a.H + h) * a.T + s_qlist[it % nq] * BT;
-        bulk_load_1d(stats + st * 256, p.L2 + srow, 512, &qdo_full[st]);
-        bulk_load_1d(stats + st * 256 + 128, p.D + srow, 512, &qdo_full[st]);
+        bulk_load_1d(stats + st * 384, p.L2 + srow, 512, &qdo_full[st]);
+        bulk_load_1d(stats + st * 384 + 128, p.D + srow, 512, &qdo_full[st]);
+        if (a.doc_start) bulk_load_1d(stats + st * 384 + 256, a.doc_start + qrow, 512, &qdo_full[st]);
         tma_load_2d(sQ + st * TILE_BYTES, &tmQ, &qdo_full[st], h * HD, qrow);
         tma_load_2d(sQ + st * TILE_BYTES + TILE_BYTES / 2, &tmQ, &qdo_full[st], h * HD + 64, qrow);
         tma_load_2d(sdO + st * TILE_BYTES, &tmdO, &qdo_full[st], h * HD, qrow);
@@ -467,7 +468,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int h2 = 0; h2 < n2; h2++) {
       const int it = h2 >> 1, hf = h2 & 1, bf = h2 & 1;
       const int qi0 = s_qlist[it % nq] * BT + hf * 64;
-      const float* sl = stats + (it & 1) * 256;
+      const float* sl = stats + (it & 1) * 384;
       const int qtile = s_qlist[it % nq];
       // the tile's statistics rows arrive with its Q / dO (already complete here: S^T was computed from them)
       if (ok && hf == 0 && !mbar_wait(&qdo_full[it & 1], (it >> 1) & 1, abort_flag, a.status)) ok = false;
@@ -495,7 +496,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
             int los[4] = {0, 0, 0, 0};
             if (a.doc_start) {
-              const int4 lo4 = *reinterpret_cast<const int4*>(a.doc_start + row0 + qf + j);
+              const int4 lo4 = *reinterpret_cast<const int4*>(sl + 256 + cq + j);
               los[0] = lo4.x; los[1] = lo4.y; los[2] = lo4.z; los[3] = lo4.w;
             }
             float p4[4], s4[4];
