@@ -234,7 +234,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok && !mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, a.status)) ok = false;
       if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
       tc_fence_after();
-      const bool need_mask = (k0 + BT - 1 > q) || (k0 < lo);
+      const bool any_mask = __any_sync(0xffffffffu, (k0 + BT - 1 > q) || (k0 < lo));
       // The two threads of a row each take two 32-key chunks.  Both chunks of dP are read first and the
       // buffer is handed back, so the tensor core can fill it for the next tile meanwhile.  dS (bf16) is
       // written over the first 64 columns of S, which the partner thread may still be reading: results
@@ -254,17 +254,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           __syncwarp();
           if (lane == 0) mbar_arrive(dp_free);
         }
+        if (any_mask) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float d2[2];
+          for (int j = 0; j < 32; j += 2) {
+            float d2[2];
 #pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const int k = k0 + cc * 32 + j + e;
-            float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - lse2);
-            if (need_mask && !(k <= q && k >= lo)) pv = 0.f;
-            d2[e] = pv * (__uint_as_float(dr[u][j + e]) - Dq);
+            for (int e = 0; e < 2; e++) {
+              const int k = k0 + cc * 32 + j + e;
+              float pv = fast_exp2(__uint_as_float(sr[j + e]) * c - lse2);
+              if (!(k <= q && k >= lo)) pv = 0.f;
+              d2[e] = pv * (__uint_as_float(dr[u][j + e]) - Dq);
+            }
+            pk[u][j >> 1] = pack2(d2[0], d2[1]);
           }
-          pk[u][j >> 1] = pack2(d2[0], d2[1]);
+        } else {   // no mask edge crosses this warp's rows in this tile: the common case, without the compares
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = fast_exp2(__uint_as_float(sr[j]) * c - lse2), p1 = fast_exp2(__uint_as_float(sr[j + 1]) * c - lse2);
+            pk[u][j >> 1] = pack2(p0 * (__uint_as_float(dr[u][j]) - Dq), p1 * (__uint_as_float(dr[u][j + 1]) - Dq));
+          }
         }
       }
       asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
