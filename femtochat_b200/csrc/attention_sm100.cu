@@ -21,8 +21,11 @@ using namespace sm100;
 namespace {
 
 constexpr int HD = 128, BQ = 128, BKV = 128;
+constexpr int NS = 2;              // threads per query row in the forward softmax (4 measured slower: 583 vs 620 TFLOP/s)
+constexpr int CW = BKV / NS;       // keys of a tile per thread
+constexpr int FWD_THREADS = 128 + NS * 128;
 constexpr int TILE_BYTES = BQ * HD * 2;  // 32 KB: two [128][64] swizzled slabs
-constexpr int FWD_SMEM = TILE_BYTES * 5 + 1024 + 256 + 3 * 1024;
+constexpr int FWD_SMEM = TILE_BYTES * 5 + 1024 + 256 + 3 * NS * 128 * 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct FwdParams {
@@ -35,7 +38,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -52,8 +55,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* pv_done = bars + 9;   // [2] P V of a tile has been accumulated; also frees its V stage and its S/P buffer
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xmax = reinterpret_cast<float*>(smem + 5 * TILE_BYTES + 256);  // [2 parities][2 halves][128 rows]
-  float* xl = xmax + 512;                                               // [2 halves][128 rows]
+  float* xmax = reinterpret_cast<float*>(smem + 5 * TILE_BYTES + 256);  // [2 parities][NS][128 rows]
+  float* xl = xmax + 2 * NS * 128;                                      // [NS][128 rows]
 
   const AttnArgs& a = p.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -81,7 +84,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; i++) {
       mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8); mbar_init(&pv_done[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], NS * 4); mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -160,9 +163,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else if (warp >= 4) {
-    // ---------------- softmax: two threads per query row, each owns 64 of the 128 keys of a tile ----------------
+    // ---------------- softmax: NS threads per query row, each owns CW = 128 / NS of the keys of a tile ----------------
     const int quad = warp & 3;
-    const int hs = (warp - 4) >> 2;        // 0: keys 0..63 of each tile, 1: keys 64..127
+    const int hs = (warp - 4) >> 2;        // which CW keys of each tile
     const int r = quad * 32 + lane;
     const int q = q0 + r;
     const bool row_ok = q < a.T;
@@ -170,43 +173,45 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float c = rsqrtf((float)HD) * LOG2E;
     int lo = max(0, q - a.window_left);
     if (a.doc_start && row_ok) lo = max(lo, a.doc_start[row0 + q]);
-    float m_used = -INFINITY, l = 0.f;   // l: this thread's share of the row sum (same m_used in both threads)
+    float m_used = -INFINITY, l = 0.f;   // l: this thread's share of the row sum (same m_used in all threads of a row)
     bool ok = true;
     for (int i = 0; i < ntile; i++) {
       const int st = i & 1;
       const uint32_t ph = (i >> 1) & 1;
-      const int k0 = (jlo + i) * BKV + hs * 64;
+      const int k0 = (jlo + i) * BKV + hs * CW;
       // After a timed-out wait the warp keeps walking the loop (skipping the work) so that it still
-      // meets its partner warp at every pair barrier.
+      // meets its partner warps at every row barrier.
       if (ok && !mbar_wait(&s_full[st], ph, abort_flag, a.status)) ok = false;
-      if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
+      if (!ok) { asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory"); continue; }
       tc_fence_after();
       // x holds the raw scores; the 1/sqrt(hd) * log2(e) factor is folded into the exponent's FMA.
       // Maxima and sums use four independent accumulators so the chains do not serialise.
-      float x[64];
-      tmem_ld32(tS[st] + lane_off + (2 * hs) * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
-      tmem_ld32(tS[st] + lane_off + (2 * hs + 1) * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+      float x[CW];
+#pragma unroll
+      for (int u = 0; u < CW / 32; u++)
+        tmem_ld32(tS[st] + lane_off + hs * CW + u * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[u * 32]));
       tmem_ld_wait();
-      const bool need_mask = (k0 + 63 > q) || (k0 < lo);
+      const bool need_mask = (k0 + CW - 1 > q) || (k0 < lo);
       if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < 64; j++) {
+        for (int j = 0; j < CW; j++) {
           const int k = k0 + j;
           x[j] = (k <= q && k >= lo) ? x[j] : -INFINITY;
         }
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < 64; j += 4) {
+      for (int j = 0; j < CW; j += 4) {
         mx[0] = fmaxf(mx[0], x[j]); mx[1] = fmaxf(mx[1], x[j + 1]);
         mx[2] = fmaxf(mx[2], x[j + 2]); mx[3] = fmaxf(mx[3], x[j + 3]);
       }
       float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;   // scaled units (c > 0 keeps the argmax)
-      // combine the two half-row maxima; after this barrier both threads hold all of S in registers,
-      // so P may overwrite S in TMEM
-      xmax[(i & 1) * 256 + hs * 128 + r] = mt;
-      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
-      mt = fmaxf(mt, xmax[(i & 1) * 256 + (hs ^ 1) * 128 + r]);
+      // combine the partial row maxima; after this barrier every thread of the row holds its part of S in
+      // registers, so P may overwrite S in TMEM
+      xmax[(i & 1) * (NS * 128) + hs * 128 + r] = mt;
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+#pragma unroll
+      for (int o = 1; o < NS; o++) mt = fmaxf(mt, xmax[(i & 1) * (NS * 128) + ((hs + o) % NS) * 128 + r]);
       const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_used, mt);
@@ -218,13 +223,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (!mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, a.status)) { ok = false; continue; }
           tc_fence_after();
 #pragma unroll
-          for (int u = 0; u < 2; u++) {
+          for (int u = 0; u < CW / 32; u++) {
             uint32_t rr[32];
-            tmem_ld32(tO + lane_off + (2 * hs + u) * 32, rr);
+            tmem_ld32(tO + lane_off + hs * CW + u * 32, rr);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; j++) rr[j] = __float_as_uint(__uint_as_float(rr[j]) * alpha);
-            tmem_st32(tO + lane_off + (2 * hs + u) * 32, rr);
+            tmem_st32(tO + lane_off + hs * CW + u * 32, rr);
           }
           tmem_st_wait();
         }
@@ -232,7 +237,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float mm = (m_used == -INFINITY) ? 0.f : m_used;
       float sm[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
+      for (int u = 0; u < CW / 32; u++) {
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
@@ -242,7 +247,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           pk[j] = pack_bf16(p0, p1);
           pk[j + 1] = pack_bf16(p2, p3);
         }
-        tmem_st16(tS[st] + lane_off + (2 * hs + u) * 16, pk);
+        tmem_st16(tS[st] + lane_off + hs * (CW / 2) + u * 16, pk);
       }
       const float sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
       l += sum;
@@ -252,15 +257,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (lane == 0) mbar_arrive(&p_ready[st]);
     }
     xl[hs * 128 + r] = l;
-    asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
-    l += xl[(hs ^ 1) * 128 + r];
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+#pragma unroll
+    for (int o = 1; o < NS; o++) l += xl[((hs + o) % NS) * 128 + r];
     if (ok && mbar_wait(&pv_done[(ntile - 1) & 1], ((ntile - 1) >> 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
       const float inv = 1.f / l;
       bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int cc = 2 * hs + u;
+      for (int u = 0; u < CW / 32; u++) {
+        const int cc = hs * (CW / 32) + u;
         uint32_t rr[32];
         tmem_ld32(tO + lane_off + cc * 32, rr);
         tmem_ld_wait();
@@ -322,7 +328,7 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
     attr_done = true;
   }
   dim3 grid(a.T / BQ, a.H, a.B);
-  attn_fwd_tc_kernel<<<grid, 384, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
+  attn_fwd_tc_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
   KERNEL_CHECK();
   return 0;
 }
