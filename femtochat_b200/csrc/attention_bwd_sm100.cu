@@ -205,8 +205,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + ks * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < BT / 16; k++)  // 16 keys = 8 TMEM columns / 2048 B of K rows
-          mma_ts(tdQ, tS[st] + k * 8, smem_desc_sw128(k_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < BT / 16; k++)  // 16 keys = 8 TMEM columns / 2048 B of K rows; dS of keys 64.. starts at column 64
+          mma_ts(tdQ, tS[st] + (k >> 2) * 64 + (k & 3) * 8, smem_desc_sw128(k_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_mn, (i > 0 || k > 0) ? 1u : 0u);
         tc_commit(&dq_done[st]);
         tc_commit(&k_free[ks]);
       }
@@ -228,17 +228,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < ntile; i++) {
       const int st = i & 1;
       const int k0 = (jlo + i) * BT;
-      // After a timed-out wait the warp keeps walking the loop (skipping the work) so that it still
-      // meets its partner warp at every pair barrier.
       if (ok && !mbar_wait(&dp_full[st], (i >> 1) & 1, abort_flag, a.status)) ok = false;
       if (ok && !mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, a.status)) ok = false;
-      if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
+      if (!ok) continue;
       tc_fence_after();
       const bool any_mask = __any_sync(0xffffffffu, (k0 + BT - 1 > q) || (k0 < lo));
       // The two threads of a row each take two 32-key chunks.  Both chunks of dP are read first and the
-      // buffer is handed back, so the tensor core can fill it for the next tile meanwhile.  dS (bf16) is
-      // written over the first 64 columns of S, which the partner thread may still be reading: results
-      // stay in registers until both have read all of S (pair barrier), then they are stored.
+      // buffer is handed back, so the tensor core can fill it for the next tile meanwhile.  Each thread
+      // writes its dS (bf16, 32 columns) over the start of its own 64 columns of S, once it has read them,
+      // so the two threads of a row never touch each other's columns.
       uint32_t dr[2][32];
       tmem_ld32(tdP + lane_off + (2 * halfsel) * 32, dr[0]);
       tmem_ld32(tdP + lane_off + (2 * halfsel + 1) * 32, dr[1]);
@@ -275,9 +273,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
 #pragma unroll
-      for (int u = 0; u < 2; u++) tmem_st16(tS[st] + lane_off + (2 * halfsel + u) * 16, pk[u]);
+      for (int u = 0; u < 2; u++) tmem_st16(tS[st] + lane_off + halfsel * 64 + u * 16, pk[u]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -456,10 +453,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES) + hf * 8192, do_addr = smem_u32(sdO + st * TILE_BYTES) + hf * 8192;
 #pragma unroll
         for (int k = 0; k < 4; k++)
-          mma_ts(tdV, tS[bf] + k * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
+          mma_ts(tdV, tS[bf] + (k >> 1) * 32 + (k & 1) * 8, smem_desc_sw128(do_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 4; k++)
-          mma_ts(tdK, tdP[bf] + k * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
+          mma_ts(tdK, tdP[bf] + (k >> 1) * 32 + (k & 1) * 8, smem_desc_sw128(q_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_out, (h2 > 0 || k > 0) ? 1u : 0u);
         tc_commit(&out_done[bf]);
         if (hf == 1) tc_commit(&qdo_empty[st]);
       }
@@ -482,9 +479,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (ok && hf == 0 && !mbar_wait(&qdo_full[it & 1], (it >> 1) & 1, abort_flag, a.status)) ok = false;
       if (ok && !mbar_wait(&s_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
       if (ok && !mbar_wait(&dp_full[bf], (h2 >> 1) & 1, abort_flag, a.status)) ok = false;
-      if (!ok) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory"); continue; }
+      if (!ok) continue;
       tc_fence_after();
-      uint32_t pp[16], pd[16];   // kept in registers until the partner thread has read S^T / dP^T
+      uint32_t pp[16], pd[16];
       {
         const int cq = hf * 64 + halfsel * 32;   // first query (within the tile) of this thread's chunk
         const int qf = qi0 + halfsel * 32;       // its position in the sequence
@@ -536,9 +533,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       }
-      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
-      tmem_st16(tS[bf] + lane_off + halfsel * 16, pp);
-      tmem_st16(tdP[bf] + lane_off + halfsel * 16, pd);
+      // P^T / dS^T of this thread's 32 queries go over the start of its own 32 columns of S^T / dP^T
+      tmem_st16(tS[bf] + lane_off + halfsel * 32, pp);
+      tmem_st16(tdP[bf] + lane_off + halfsel * 32, pd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
