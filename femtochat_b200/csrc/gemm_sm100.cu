@@ -22,7 +22,7 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STORE_STAGE_BYTES = 8 * 2 * 2048;  // 8 epilogue warps x 2 buffers x [32 rows][32 bf16]
+constexpr int STORE_STAGE_BYTES = 8 * 4096;  // 8 epilogue warps x [32 rows][64 bf16]
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int TMEM_COLS = 512;
@@ -69,26 +69,32 @@ __device__ __forceinline__ float* f32_dst(const GemmArgs& g, long long bz, int m
   return nullptr;
 }
 
-// The warp's 32 x 32 block of bf16 results goes to shared memory (64-byte swizzle, so the 16-byte
-// stores of a quarter warp hit distinct banks) and leaves as one TMA tiled store, which also clips
-// rows >= M and columns >= N.
-__device__ __forceinline__ void stage_store_bf16(const float (&v)[32], uint8_t* stage_buf, const CUtensorMap* tmC, int nc,
-                                                 int m_warp0, int bz, int lane) {
-  if (lane == 0) bulk_wait_read<1>();   // the store that last used this buffer has read it
-  __syncwarp();
+// A warp's results leave in blocks of 32 rows x 64 columns (two adjacent 32-column chunks): each lane writes
+// its row into shared memory (128-byte rows, 128-byte swizzle, so the 16-byte stores of eight lanes hit distinct
+// banks) and one TMA tiled store writes whole 128-byte lines, clipping rows >= M and columns >= N.
+// sub: 0 = first chunk of the pair (waits until the previous store has read the buffer), 1 = second;
+// flush: this chunk is the last valid one of its pair.
+__device__ __forceinline__ void stage_store_bf16(const float (&v)[32], uint8_t* stage_buf, const CUtensorMap* tmC, int sub, bool flush,
+                                                 int nc_pair, int m_warp0, int bz, int lane) {
+  if (sub == 0) {
+    if (lane == 0) bulk_wait_read<0>();
+    __syncwarp();
+  }
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     uint4 q;
     __nv_bfloat162* hq = reinterpret_cast<__nv_bfloat162*>(&q);
 #pragma unroll
     for (int e = 0; e < 4; e++) hq[e] = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
-    *reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = q;
+    *reinterpret_cast<uint4*>(stage_buf + lane * 128 + (((sub * 4 + j) ^ (lane & 7)) << 4)) = q;
   }
-  fence_proxy_async();
-  __syncwarp();
-  if (lane == 0) {
-    tma_store_3d(tmC, stage_buf, nc, m_warp0, bz);
-    bulk_commit();
+  if (flush) {
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(tmC, stage_buf, nc_pair, m_warp0, bz);
+      bulk_commit();
+    }
   }
 }
 
@@ -96,7 +102,8 @@ __device__ __forceinline__ void stage_store_bf16(const float (&v)[32], uint8_t* 
 template <int EPI>
 __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], int bz, int m, int nc, bool full_chunk,
                                            const uint4 (&pre)[4], bool use_pre, bool row_ok,
-                                           uint8_t* stage_buf, const CUtensorMap* tmC, int m_warp0, int lane) {
+                                           uint8_t* stage_buf, const CUtensorMap* tmC, int sub, bool flush, int nc_pair, int m_warp0,
+                                           int lane) {
   bf16* C = reinterpret_cast<bf16*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + nc;
   constexpr bool need_aux = EPI == EPI_RESID || EPI == EPI_DRELU2 || EPI == EPI_AXPBY;
   const bool vec = full_chunk && (g.ldc & 7) == 0 && (!need_aux || (g.ldaux & 7) == 0);
@@ -136,7 +143,7 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
     for (int j = 0; j < 32; j++) t += v[j];
     if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
   } else if (stage_buf != nullptr) {
-    stage_store_bf16(v, stage_buf, tmC, nc, m_warp0, bz, lane);
+    stage_store_bf16(v, stage_buf, tmC, sub, flush, nc_pair, m_warp0, bz, lane);
   } else if (!row_ok) {
     // nothing to store for rows past M
   } else if (vec) {
@@ -275,7 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ---------------- epilogue (warps 2..9) ----------------
     const int quad = warp & 3;           // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;    // the two warps of a quadrant take alternate 32-column chunks
+    const int half = (warp - 2) >> 2;    // the two warps of a quadrant take alternate pairs of 32-column chunks
     const int row_in_tile = quad * 32 + lane;
     int acc = 0; uint32_t acc_phase = 0;
     for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
@@ -296,13 +303,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                            (g.ldaux & 7) == 0 && (g.ldc & 7) == 0 && row_ok;
       const bf16* aux_row = aux_epi ? reinterpret_cast<const bf16*>(g.aux) + (long long)bz * g.strideAux + (long long)m * g.ldaux : nullptr;
       uint4 auxq[4], auxn[4];
-      bool pre_ok = false, next_ok = aux_epi && n0 + half * 32 + 32 <= g.N;
+      // this warp's chunks in order: 2*half, 2*half+1, 4+2*half, 4+2*half+1 (64 adjacent columns leave in one store)
+      auto chunk_of = [&](int ci) { return (ci >> 1) * 4 + 2 * half + (ci & 1); };
+      bool pre_ok = false, next_ok = aux_epi && n0 + chunk_of(0) * 32 + 32 <= g.N;
       if (next_ok) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) auxn[j] = *reinterpret_cast<const uint4*>(aux_row + n0 + half * 32 + j * 8);
+        for (int j = 0; j < 4; j++) auxn[j] = *reinterpret_cast<const uint4*>(aux_row + n0 + chunk_of(0) * 32 + j * 8);
       }
 #pragma unroll 1
-      for (int c = half; c < BN / 32; c += 2) {
+      for (int ci = 0; ci < BN / 64; ci++) {
+        const int c = chunk_of(ci);
         uint32_t r[32];
         __syncwarp();
         if (g.dbg == 2) continue;
@@ -310,17 +320,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         pre_ok = next_ok;
 #pragma unroll
         for (int j = 0; j < 4; j++) auxq[j] = auxn[j];
-        next_ok = aux_epi && c + 2 < BN / 32 && n0 + (c + 2) * 32 + 32 <= g.N;
+        const int cn = chunk_of(ci + 1);
+        next_ok = aux_epi && ci + 1 < BN / 64 && n0 + cn * 32 + 32 <= g.N;
         if (next_ok) {
 #pragma unroll
-          for (int j = 0; j < 4; j++) auxn[j] = *reinterpret_cast<const uint4*>(aux_row + n0 + (c + 2) * 32 + j * 8);
+          for (int j = 0; j < 4; j++) auxn[j] = *reinterpret_cast<const uint4*>(aux_row + n0 + cn * 32 + j * 8);
         }
         tmem_ld_wait();
         const int nc = n0 + c * 32;
         if (g.dbg == 3) { if (r[0] == 0x12345678u && r[31] == 0x1u) reinterpret_cast<bf16*>(g.C)[0] = __float2bfloat16_rn(1.f); continue; }
         const bool tma_out = p.tma_store != 0 && p.splits == 1 && g.epi != EPI_F32;
         if (nc >= g.N || (!row_ok && !tma_out)) continue;   // on the TMA path the whole warp stays together
-        uint8_t* sbuf = tma_out ? store_stage + ((warp - 2) * 2 + ((c >> 1) & 1)) * 2048 : nullptr;
+        uint8_t* sbuf = tma_out ? store_stage + (warp - 2) * 4096 : nullptr;
+        const int sub = ci & 1, nc_pair = n0 + (c & ~1) * 32;
+        const bool flush = sub == 1 || nc + 32 >= g.N;   // last valid chunk of its pair
         const bool full_chunk = nc + 32 <= g.N;
         float v[32];
 #pragma unroll
@@ -360,7 +373,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (tma_out) {
 #pragma unroll
               for (int j = 0; j < 32; j++) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
-              stage_store_bf16(v, sbuf, &tmC, nc, mt * BM + quad * 32, bz, lane);
+              stage_store_bf16(v, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, bz, lane);
             }
             float cm = -INFINITY;
 #pragma unroll
@@ -379,11 +392,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             rsum = rsum * __expf(rmax - nm) + cs;
             rmax = nm;
           } break;
-          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
-          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, mt * BM + quad * 32, lane); break;
+          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
+          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
+          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
+          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
+          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
           default: break;
         }
       }
@@ -608,7 +621,7 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   p.tma_store = 0;
   const bool bf16_out = g.epi != EPI_F32 && (g.epi != EPI_XENT_STATS || g.C != nullptr);
   if (bf16_out && splits == 1 && (g.ldc & 7) == 0 && (g.strideC & 7) == 0 && aligned16(g.C)) {
-    FEMTO_TRY(make_tmap_3d_bf16_sw(&tmC, g.C, g.N, g.M, nb, g.ldc, g.strideC, 32, 32, 2));
+    FEMTO_TRY(make_tmap_3d_bf16_sw(&tmC, g.C, g.N, g.M, nb, g.ldc, g.strideC, 64, 32, 3));
     p.tma_store = 1;
   }
   const int grid = std::min(p.total_units, sms);
