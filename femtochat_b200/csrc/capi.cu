@@ -116,6 +116,13 @@ int32_t femto_forward_loss(femto_handle* h, const float* theta, const int32_t* t
                     (cudaStream_t)stream);
 }
 
+int32_t femto_forward_logits(femto_handle* h, const float* theta, const int32_t* tokens, const int32_t* positions,
+                             int32_t B, float* logits_out, void* stream) {
+  if (!h || !logits_out) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  return model_step(h, theta, nullptr, tokens, nullptr, positions, B, FEMTO_REDUCTION_SUM, false, false, nullptr, nullptr,
+                    (cudaStream_t)stream, logits_out);
+}
+
 int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float* delta, const int32_t* h_tokens,
                                      const int32_t* h_targets, const int32_t* h_positions, int32_t B,
                                      int32_t reduction, int32_t accumulate, float* h_loss, int32_t* h_n_valid,

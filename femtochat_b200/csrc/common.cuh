@@ -178,8 +178,9 @@ int reduce_partials(const float* partial, int nrow, int ncol, float* out, const 
 
 // ---- lm_head tail ------------------------------------------------------------------------------
 // loss rows and (optionally) dX, dW of sum_valid(logsumexp(z) - z[target]), z = 15 tanh(xW/15),
-// processed in token chunks; the logits themselves are never written to HBM on the tensor-core
-// path (a chunk of bf16 dlogits is, as the operand of the two reverse GEMMs).
+// processed in token chunks; on the tensor-core path a forward-only call writes no logits at all, and a
+// call with the reverse pass keeps one chunk of bf16 logits, rewritten in place as d loss/d logit (the
+// operand of the two reverse GEMMs).
 struct XentArgs {
   const void* x = nullptr; const void* W = nullptr; long long ldw = 0; const int* targets0 = nullptr;
   int N = 0, D = 0, V = 0;

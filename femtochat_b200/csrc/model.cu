@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(1024) k_inv_nvalid(const int* tgt0, int n, flo
 template <typename T>
 static int step_t(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                   const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-                  int* nvalid_out, cudaStream_t s) {
+                  int* nvalid_out, cudaStream_t s, float* logits_out) {
   typedef Stream<T> S;
   const int N = B * h->T, d = h->d, dq = h->dq, kv = h->kv, H = h->H, Hkv = h->Hkv, hd = h->hd, Vp = h->Vp, V = h->V;
   const int Tl = h->T, L = h->L;
@@ -340,6 +340,15 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   const T* xlast = (const T*)h->lb[L - 1].xout;
   const T* xb = (const T*)h->lb[h->backout].xout;
   FEMTO_TRY(S::backout_norm(xlast, xb, theta + h->off_lam_y, nullptr, (T*)h->xnf, h->rf, N, d, eps, s));
+
+  // ---- the model call without targets returns the soft-capped logits of the first V rows (src/gpt.jl:165-170) ----
+  if (logits_out) {
+    GemmArgs g = GA();
+    g.A = h->xnf; g.lda = d; g.a_kmajor = true; g.B = h->sh_lm; g.ldb = Vp; g.b_kmajor = false;
+    g.C = logits_out; g.ldc = V; g.M = N; g.N = V; g.K = d; g.epi = EPI_F32; g.beta = 0.f;
+    FEMTO_TRY(gemm<T>(g, s));
+    return softcap_inplace(logits_out, (long long)N * V, s);
+  }
 
   // ---- lm_head tail (src/gpt.jl:165-194), token chunks; reverse fused in (src/kernels.jl:16-28) ----
   if (mean) {
@@ -434,8 +443,8 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
 
 int model_step(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-               int* nvalid_out, cudaStream_t s) {
-  if (!h || !theta || !tokens || !targets || !loss_out) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+               int* nvalid_out, cudaStream_t s, float* logits_out) {
+  if (!h || !theta || !tokens || (!logits_out && (!targets || !loss_out))) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   if (backward && !delta) return femto_fail(FEMTO_ERR_ARG, "delta is NULL");
   if (B <= 0 || B > h->maxB) return femto_fail(FEMTO_ERR_SHAPE, "B=%d outside 1..max_batch=%d", B, h->maxB);
   if (reduction != FEMTO_REDUCTION_SUM && reduction != FEMTO_REDUCTION_MEAN)
@@ -443,7 +452,7 @@ int model_step(femto_handle* h, const float* theta, float* delta, const int* tok
   if (!h->weights_valid) return femto_fail(FEMTO_ERR_STATE, "call femto_refresh_weights before the first step");
   if (!aligned16(theta) || (delta && !aligned16(delta))) return femto_fail(FEMTO_ERR_ALIGN, "Theta/delta must be 16-byte aligned");
   return h->bf ? step_t<bf16>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate, loss_out,
-                              nvalid_out, s)
+                              nvalid_out, s, logits_out)
                : step_t<float>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate,
-                               loss_out, nvalid_out, s);
+                               loss_out, nvalid_out, s, logits_out);
 }

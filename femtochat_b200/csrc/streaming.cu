@@ -1034,6 +1034,18 @@ int xent_dlogit_inplace(void* logits_bf16, long long ld, const float* lse_rows, 
   KERNEL_CHECK();
   return 0;
 }
+namespace {
+// z = 15 tanh(x / 15) in place (src/gpt.jl:12)
+__global__ void __launch_bounds__(256) k_softcap(float* __restrict__ x, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] = 15.f * tanhf(x[i] * (1.f / 15.f));
+}
+}  // namespace
+int softcap_inplace(float* x, long long n, cudaStream_t s) {
+  k_softcap<<<(int)std::min<long long>(cdiv(n, 256), 148 * 16), 256, 0, s>>>(x, n);
+  KERNEL_CHECK();
+  return 0;
+}
 int fill_zero(void* p, size_t bytes, cudaStream_t s) {
   cudaError_t e = cudaMemsetAsync(p, 0, bytes, s);
   if (e != cudaSuccess) return femto_fail((int)e, "cudaMemsetAsync failed: %s", cudaGetErrorString(e));

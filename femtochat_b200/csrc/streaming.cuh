@@ -48,6 +48,7 @@ int sum_rows_to_scalar(const float* rows, int n, float* out, const int* tgt0, in
                        cudaStream_t s);
 int xent_dlogit_inplace(void* logits_bf16, long long ld, const float* lse_rows, const int* tgt0, int n, int V, float w,
                         const float* w_dev, cudaStream_t s);
+int softcap_inplace(float* x, long long n, cudaStream_t s);
 int xent_finalize(const float2* stats, int ntile, const float* tz, const int* tgt0, int n, float* lse,
                   float* loss_rows, cudaStream_t s);
 int fill_zero(void* p, size_t bytes, cudaStream_t s);

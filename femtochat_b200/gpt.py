@@ -164,7 +164,11 @@ class GPT:
             self._state = GradientState(self.config, max_batch=B, compute_type=self.compute_type, **self.options)
         return self._state
 
-    def __call__(self, tokens, targets, positions=None, reduction: str = "mean"):
+    def __call__(self, tokens, targets=None, positions=None, reduction: str = "mean"):
+        """With targets: the loss (src/gpt.jl:196-199).  Without: the soft-capped logits as a float32
+        [B][T][vocab_size] tensor, the reference's (V,T,B) array (src/gpt.jl:129-170)."""
+        if targets is None:
+            return self.logits(tokens, positions)
         tok, tgt, pos = _dev_i32(tokens), _dev_i32(targets), _dev_i32(positions)
         st = self.state(tok.shape[0])
         st.refresh_weights(self.params.theta)
@@ -172,3 +176,12 @@ class GPT:
             st.h, _lib.ptr(self.params.theta), _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), tok.shape[0],
             _lib.REDUCTION[reduction], _lib.ptr(st._loss), _lib.ptr(st._nvalid), _lib.stream_ptr()))
         return float(st._loss.item())
+
+    def logits(self, tokens, positions=None):
+        tok, pos = _dev_i32(tokens), _dev_i32(positions)
+        st = self.state(tok.shape[0])
+        st.refresh_weights(self.params.theta)
+        out = torch.empty(tok.shape[0], tok.shape[1], self.config.vocab_size, device="cuda", dtype=torch.float32)
+        _lib.check(_lib.lib().femto_forward_logits(st.h, _lib.ptr(self.params.theta), _lib.ptr(tok), _lib.ptr(pos),
+                                                   tok.shape[0], _lib.ptr(out), _lib.stream_ptr()))
+        return out

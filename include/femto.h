@@ -105,6 +105,11 @@ int32_t femto_loss_and_gradient(femto_handle* h, const float* theta, float* delt
 int32_t femto_forward_loss(femto_handle* h, const float* theta, const int32_t* tokens,
                            const int32_t* targets, const int32_t* positions, int32_t B, int32_t reduction,
                            float* loss_out, int32_t* n_valid_out, void* stream);
+/* The model call without targets (src/gpt.jl:129-170, `logits = omega(tokens; positions)`): writes the
+ * soft-capped logits z = 15 tanh(x W / 15) of the first vocab_size rows as fp32 [B][T][vocab_size]
+ * (the reference's (V,T,B) array).  Meant for small evaluation shapes: the output is B*T*V floats. */
+int32_t femto_forward_logits(femto_handle* h, const float* theta, const int32_t* tokens,
+                             const int32_t* positions, int32_t B, float* logits_out, void* stream);
 /* Host-buffer convenience used by the end-to-end path: copies the three int32 [B][T] host arrays to
  * the device, runs femto_loss_and_gradient, reads loss and n_valid back and synchronises. */
 int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float* delta,

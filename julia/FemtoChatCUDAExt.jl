@@ -64,6 +64,16 @@ function loss_and_gradient!(params::Params, state::FemtoGradientState, layout, t
     Array(state.loss)[1]
 end
 
+# logits = model(tokens; positions)   (src/gpt.jl:129-170): (V, T, B) Float32, soft-capped, first vocab_size rows
+function forward_logits(params::Params, state::FemtoGradientState, config, tokens; positions=nothing)
+    pos = isnothing(positions) ? CU_NULL : pointer(positions)
+    logits = CUDA.zeros(Float32, config.vocab_size, size(tokens, 1), size(tokens, 2))
+    check(ccall((:femto_forward_logits, libfemto), Int32,
+                (Ptr{Cvoid}, CuPtr{Float32}, CuPtr{Int32}, CuPtr{Int32}, Int32, CuPtr{Float32}, Ptr{Cvoid}),
+                state.handle, params.Θ, tokens, pos, size(tokens, 2), logits, stream().handle))
+    logits
+end
+
 # attention!(𝒜, O, ℓ, m, Q, K, V, window)   (ext/FemtoChatCUDAExt.jl:1242 of the reference)
 function attention!(_, O::CuArray{T,4}, ℓ, m, Q, K, V, window) where {T}
     D, H, Tn, B = size(Q)

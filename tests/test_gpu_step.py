@@ -171,3 +171,21 @@ def test_forward_only_model_call_matches():
     ref = float(fo.Model(ocfg, fo.StepOptions(reduction="mean")).forward(th.double(), tok, tgt, pos))
     model = fb.GPT(fb.Params(th.cuda()), cfg, lay)
     assert model(tok, tgt, positions=pos) == pytest.approx(ref, rel=1e-5)   # reduction=:mean is the call's default
+
+
+def test_model_call_without_targets_returns_softcapped_logits():
+    """`logits = model(tokens; positions)` (src/gpt.jl:129-170): fp32 [B][T][vocab_size], first V rows only."""
+    cfg = fb.GPTConfig(**MID)
+    lay = fb.parameter_layout(cfg)
+    th = torch.zeros(lay.nparams)
+    ocfg = fo.GPTConfig(**MID)
+    fo.initialize(th, ocfg, fo.parameter_layout(ocfg), 5, all_nonzero=True)
+    tok, tgt, pos = inputs(MID, 2)
+    cache = {}
+    fo.Model(ocfg, fo.StepOptions(reduction="sum")).forward(th.double(), tok, tgt, pos, cache=cache)
+    z_ref = cache["z"].float()
+    model = fb.GPT(fb.Params(th.cuda()), cfg, lay)
+    z = model(tok, positions=pos).cpu()
+    assert z.shape == (tok.shape[0], tok.shape[1], cfg.vocab_size)
+    assert (z - z_ref.reshape(z.shape)).abs().max() <= 2e-4   # fp32 build: tolerance of the tanh/GEMM rounding
+    assert z.abs().max() <= 15.0
