@@ -178,6 +178,7 @@ class GPT:
         return float(st._loss.item())
 
     def logits(self, tokens, positions=None):
+        import torch
         tok, pos = _dev_i32(tokens), _dev_i32(positions)
         st = self.state(tok.shape[0])
         st.refresh_weights(self.params.theta)
