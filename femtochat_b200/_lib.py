@@ -78,6 +78,8 @@ SIGNATURES = {
     "femto_embedding_gradient": (I32, [I32, P, P, P, I32, I32, I32, P]),
     "femto_xent_fused": (I32, [I32, P, P, I64, P, I32, I32, I32, F, P, P, P, P, P]),
     "femto_newton_schulz": (I32, [I32, P, I32, I32, I32, C.POINTER(F), I32, P]),
+    "femto_cross_entropy": (I32, [P, I64, P, I32, I32, I32, P, P, P]),
+    "femto_cross_entropy_gradient": (I32, [P, I64, P, I64, P, I32, I32, I32, F, P, P]),
     "femto_adamw": (I32, [P, P, P, P, I64, F, F, F, F, F, I32, F, P]),
     "femto_status_word": (I32, [P, C.POINTER(I32)]),
     "femto_sync": (I32, [P, P]),

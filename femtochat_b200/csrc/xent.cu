@@ -94,3 +94,99 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   cudaFree(buf);
   return r;
 }
+
+// ---- cross-entropy on materialised logits (the reference's stand-alone methods) ------------------
+namespace {
+// One block per row of fp32 logits [N][ldl]: loss = logsumexp(l) - l[target] (src/gpt.jl:175-193), or, in
+// reverse, delta += scale (softmax(l) - onehot) for rows with a target (src/kernels.jl:16-28).
+// Fixed reduction trees: repeatable.
+template <bool REVERSE>
+__global__ void __launch_bounds__(256) k_ce_rows(const float* __restrict__ logits, long long ldl,
+                                                 const int* __restrict__ tgt0, int V, float* __restrict__ loss_rows,
+                                                 float* __restrict__ delta, long long ldd, float scale_host,
+                                                 const float* __restrict__ scale_rows, const int* __restrict__ n_valid) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const long long row = blockIdx.x;
+  const float* l = logits + row * ldl;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tg = tgt0[row];
+  if (REVERSE && tg < 0) return;   // ignored rows contribute nothing
+  float mx = -INFINITY;
+  for (int v = threadIdx.x; v < V; v += 256) mx = fmaxf(mx, l[v]);
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) { float m = red[0]; for (int i = 1; i < 8; i++) m = fmaxf(m, red[i]); bc = m; }
+  __syncthreads();
+  mx = bc;
+  float sum = 0.f;
+  for (int v = threadIdx.x; v < V; v += 256) sum += expf(l[v] - mx);
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) { float a = 0.f; for (int i = 0; i < 8; i++) a += red[i]; bc = a; }
+  __syncthreads();
+  const float norm = bc;
+  if (!REVERSE) {
+    if (threadIdx.x == 0) loss_rows[row] = tg >= 0 ? mx + logf(norm) - l[tg] : 0.f;
+  } else {
+    float w = scale_rows ? scale_rows[row] : scale_host;
+    if (n_valid) w /= (float)n_valid[0];
+    float* d = delta + row * ldd;
+    for (int v = threadIdx.x; v < V; v += 256) d[v] += w * (expf(l[v] - mx) / norm - (v == tg ? 1.f : 0.f));
+  }
+}
+__global__ void __launch_bounds__(1024) k_count_valid(const int* tgt0, int n, int* out) {
+  __shared__ int red[32];
+  int c = 0;
+  for (int i = threadIdx.x; i < n; i += 1024) c += tgt0[i] >= 0 ? 1 : 0;
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) { int a = 0; for (int i = 0; i < 32; i++) a += red[i]; out[0] = a; }
+}
+}  // namespace
+
+extern "C" int32_t femto_cross_entropy(const float* logits, int64_t ldl, const int32_t* targets0, int32_t N, int32_t V,
+                                       int32_t reduction, float* out, int32_t* n_valid_out, void* stream) {
+  if (!logits || !targets0 || !out || N <= 0 || V <= 0 || ldl < V) return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if (reduction < 0 || reduction > 2) return femto_fail(FEMTO_ERR_ARG, "reduction must be 0 (sum), 1 (mean) or 2 (none)");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (reduction == FEMTO_REDUCTION_NONE) {   // out is [N]
+    k_ce_rows<false><<<N, 256, 0, s>>>(logits, ldl, targets0, V, out, nullptr, 0, 0.f, nullptr, nullptr);
+    KERNEL_CHECK();
+    if (n_valid_out) { k_count_valid<<<1, 1024, 0, s>>>(targets0, N, n_valid_out); KERNEL_CHECK(); }
+    return 0;
+  }
+  float* rows = nullptr;
+  CUDA_TRY(cudaMalloc(&rows, sizeof(float) * (size_t)N));
+  k_ce_rows<false><<<N, 256, 0, s>>>(logits, ldl, targets0, V, rows, nullptr, 0, 0.f, nullptr, nullptr);
+  int r = 0;
+  { cudaError_t e = cudaGetLastError(); if (e != cudaSuccess) r = femto_fail((int)e, "cross-entropy kernel launch failed: %s", cudaGetErrorString(e)); }
+  if (!r) r = sum_rows_to_scalar(rows, N, out, targets0, n_valid_out, reduction == FEMTO_REDUCTION_MEAN ? 1.f : 0.f, s);
+  cudaStreamSynchronize(s);
+  cudaFree(rows);
+  return r;
+}
+
+extern "C" int32_t femto_cross_entropy_gradient(float* delta, int64_t ldd, const float* logits, int64_t ldl,
+                                                const int32_t* targets0, int32_t N, int32_t V, int32_t reduction,
+                                                float dy, const float* dy_rows, void* stream) {
+  if (!delta || !logits || !targets0 || N <= 0 || V <= 0 || ldl < V || ldd < V) return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if (reduction < 0 || reduction > 2) return femto_fail(FEMTO_ERR_ARG, "reduction must be 0 (sum), 1 (mean) or 2 (none)");
+  if (reduction == FEMTO_REDUCTION_NONE && !dy_rows) return femto_fail(FEMTO_ERR_ARG, "reduction none needs dy_rows [N]");
+  cudaStream_t s = (cudaStream_t)stream;
+  int* nv = nullptr;
+  if (reduction == FEMTO_REDUCTION_MEAN) {
+    CUDA_TRY(cudaMalloc(&nv, sizeof(int)));
+    k_count_valid<<<1, 1024, 0, s>>>(targets0, N, nv);
+  }
+  k_ce_rows<true><<<N, 256, 0, s>>>(logits, ldl, targets0, V, nullptr, delta, ldd, dy,
+                                    reduction == FEMTO_REDUCTION_NONE ? dy_rows : nullptr, nv);
+  int r = 0;
+  { cudaError_t e = cudaGetLastError(); if (e != cudaSuccess) r = femto_fail((int)e, "cross-entropy gradient launch failed: %s", cudaGetErrorString(e)); }
+  if (nv) { cudaStreamSynchronize(s); cudaFree(nv); }
+  return r;
+}

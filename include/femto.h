@@ -36,6 +36,7 @@ extern "C" {
 
 #define FEMTO_REDUCTION_SUM 0  /* reduction=:sum, the training script's call (scripts/train.jl:118) */
 #define FEMTO_REDUCTION_MEAN 1 /* reduction=:mean, the default of the model call (src/gpt.jl:196) */
+#define FEMTO_REDUCTION_NONE 2 /* reduction=:none, per-token losses (stand-alone cross-entropy entry points only) */
 
 /* Mirrors GPTConfig (src/parameters.jl:71-80) plus the build options the reference passes as
  * keyword arguments (compute_type, src/parameters.jl:451) and the four switches on which the
@@ -188,6 +189,18 @@ int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void
  * (fixed summation order), tokens 0-based int32 [N], dy [N][D] of `dtype`, δ fp32 [rows][D]. */
 int32_t femto_embedding_gradient(int32_t dtype, float* delta_table, const void* dy, const int32_t* tokens0,
                                  int32_t N, int32_t D, int32_t rows, void* stream);
+/* cross_entropy(logits, targets, ignore, reduction) on materialised logits (src/gpt.jl:175-193; the
+ * reference's GPU method ext/FemtoChatCUDAExt.jl:49-55): logits fp32 [N][ldl] (the (V,T,B) array, first V
+ * columns used), targets0 0-based or -1.  out: one float (sum / mean over valid targets) or [N] floats
+ * (FEMTO_REDUCTION_NONE, ignored rows 0).  Synchronises for sum / mean (scratch is allocated per call). */
+int32_t femto_cross_entropy(const float* logits, int64_t ldl, const int32_t* targets0, int32_t N, int32_t V,
+                            int32_t reduction, float* out, int32_t* n_valid_out, void* stream);
+/* cross_entropy_gradient!(delta, logits, targets, dy, ignore, reduction) (src/kernels.jl:16-28; GPU method
+ * ext/FemtoChatCUDAExt.jl:57-61): delta[N][ldd] += scale (softmax(logits) - onehot) on rows with a target,
+ * scale = dy (sum), dy / n_valid (mean) or dy_rows[row] (none; device array [N]). */
+int32_t femto_cross_entropy_gradient(float* delta, int64_t ldd, const float* logits, int64_t ldl,
+                                     const int32_t* targets0, int32_t N, int32_t V, int32_t reduction, float dy,
+                                     const float* dy_rows, void* stream);
 /* Fused lm_head tail (src/gpt.jl:165-170,172-194; src/kernels.jl:16-28): loss = sum over valid
  * targets of logsumexp(z) - z[target], z = 15 tanh(x W / 15); dX and dW (+=) of that loss.
  * x: [N][D] dtype, W: [D][ldw] dtype (first V columns used), targets0: 0-based or -1,

@@ -74,6 +74,30 @@ function forward_logits(params::Params, state::FemtoGradientState, config, token
     logits
 end
 
+# cross_entropy(logits, targets, ignore, reduction) on a (V, T, B) Float32 CuArray   (src/gpt.jl:175-193)
+function cross_entropy(logits::CuArray{Float32,3}, targets::CuArray, ignore, reduction)
+    V, Tn, B = size(logits)
+    tg0 = Int32.(ifelse.(targets .== ignore, Int32(-1), targets .- Int32(1)))
+    red = reduction == :sum ? 0 : reduction == :mean ? 1 : 2
+    out = CUDA.zeros(Float32, red == 2 ? Tn * B : 1)
+    check(ccall((:femto_cross_entropy, libfemto), Int32,
+                (CuPtr{Float32}, Int64, CuPtr{Int32}, Int32, Int32, Int32, CuPtr{Float32}, CuPtr{Int32}, Ptr{Cvoid}),
+                logits, V, tg0, Tn * B, V, red, out, CU_NULL, stream().handle))
+    red == 2 ? reshape(out, Tn, B) : Array(out)[1]
+end
+
+# cross_entropy_gradient!(δ, logits, targets, dy, ignore, reduction)   (src/kernels.jl:16-28)
+function cross_entropy_gradient!(δ::CuArray{Float32}, logits::CuArray{Float32,3}, targets::CuArray, dy, ignore, reduction)
+    V, Tn, B = size(logits)
+    tg0 = Int32.(ifelse.(targets .== ignore, Int32(-1), targets .- Int32(1)))
+    red = reduction == :sum ? 0 : reduction == :mean ? 1 : 2
+    rows = red == 2 ? pointer(CuArray{Float32}(vec(dy))) : CU_NULL
+    check(ccall((:femto_cross_entropy_gradient, libfemto), Int32,
+                (CuPtr{Float32}, Int64, CuPtr{Float32}, Int64, CuPtr{Int32}, Int32, Int32, Int32, Float32, CuPtr{Float32}, Ptr{Cvoid}),
+                δ, V, logits, V, tg0, Tn * B, V, red, red == 2 ? 0f0 : Float32(dy), rows, stream().handle))
+    nothing
+end
+
 # attention!(𝒜, O, ℓ, m, Q, K, V, window)   (ext/FemtoChatCUDAExt.jl:1242 of the reference)
 function attention!(_, O::CuArray{T,4}, ℓ, m, Q, K, V, window) where {T}
     D, H, Tn, B = size(Q)

@@ -230,3 +230,44 @@ def test_muon_adamw_three_steps_against_golden():
         assert err <= 2e-4, (i, float(err))
     assert opt.get_t() == [3] * 10
     assert float(opt.adamw[0].m.abs().max()) > 0 and float(opt.muon[0].m.abs().max()) > 0
+
+
+@pytest.mark.parametrize("reduction", ["sum", "mean", "none"])
+def test_cross_entropy_on_materialised_logits(reduction):
+    """cross_entropy / cross_entropy_gradient! on a (V,T,B) logits array (src/gpt.jl:175-193,
+    src/kernels.jl:16-28): fp32, ignored targets contribute nothing, delta is accumulated into."""
+    L = _lib.lib()
+    N, V, ld = 70, 50, 56
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(N, ld, generator=g) * 3
+    tgt = torch.randint(0, V, (N,), generator=g, dtype=torch.int32)
+    tgt[::9] = -1
+    valid = tgt >= 0
+    z = logits[:, :V].double()
+    losses = torch.where(valid, torch.logsumexp(z, -1) - z.gather(1, tgt.clamp(min=0).long()[:, None])[:, 0], torch.zeros(N, dtype=torch.float64))
+    red = {"sum": 0, "mean": 1, "none": 2}[reduction]
+    lg, tg = logits.cuda(), tgt.cuda()
+    out = torch.zeros(N if reduction == "none" else 1, device="cuda")
+    nv = torch.zeros(1, device="cuda", dtype=torch.int32)
+    _lib.check(L.femto_cross_entropy(_lib.ptr(lg), ld, _lib.ptr(tg), N, V, red, _lib.ptr(out), _lib.ptr(nv), None))
+    torch.cuda.synchronize()
+    assert int(nv) == int(valid.sum())
+    ref = {"sum": losses.sum(), "mean": losses.sum() / valid.sum(), "none": losses}[reduction]
+    assert torch.allclose(out.double().cpu().reshape(ref.shape), ref, rtol=1e-5, atol=1e-5)
+    # gradient, accumulated into a non-zero delta
+    dy = 0.7
+    dy_rows = torch.rand(N, generator=g) + 0.5
+    scale = {"sum": torch.full((N,), dy, dtype=torch.float64), "mean": torch.full((N,), dy / int(valid.sum()), dtype=torch.float64),
+             "none": dy_rows.double()}[reduction]
+    onehot = torch.zeros(N, V, dtype=torch.float64)
+    onehot[valid, tgt[valid].long()] = 1.0
+    d_ref = torch.where(valid[:, None], scale[:, None] * (torch.softmax(z, -1) - onehot), torch.zeros(N, V, dtype=torch.float64))
+    delta0 = torch.randn(N, ld, generator=g)
+    delta = delta0.clone().cuda()
+    dyr = dy_rows.cuda()
+    _lib.check(L.femto_cross_entropy_gradient(_lib.ptr(delta), ld, _lib.ptr(lg), ld, _lib.ptr(tg), N, V, red, dy,
+                                              _lib.ptr(dyr) if reduction == "none" else None, None))
+    torch.cuda.synchronize()
+    got = delta.double().cpu()
+    assert torch.allclose(got[:, :V], delta0[:, :V].double() + d_ref, rtol=1e-5, atol=1e-6)
+    assert torch.equal(got[:, V:], delta0[:, V:].double())   # padded columns untouched
