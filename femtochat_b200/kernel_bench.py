@@ -1,7 +1,7 @@
 """Isolated kernel sweep (BASELINE.json configs[1]): attention forward/reverse, fused lm_head tail,
 Newton-Schulz chains and the GEMM forms of the step, timed with CUDA events on seeded Gaussian inputs.
 
-    python -m femtochat_b200.kernel_bench [--kernel all|attn|xent|ns|gemm] [--small] [--iters N]
+    python -m femtochat_b200.kernel_bench [--kernel all|attn|xent|ns|gemm|stream] [--small] [--iters N]
 
 `--small` shrinks the problem (for profiler captures); the default shapes are the benchmark's:
 attention B=8, T=2048, 10 query / 5 kv heads, head_dim 128, geometric(512) documents;
@@ -125,9 +125,35 @@ def bench_gemm(small, iters):
         print(f"gemm {nm} {M}x{Nn}x{K}: {t:7.3f} ms {2.0 * M * Nn * K / t / 1e9:7.0f} TFLOP/s")
 
 
+def bench_stream(small, iters):
+    """HBM-bound kernels that have their own entry point: AdamW (28 B per parameter) and the deterministic
+    embedding-gradient scatter (2 B per input element read + fp32 read-modify-write of the touched rows)."""
+    L = _lib.lib()
+    n = (1 << 22) if small else 83886080          # one embedding table of the d20 model
+    th, de = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    fn = lambda: _lib.check(L.femto_adamw(_lib.ptr(th), _lib.ptr(de), _lib.ptr(m), _lib.ptr(v), n, 1e-3, 0.9, 0.95, 1e-10,
+                                          0.0, 3, 65536.0, None))
+    t = _time(fn, iters)
+    print(f"adamw n={n}: {t:7.3f} ms {28.0 * n / t / 1e6:7.0f} GB/s (28 B/param)")
+    N, D, rows = (8192, 1280, 65536) if small else (65536, 1280, 65536)
+    rng = np.random.default_rng(4)
+    ranks = np.arange(1, rows + 1, dtype=np.float64) ** -1.1     # Zipf(1.1): a few rows receive thousands of adds
+    tok = torch.from_numpy(rng.choice(rows, size=N, p=ranks / ranks.sum()).astype(np.int32)).cuda()
+    dy = torch.randn(N, D, device="cuda").bfloat16()
+    table = torch.zeros(rows, D, device="cuda")
+    fn = lambda: _lib.check(L.femto_embedding_gradient(_lib.BF16, _lib.ptr(table), _lib.ptr(dy), _lib.ptr(tok), N, D, rows, None))
+    t = _time(fn, iters)
+    touched = int(torch.unique(tok).numel())
+    byts = 2.0 * N * D + 8.0 * touched * D
+    print(f"embedding scatter N={N} D={D} rows touched {touched}: {t:7.3f} ms {byts / t / 1e6:7.0f} GB/s "
+          f"(input read + fp32 read-modify-write of touched rows; the stand-alone call also allocates and builds the sort / "
+          f"run-length plan every time, which the training step does once per batch for its eleven tables)")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="all", choices=["all", "attn", "xent", "ns", "gemm"])
+    ap.add_argument("--kernel", default="all", choices=["all", "attn", "xent", "ns", "gemm", "stream"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
@@ -139,6 +165,8 @@ def main():
         bench_xent(a.small, a.iters)
     if a.kernel in ("all", "ns"):
         bench_ns(a.small, a.iters)
+    if a.kernel in ("all", "stream"):
+        bench_stream(a.small, a.iters)
 
 
 if __name__ == "__main__":
