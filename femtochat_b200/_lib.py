@@ -62,6 +62,7 @@ SIGNATURES = {
     "femto_loss_and_gradient": (I32, [P, P, P, P, P, P, I32, I32, I32, P, P, P]),
     "femto_forward_loss": (I32, [P, P, P, P, P, I32, I32, P, P, P]),
     "femto_forward_logits": (I32, [P, P, P, P, I32, P, P]),
+    "femto_forward_token_losses": (I32, [P, P, P, P, P, I32, P, P, P]),
     "femto_loss_and_gradient_host": (I32, [P, P, P, P, P, P, I32, I32, I32, C.POINTER(F), C.POINTER(I32), P]),
     "femto_grad_sync": (I32, [P, P, P, P, P]),
     "femto_set_overlap": (I32, [P, I32]),

@@ -123,6 +123,15 @@ int32_t femto_forward_logits(femto_handle* h, const float* theta, const int32_t*
                     (cudaStream_t)stream, logits_out);
 }
 
+int32_t femto_forward_token_losses(femto_handle* h, const float* theta, const int32_t* tokens, const int32_t* targets,
+                                   const int32_t* positions, int32_t B, float* losses_out, int32_t* n_valid_out,
+                                   void* stream) {
+  if (!h || !losses_out) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  // the scalar path also counts the valid targets; its sum goes to the handle's own loss scalar
+  return model_step(h, theta, nullptr, tokens, targets, positions, B, FEMTO_REDUCTION_SUM, false, false, h->loss_dev,
+                    n_valid_out ? n_valid_out : h->nvalid_dev, (cudaStream_t)stream, nullptr, losses_out);
+}
+
 int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float* delta, const int32_t* h_tokens,
                                      const int32_t* h_targets, const int32_t* h_positions, int32_t B,
                                      int32_t reduction, int32_t accumulate, float* h_loss, int32_t* h_n_valid,

@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(1024) k_inv_nvalid(const int* tgt0, int n, flo
 template <typename T>
 static int step_t(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                   const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-                  int* nvalid_out, cudaStream_t s, float* logits_out) {
+                  int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out) {
   typedef Stream<T> S;
   const int N = B * h->T, d = h->d, dq = h->dq, kv = h->kv, H = h->H, Hkv = h->Hkv, hd = h->hd, Vp = h->Vp, V = h->V;
   const int Tl = h->T, L = h->L;
@@ -365,7 +365,9 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     x.ws = h->gemm_ws; x.ws_bytes = h->gemm_ws_bytes; x.status = h->status;
     FEMTO_TRY(xent_tail<T>(x, s));
   }
-  FEMTO_TRY(sum_rows_to_scalar(h->loss_rows, N, loss_out, h->tgt0, nvalid_out, mean ? 1.f : 0.f, s));
+  if (token_losses_out)   // reduction=:none (src/gpt.jl:191-193): one loss per token slot, 0 where the target is ignored
+    CUDA_TRY(cudaMemcpyAsync(token_losses_out, h->loss_rows, sizeof(float) * (size_t)N, cudaMemcpyDeviceToDevice, s));
+  if (loss_out) FEMTO_TRY(sum_rows_to_scalar(h->loss_rows, N, loss_out, h->tgt0, nvalid_out, mean ? 1.f : 0.f, s));
   if (!backward) return 0;
 
   // ---- reverse ----
@@ -443,8 +445,9 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
 
 int model_step(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-               int* nvalid_out, cudaStream_t s, float* logits_out) {
-  if (!h || !theta || !tokens || (!logits_out && (!targets || !loss_out))) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+               int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out) {
+  if (!h || !theta || !tokens || (!logits_out && (!targets || (!loss_out && !token_losses_out))))
+    return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   if (backward && !delta) return femto_fail(FEMTO_ERR_ARG, "delta is NULL");
   if (B <= 0 || B > h->maxB) return femto_fail(FEMTO_ERR_SHAPE, "B=%d outside 1..max_batch=%d", B, h->maxB);
   if (reduction != FEMTO_REDUCTION_SUM && reduction != FEMTO_REDUCTION_MEAN)
@@ -452,7 +455,7 @@ int model_step(femto_handle* h, const float* theta, float* delta, const int* tok
   if (!h->weights_valid) return femto_fail(FEMTO_ERR_STATE, "call femto_refresh_weights before the first step");
   if (!aligned16(theta) || (delta && !aligned16(delta))) return femto_fail(FEMTO_ERR_ALIGN, "Theta/delta must be 16-byte aligned");
   return h->bf ? step_t<bf16>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate, loss_out,
-                              nvalid_out, s, logits_out)
+                              nvalid_out, s, logits_out, token_losses_out)
                : step_t<float>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate,
-                               loss_out, nvalid_out, s, logits_out);
+                               loss_out, nvalid_out, s, logits_out, token_losses_out);
 }

@@ -69,7 +69,7 @@ void model_free(femto_handle* h);
 int model_refresh(femto_handle* h, const float* theta, cudaStream_t s);
 int model_step(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-               int* nvalid_out, cudaStream_t s, float* logits_out = nullptr);
+               int* nvalid_out, cudaStream_t s, float* logits_out = nullptr, float* token_losses_out = nullptr);
 int layout_describe(const femto_config* cfg, std::vector<femto_tensor_desc>& out, long long* nparams, int* Vp);
 int layout_windows(const femto_config* cfg, std::vector<int>& left, std::vector<int>& has_ve);
 

@@ -172,6 +172,13 @@ class GPT:
         tok, tgt, pos = _dev_i32(tokens), _dev_i32(targets), _dev_i32(positions)
         st = self.state(tok.shape[0])
         st.refresh_weights(self.params.theta)
+        if reduction == "none":   # per-token losses [B][T] (src/gpt.jl:191-193)
+            import torch
+            out = torch.empty(tok.shape[0], tok.shape[1], device="cuda", dtype=torch.float32)
+            _lib.check(_lib.lib().femto_forward_token_losses(
+                st.h, _lib.ptr(self.params.theta), _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), tok.shape[0],
+                _lib.ptr(out), None, _lib.stream_ptr()))
+            return out
         _lib.check(_lib.lib().femto_forward_loss(
             st.h, _lib.ptr(self.params.theta), _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), tok.shape[0],
             _lib.REDUCTION[reduction], _lib.ptr(st._loss), _lib.ptr(st._nvalid), _lib.stream_ptr()))

@@ -111,6 +111,11 @@ int32_t femto_forward_loss(femto_handle* h, const float* theta, const int32_t* t
  * (the reference's (V,T,B) array).  Meant for small evaluation shapes: the output is B*T*V floats. */
 int32_t femto_forward_logits(femto_handle* h, const float* theta, const int32_t* tokens,
                              const int32_t* positions, int32_t B, float* logits_out, void* stream);
+/* The model call with reduction=:none (src/gpt.jl:191-193), what the reference's evaluation loop uses
+ * (src/loss_eval.jl:8-46): fp32 losses [B][T], zero where the target is ignored. */
+int32_t femto_forward_token_losses(femto_handle* h, const float* theta, const int32_t* tokens,
+                                   const int32_t* targets, const int32_t* positions, int32_t B,
+                                   float* losses_out, int32_t* n_valid_out, void* stream);
 /* Host-buffer convenience used by the end-to-end path: copies the three int32 [B][T] host arrays to
  * the device, runs femto_loss_and_gradient, reads loss and n_valid back and synchronises. */
 int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float* delta,

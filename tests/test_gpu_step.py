@@ -189,3 +189,20 @@ def test_model_call_without_targets_returns_softcapped_logits():
     assert z.shape == (tok.shape[0], tok.shape[1], cfg.vocab_size)
     assert (z - z_ref.reshape(z.shape)).abs().max() <= 2e-4   # fp32 build: tolerance of the tanh/GEMM rounding
     assert z.abs().max() <= 15.0
+
+
+def test_model_call_reduction_none_returns_token_losses():
+    """reduction=:none (src/gpt.jl:191-193), the form the evaluation loop consumes (src/loss_eval.jl:8-46)."""
+    cfg = fb.GPTConfig(**MID)
+    lay = fb.parameter_layout(cfg)
+    th = torch.zeros(lay.nparams)
+    ocfg = fo.GPTConfig(**MID)
+    fo.initialize(th, ocfg, fo.parameter_layout(ocfg), 7, all_nonzero=True)
+    tok, tgt, pos = inputs(MID, 2)
+    ref = fo.Model(ocfg, fo.StepOptions(reduction="none")).forward(th.double(), tok, tgt, pos)
+    model = fb.GPT(fb.Params(th.cuda()), cfg, lay)
+    got = model(tok, tgt, positions=pos, reduction="none").cpu()
+    assert got.shape == tok.shape
+    assert torch.equal(got == 0, (tgt == -1) | (ref.float() == 0))          # ignored slots are exactly zero
+    assert torch.allclose(got.double(), ref.reshape(got.shape), rtol=1e-5, atol=1e-5)
+    assert float(got.sum()) == pytest.approx(model(tok, tgt, positions=pos, reduction="sum"), rel=1e-6)
