@@ -132,7 +132,6 @@ struct GemmArgs {
   // tensor-core path scratch
   void* ws = nullptr; size_t ws_bytes = 0;  // stream-K partials
   unsigned int* status = nullptr;
-  int dbg = 0;  // developer experiments only
 };
 
 template <typename T> int gemm_simt(const GemmArgs& g, cudaStream_t s);

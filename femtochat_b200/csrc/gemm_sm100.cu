@@ -137,12 +137,7 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
     if constexpr (EPI == EPI_AXPBY) x = alpha * a[j] + beta * x;
     v[j] = x;
   }
-  if (g.dbg == 1) {
-    float t = 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; j++) t += v[j];
-    if (t == 1.2345e30f) C[0] = __float2bfloat16_rn(t);
-  } else if (stage_buf != nullptr) {
+  if (stage_buf != nullptr) {
     stage_store_bf16(v, stage_buf, tmC, sub, flush, nc_pair, m_warp0, bz, lane);
   } else if (!row_ok) {
     // nothing to store for rows past M
@@ -315,7 +310,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int c = chunk_of(ci);
         uint32_t r[32];
         __syncwarp();
-        if (g.dbg == 2) continue;
         tmem_ld32(taddr + c * 32, r);
         pre_ok = next_ok;
 #pragma unroll
@@ -328,7 +322,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tmem_ld_wait();
         const int nc = n0 + c * 32;
-        if (g.dbg == 3) { if (r[0] == 0x12345678u && r[31] == 0x1u) reinterpret_cast<bf16*>(g.C)[0] = __float2bfloat16_rn(1.f); continue; }
         const bool tma_out = p.tma_store != 0 && p.splits == 1 && g.epi != EPI_F32;
         if (nc >= g.N || (!row_ok && !tma_out)) continue;   // on the TMA path the whole warp stays together
         uint8_t* sbuf = tma_out ? store_stage + (warp - 2) * 4096 : nullptr;
@@ -586,7 +579,6 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   if (!gemm_tc_supported(g)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "gemm_tc: shape/alignment not supported");
   TcParams p;
   p.g = g;
-  if (const char* e = getenv("FEMTO_DBG")) p.g.dbg = atoi(e);
   p.tiles_m = cdiv(g.M, BM);
   p.tiles_n = cdiv(g.N, BN);
   p.kblocks = cdiv(g.K, BK);
