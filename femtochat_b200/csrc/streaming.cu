@@ -303,33 +303,35 @@ __global__ void __launch_bounds__(256) k_qkv_post_bwd(T* __restrict__ dqkv, cons
 }
 
 
-// head_dim 128 specialisation: 16 lanes per (token, slot), 8 channels per lane (4 RoPE pairs), one
-// pass with the rotated values kept in registers, 8/16-byte loads and stores.
-__device__ __forceinline__ float half_warp_sum(float v) {
+// head_dim 128 specialisation: 8 lanes per (token, slot), 16 channels per lane (8 RoPE pairs), one pass
+// with the rotated values kept in registers and 16-byte (bf16) / 32-byte (fp32) accesses: with fewer bytes
+// per thread the kernel was bound by loads in flight, not by HBM.
+__device__ __forceinline__ float oct_sum(float v) {
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-template <typename T> __device__ __forceinline__ void load4(const T* p, float (&f)[4]) {
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
   if constexpr (sizeof(T) == 4) {
-    float4 v = *reinterpret_cast<const float4*>(p);
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    const float4 u = *reinterpret_cast<const float4*>(p), w = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w; f[4] = w.x; f[5] = w.y; f[6] = w.z; f[7] = w.w;
   } else {
-    uint2 v = *reinterpret_cast<const uint2*>(p);
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
     const bf16* h = reinterpret_cast<const bf16*>(&v);
 #pragma unroll
-    for (int i = 0; i < 4; i++) f[i] = __bfloat162float(h[i]);
+    for (int i = 0; i < 8; i++) f[i] = __bfloat162float(h[i]);
   }
 }
-template <typename T> __device__ __forceinline__ void store4(T* p, const float (&f)[4]) {
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
   if constexpr (sizeof(T) == 4) {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
   } else {
-    uint2 v;
+    uint4 v;
     bf16* h = reinterpret_cast<bf16*>(&v);
 #pragma unroll
-    for (int i = 0; i < 4; i++) h[i] = __float2bfloat16_rn(f[i]);
-    *reinterpret_cast<uint2*>(p) = v;
+    for (int i = 0; i < 8; i++) h[i] = __float2bfloat16_rn(f[i]);
+    *reinterpret_cast<uint4*>(p) = v;
   }
 }
 
@@ -341,49 +343,51 @@ __global__ void __launch_bounds__(256) k_qkv_post_128(T* __restrict__ qkv, long 
                                                       long long N, int H, int Hkv, float eps, float* __restrict__ rqk,
                                                       float* __restrict__ sv) {
   constexpr int hd = 128, half = 64;
-  const int sub = threadIdx.x & 15;
+  const int sub = threadIdx.x & 7;
   const int nslot = H + 2 * Hkv;
-  const long long w0 = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
-  const bool live = w0 < N * nslot;  // surplus half-warps recompute the last slot but never store
+  const long long w0 = (long long)blockIdx.x * 32 + (threadIdx.x >> 3);
+  const bool live = w0 < N * nslot;  // surplus groups recompute the last slot but never store
   const long long w = live ? w0 : N * nslot - 1;
   const long long n = w / nslot;
   const int slot = (int)(w % nslot);
   T* base = qkv + n * ldq + (long long)slot * hd;
   if (slot < H + Hkv) {
-    float x1[4], x2[4], cs[4], sn[4];
-    load4<T>(base + sub * 4, x1);
-    load4<T>(base + half + sub * 4, x2);
-    load4<float>(cos_t + (long long)pos[n] * half + sub * 4, cs);
-    load4<float>(sin_t + (long long)pos[n] * half + sub * 4, sn);
+    float x1[8], x2[8], cs[8], sn[8];
+    const long long tp = (long long)pos[n] * half + sub * 8;
+    load8<T>(base + sub * 8, x1);
+    load8<T>(base + half + sub * 8, x2);
+    load8<float>(cos_t + tp, cs);
+    load8<float>(sin_t + tp, sn);
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 8; i++) {
       const float c = round_to<T>(cs[i]), s = round_to<T>(sn[i]);
       const float y1 = round_to<T>(x1[i] * c + x2[i] * s), y2 = round_to<T>(-x1[i] * s + x2[i] * c);
       x1[i] = y1; x2[i] = y2;
       ss += y1 * y1 + y2 * y2;
     }
-    ss = half_warp_sum(ss);
+    ss = oct_sum(ss);
     const float rr = sqrtf(ss / hd + eps);
     if (live && sub == 0) rqk[n * (H + Hkv) + slot] = rr;
     const float g = 1.2f / rr;
 #pragma unroll
-    for (int i = 0; i < 4; i++) { x1[i] *= g; x2[i] *= g; }
-    if (live) store4<T>(base + sub * 4, x1);
-    if (live) store4<T>(base + half + sub * 4, x2);
+    for (int i = 0; i < 8; i++) { x1[i] *= g; x2[i] *= g; }
+    if (live) { store8<T>(base + sub * 8, x1); store8<T>(base + half + sub * 8, x2); }
   } else if (ve_table != nullptr) {
     const int kvh = slot - H - Hkv;
-    float pre = sub < 12 ? to_f<T>(xn1[n * D + sub]) * ve_gate[sub * Hkv + kvh] : 0.f;
-    pre = half_warp_sum(pre);
+    // gate input: the first 12 channels of the normed block input, two per lane for lanes 0-3
+    float pre = to_f<T>(xn1[n * D + sub]) * ve_gate[sub * Hkv + kvh];
+    if (sub < 4) pre += to_f<T>(xn1[n * D + sub + 8]) * ve_gate[(sub + 8) * Hkv + kvh];
+    pre = oct_sum(pre);
     const float sig = 1.f / (1.f + expf(-pre));
     if (live && sub == 0) sv[n * Hkv + kvh] = sig;
-    const T* ve = ve_table + (long long)tok0[n] * (Hkv * hd) + (long long)kvh * hd + sub * 8;
-    float a[4], b[4], e0[4], e1[4];
-    load4<T>(base + sub * 8, a); load4<T>(base + sub * 8 + 4, b);
-    load4<T>(ve, e0); load4<T>(ve + 4, e1);
+    const T* ve = ve_table + (long long)tok0[n] * (Hkv * hd) + (long long)kvh * hd + sub * 16;
+    float a[8], b[8], e0[8], e1[8];
+    load8<T>(base + sub * 16, a); load8<T>(base + sub * 16 + 8, b);
+    load8<T>(ve, e0); load8<T>(ve + 8, e1);
 #pragma unroll
-    for (int i = 0; i < 4; i++) { a[i] += 3.f * sig * e0[i]; b[i] += 3.f * sig * e1[i]; }
-    if (live) store4<T>(base + sub * 8, a); if (live) store4<T>(base + sub * 8 + 4, b);
+    for (int i = 0; i < 8; i++) { a[i] += 3.f * sig * e0[i]; b[i] += 3.f * sig * e1[i]; }
+    if (live) { store8<T>(base + sub * 16, a); store8<T>(base + sub * 16 + 8, b); }
   }
 }
 
@@ -395,47 +399,49 @@ __global__ void __launch_bounds__(256) k_qkv_post_bwd_128(T* __restrict__ dqkv, 
                                                           const float* __restrict__ rqk, const float* __restrict__ sv,
                                                           T* __restrict__ dve, float* __restrict__ dpre) {
   constexpr int hd = 128, half = 64;
-  const int sub = threadIdx.x & 15;
+  const int sub = threadIdx.x & 7;
   const int nslot = H + 2 * Hkv;
-  const long long w0 = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
-  const bool live = w0 < N * nslot;  // surplus half-warps recompute the last slot but never store
+  const long long w0 = (long long)blockIdx.x * 32 + (threadIdx.x >> 3);
+  const bool live = w0 < N * nslot;  // surplus groups recompute the last slot but never store
   const long long w = live ? w0 : N * nslot - 1;
   const long long n = w / nslot;
   const int slot = (int)(w % nslot);
   T* g = dqkv + n * ldq + (long long)slot * hd;
   const T* y = qkv + n * ldq + (long long)slot * hd;
   if (slot < H + Hkv) {
-    float g1[4], g2[4], y1[4], y2[4], cs[4], sn[4];
-    load4<T>(g + sub * 4, g1); load4<T>(g + half + sub * 4, g2);
-    load4<T>(y + sub * 4, y1); load4<T>(y + half + sub * 4, y2);
-    load4<float>(cos_t + (long long)pos[n] * half + sub * 4, cs);
-    load4<float>(sin_t + (long long)pos[n] * half + sub * 4, sn);
+    float g1[8], g2[8], y1[8], y2[8], cs[8], sn[8];
+    const long long tp = (long long)pos[n] * half + sub * 8;
+    const float rq = rqk[n * (H + Hkv) + slot];
+    load8<T>(g + sub * 8, g1); load8<T>(g + half + sub * 8, g2);
+    load8<T>(y + sub * 8, y1); load8<T>(y + half + sub * 8, y2);
+    load8<float>(cos_t + tp, cs);
+    load8<float>(sin_t + tp, sn);
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; i++) dot += g1[i] * y1[i] + g2[i] * y2[i];
-    dot = half_warp_sum(dot) / hd;
-    const float inv = 1.f / rqk[n * (H + Hkv) + slot];
+    for (int i = 0; i < 8; i++) dot += g1[i] * y1[i] + g2[i] * y2[i];
+    dot = oct_sum(dot) / hd;
+    const float inv = 1.f / rq;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 8; i++) {
       const float d1 = (1.2f * g1[i] - y1[i] * (1.f / 1.2f) * dot) * inv, d2 = (1.2f * g2[i] - y2[i] * (1.f / 1.2f) * dot) * inv;
       const float c = round_to<T>(cs[i]), s = round_to<T>(sn[i]);
       g1[i] = d1 * c - d2 * s;
       g2[i] = d1 * s + d2 * c;
     }
-    if (live) store4<T>(g + sub * 4, g1); if (live) store4<T>(g + half + sub * 4, g2);
+    if (live) { store8<T>(g + sub * 8, g1); store8<T>(g + half + sub * 8, g2); }
   } else if (ve_table != nullptr) {
     const int kvh = slot - H - Hkv;
-    const T* ve = ve_table + (long long)tok0[n] * (Hkv * hd) + (long long)kvh * hd + sub * 8;
+    const T* ve = ve_table + (long long)tok0[n] * (Hkv * hd) + (long long)kvh * hd + sub * 16;
     const float sig = sv[n * Hkv + kvh];
-    float a[4], b[4], e0[4], e1[4];
-    load4<T>(g + sub * 8, a); load4<T>(g + sub * 8 + 4, b);
-    load4<T>(ve, e0); load4<T>(ve + 4, e1);
+    float a[8], b[8], e0[8], e1[8];
+    load8<T>(g + sub * 16, a); load8<T>(g + sub * 16 + 8, b);
+    load8<T>(ve, e0); load8<T>(ve + 8, e1);
     float dg = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; i++) { dg += a[i] * e0[i] + b[i] * e1[i]; a[i] *= 3.f * sig; b[i] *= 3.f * sig; }
-    T* out = dve + n * (Hkv * hd) + (long long)kvh * hd + sub * 8;
-    if (live) store4<T>(out, a); if (live) store4<T>(out + 4, b);
-    dg = half_warp_sum(dg);
+    for (int i = 0; i < 8; i++) { dg += a[i] * e0[i] + b[i] * e1[i]; a[i] *= 3.f * sig; b[i] *= 3.f * sig; }
+    T* out = dve + n * (Hkv * hd) + (long long)kvh * hd + sub * 16;
+    if (live) { store8<T>(out, a); store8<T>(out + 8, b); }
+    dg = oct_sum(dg);
     if (live && sub == 0) dpre[n * Hkv + kvh] = dg * 3.f * sig * (1.f - sig);
   }
 }
@@ -892,8 +898,8 @@ int Stream<T>::qkv_post(T* qkv, long long ldq, const T* xn1, int D, const float*
                         const int* tok0, const int* pos, const float* sin_t, const float* cos_t, int N, int H,
                         int Hkv, int hd, float eps, float* rqk, float* sv, cudaStream_t s) {
   long long warps = (long long)N * (H + 2 * Hkv);
-  if (hd == 128 && ldq % 4 == 0 && D % 4 == 0)
-    k_qkv_post_128<T><<<cdiv(warps, 16), 256, 0, s>>>(qkv, ldq, xn1, D, ve_gate, ve_table, tok0, pos, sin_t, cos_t, N, H,
+  if (hd == 128 && ldq % 8 == 0 && aligned16(qkv) && (!ve_table || aligned16(ve_table)))
+    k_qkv_post_128<T><<<cdiv(warps, 32), 256, 0, s>>>(qkv, ldq, xn1, D, ve_gate, ve_table, tok0, pos, sin_t, cos_t, N, H,
                                                      Hkv, eps, rqk, sv);
   else
     k_qkv_post<T><<<cdiv(warps, WPB), 256, 0, s>>>(qkv, ldq, xn1, D, ve_gate, ve_table, tok0, pos, sin_t, cos_t, N, H,
@@ -906,8 +912,8 @@ int Stream<T>::qkv_post_bwd(T* dqkv, const T* qkv, long long ldq, const T* ve_ta
                             const int* pos, const float* sin_t, const float* cos_t, int N, int H, int Hkv, int hd,
                             const float* rqk, const float* sv, T* dve, float* dpre, cudaStream_t s) {
   long long warps = (long long)N * (H + 2 * Hkv);
-  if (hd == 128 && ldq % 4 == 0)
-    k_qkv_post_bwd_128<T><<<cdiv(warps, 16), 256, 0, s>>>(dqkv, qkv, ldq, ve_table, tok0, pos, sin_t, cos_t, N, H, Hkv,
+  if (hd == 128 && ldq % 8 == 0 && aligned16(qkv) && aligned16(dqkv) && (!ve_table || (aligned16(ve_table) && aligned16(dve))))
+    k_qkv_post_bwd_128<T><<<cdiv(warps, 32), 256, 0, s>>>(dqkv, qkv, ldq, ve_table, tok0, pos, sin_t, cos_t, N, H, Hkv,
                                                          rqk, sv, dve, dpre);
   else
     k_qkv_post_bwd<T><<<cdiv(warps, WPB), 256, 0, s>>>(dqkv, qkv, ldq, ve_table, tok0, pos, sin_t, cos_t, N, H, Hkv,
