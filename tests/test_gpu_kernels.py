@@ -74,7 +74,9 @@ def _attn_inputs(dtype, B, T, H, Hkv, hd, seed, docs):
 @pytest.mark.parametrize("dtype,B,T,H,Hkv,hd,left,docs", [
     (_lib.F32, 2, 40, 4, 2, 16, 40, False), (_lib.F32, 2, 40, 4, 1, 16, 7, True), (_lib.F32, 1, 33, 2, 2, 64, 33, False),
     (_lib.BF16, 2, 256, 4, 2, 128, 256, False), (_lib.BF16, 2, 512, 4, 2, 128, 100, True),
-    (_lib.BF16, 1, 1024, 10, 5, 128, 300, True), (_lib.BF16, 2, 96, 2, 1, 64, 30, False)])
+    (_lib.BF16, 1, 1024, 10, 5, 128, 300, True), (_lib.BF16, 2, 96, 2, 1, 64, 30, False),
+    # one query head per kv head (the single-head forward kernel) and four per kv head (two CTAs per group)
+    (_lib.BF16, 2, 384, 3, 3, 128, 200, True), (_lib.BF16, 1, 512, 8, 2, 128, 512, False)])
 def test_attention_forward_and_reverse(dtype, B, T, H, Hkv, hd, left, docs):
     """attention! / Δattention! against naive_attention (src/kernels.jl:59-96) and the blockwise reverse."""
     Q, K, V, dO, ds = _attn_inputs(dtype, B, T, H, Hkv, hd, seed=T + hd, docs=docs)
