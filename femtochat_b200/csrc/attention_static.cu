@@ -1,7 +1,8 @@
 // Attention reverse pass for callers that must not allocate device memory.
 //
 // femto_attention_bwd takes its scratch (the per-row terms D = rowsum(dO * O) and lse * log2(e), two
-// floats per (batch, head, query)) from cudaMalloc on every call.  Some callers cannot do that: a host runtime
+// floats per (batch, head, query)) from a buffer that it allocates with cudaMalloc on its first call and again
+// whenever a larger one is needed.  Some callers cannot do that: a host runtime
 // that has handed all device memory to its own pool (XLA-style allocators, a Julia session with a
 // capped CUDA.jl pool), or code that runs while allocation is forbidden or would synchronise the
 // device.  For them the scratch below is compiled into the library image: every GPU that loads the

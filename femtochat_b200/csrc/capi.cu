@@ -23,6 +23,22 @@ int newton_schulz_t(T* S, T* S2, T* A, T* B2, int k, int in, int out, const floa
 
 static std::string g_create_err;
 
+int standalone_scratch(size_t bytes, char** out) {
+  static char* buf[64] = {nullptr};
+  static size_t cap[64] = {0};
+  int dev = -1;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return femto_fail(FEMTO_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  if (cap[dev] < bytes) {
+    if (buf[dev]) { cudaDeviceSynchronize(); cudaFree(buf[dev]); buf[dev] = nullptr; cap[dev] = 0; }
+    cudaError_t e = cudaMalloc(&buf[dev], bytes);
+    if (e != cudaSuccess) return femto_fail(FEMTO_ERR_NOMEM, "cudaMalloc of %zu bytes of scratch failed: %s", bytes, cudaGetErrorString(e));
+    cap[dev] = bytes;
+  }
+  *out = buf[dev];
+  return 0;
+}
+
 static int require_device() {
   int n = 0;
   cudaError_t e = cudaGetDeviceCount(&n);
@@ -229,12 +245,11 @@ int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const v
   a.lse = const_cast<float*>(lse); a.dO = dO; a.dQ = dQ; a.dK = dK; a.dV = dV;
   a.do_stride = a.q_stride; a.dq_stride = a.q_stride; a.dkv_stride = a.kv_stride;
   size_t need = std::max(sizeof(float) * (size_t)B * H * T * 2, attention_bwd_tc_ws_bytes(B, T, H, hd));
-  void* ws = nullptr;
-  CUDA_TRY(cudaMalloc(&ws, need));
+  char* ws = nullptr;
+  FEMTO_TRY(standalone_scratch(need, &ws));
   a.ws = ws; a.ws_bytes = need;
   int r = dtype == FEMTO_BF16 ? attention_bwd<bf16>(a, (cudaStream_t)stream) : attention_bwd<float>(a, (cudaStream_t)stream);
   cudaStreamSynchronize((cudaStream_t)stream);
-  cudaFree(ws);
   return r;
 }
 
@@ -249,13 +264,12 @@ int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void
   g.M = M; g.N = N; g.K = K; g.batch = batch < 1 ? 1 : batch; g.strideA = strideA; g.strideB = strideB; g.strideC = strideC;
   g.epi = out_f32 ? EPI_F32 : EPI_STORE; g.beta = accumulate ? 1.f : 0.f;
   if (!out_f32) return gemm<bf16>(g, (cudaStream_t)stream);  // asynchronous, no scratch
-  void* ws = nullptr;  // split-K partials of the fp32 form
+  char* ws = nullptr;  // split-K partials of the fp32 form
   const size_t wsb = (size_t)160 << 20;
-  CUDA_TRY(cudaMalloc(&ws, wsb));
+  FEMTO_TRY(standalone_scratch(wsb, &ws));
   g.ws = ws; g.ws_bytes = wsb;
   int r = gemm<bf16>(g, (cudaStream_t)stream);
   cudaStreamSynchronize((cudaStream_t)stream);
-  cudaFree(ws);
   return r;
 }
 
@@ -263,14 +277,23 @@ int32_t femto_embedding_gradient(int32_t dtype, float* table, const void* dy, co
                                  int32_t D, int32_t rows, void* stream) {
   FEMTO_TRY(require_device());
   if (!table || !dy || !tokens0 || N <= 0 || D <= 0 || rows <= 0) return femto_fail(FEMTO_ERR_ARG, "bad argument");
-  ScatterPlan* p = nullptr;
-  FEMTO_TRY(scatter_plan_create(&p, N, D));
+  // the sort / run-length plan's buffers are kept per device and re-created only for a larger problem
+  static ScatterPlan* plan[64] = {nullptr};
+  static int plan_n[64] = {0}, plan_d[64] = {0};
+  int dev = -1;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return femto_fail(FEMTO_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  if (!plan[dev] || plan_n[dev] < N || plan_d[dev] < D) {
+    if (plan[dev]) { cudaDeviceSynchronize(); scatter_plan_destroy(plan[dev]); plan[dev] = nullptr; }
+    FEMTO_TRY(scatter_plan_create(&plan[dev], std::max(N, plan_n[dev]), std::max(D, plan_d[dev])));
+    plan_n[dev] = std::max(N, plan_n[dev]); plan_d[dev] = std::max(D, plan_d[dev]);
+  }
+  ScatterPlan* p = plan[dev];
   cudaStream_t s = (cudaStream_t)stream;
   int r = scatter_plan_build(p, tokens0, N, rows, s);
   if (!r) r = dtype == FEMTO_BF16 ? scatter_rows<bf16>(p, table, (const bf16*)dy, D, D, s)
                                   : scatter_rows<float>(p, table, (const float*)dy, D, D, s);
   cudaStreamSynchronize(s);
-  scatter_plan_destroy(p);
   return r;
 }
 
@@ -290,7 +313,7 @@ int32_t femto_newton_schulz(int32_t dtype, void* X, int32_t k, int32_t rows, int
   const size_t wsb = (size_t)160 << 20;
   char* buf = nullptr;
   auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
-  CUDA_TRY(cudaMalloc(&buf, al(es * per * k) + 2 * al(es * r * r * k) + wsb + 256));
+  FEMTO_TRY(standalone_scratch(al(es * per * k) + 2 * al(es * r * r * k) + wsb + 256, &buf));
   void* S2 = buf;
   void* A = buf + al(es * per * k);
   void* B2 = (char*)A + al(es * r * r * k);
@@ -301,7 +324,6 @@ int32_t femto_newton_schulz(int32_t dtype, void* X, int32_t k, int32_t rows, int
                ? newton_schulz_t<bf16>((bf16*)X, (bf16*)S2, (bf16*)A, (bf16*)B2, k, rows, cols, coeffs, steps, ws, wsb, nullptr, s)
                : newton_schulz_t<float>((float*)X, (float*)S2, (float*)A, (float*)B2, k, rows, cols, coeffs, steps, ws, wsb, nullptr, s);
   cudaStreamSynchronize(s);
-  cudaFree(buf);
   return rc;
 }
 

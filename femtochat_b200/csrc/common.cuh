@@ -124,6 +124,9 @@ struct GemmArgs {
   // fp32 split output: up to 3 column segments of C go to different destinations (fused QKV dW).
   int nseg = 0; int seg_col0[3] = {0, 0, 0}; int seg_ncol[3] = {0, 0, 0};
   float* seg_ptr[3] = {nullptr, nullptr, nullptr}; long long seg_ld[3] = {0, 0, 0};
+  // square symmetric result: tiles that lie entirely below the diagonal are not computed (the caller mirrors
+  // the upper triangle afterwards); honoured by the tensor-core kernel, ignored by the SIMT fallback
+  bool upper_only = false;
   // cross-entropy statistics epilogue
   const int* targets0 = nullptr;   // [M] 0-based target or -1
   float2* stats = nullptr;         // [M][2 * ntiles_n] partial (max, sumexp)
@@ -174,6 +177,12 @@ int scatter_rows(ScatterPlan* p, float* table, const T* dy, long long dy_stride,
 // out[j] (+)= sum_i partial[i*ncol + j], one block, fixed order.
 int reduce_partials(const float* partial, int nrow, int ncol, float* out, const float* scale_dev,
                     float scale, bool accumulate, cudaStream_t s);
+
+// Scratch of the stand-alone kernel-level entry points (femto_attention_bwd, femto_gemm_bf16 with fp32 output,
+// femto_xent_fused, femto_newton_schulz, femto_cross_entropy*): one grow-only buffer per device, kept until the
+// process exits.  cudaMalloc / cudaFree on every call cost more than the kernels.  Those entry points synchronise
+// before returning, so consecutive calls may share it; calls from several host threads at once may not.
+int standalone_scratch(size_t bytes, char** out);
 
 // ---- lm_head tail ------------------------------------------------------------------------------
 // loss rows and (optionally) dX, dW of sum_valid(logsumexp(z) - z[target]), z = 15 tanh(xW/15),

@@ -98,6 +98,11 @@ __device__ __forceinline__ void stage_store_bf16(const float (&v)[32], uint8_t* 
   }
 }
 
+// Tiles of a symmetric result that no element of the upper triangle touches (every role skips the same units).
+__device__ __forceinline__ bool below_diagonal(const GemmArgs& g, int mt, int nt) {
+  return g.upper_only && (nt + 1) * BN <= mt * BM;
+}
+
 // One 32-column chunk of one output row with a bf16 result: C = f(acc, aux).
 template <int EPI>
 __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], int bz, int m, int nc, bool full_chunk,
@@ -210,6 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         int bz, mt, nt, kb0, kb1;
         unit_coords(u, bz, mt, nt, kb0, kb1);
+        if (below_diagonal(g, mt, nt)) continue;
         for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, g.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -249,6 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
         int bz, mt, nt, kb0, kb1;
         unit_coords(u, bz, mt, nt, kb0, kb1);
+        if (below_diagonal(g, mt, nt)) continue;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, g.status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -283,6 +290,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
       int bz, mt, nt, kb0, kb1;
       unit_coords(u, bz, mt, nt, kb0, kb1);
+      if (below_diagonal(g, mt, nt)) continue;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, g.status)) break;
       tc_fence_after();
       const int m = mt * BM + row_in_tile;

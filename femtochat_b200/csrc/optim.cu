@@ -201,6 +201,32 @@ int adamw_launch(float* theta, const float* delta, float* m, float* v, long long
   return 0;
 }
 
+// C[b][i][j] = C[b][j][i] for i > j on a stack of r x r matrices: completes a symmetric product of which only the
+// tiles touching the upper triangle were computed.  32 x 32 tiles through shared memory, one block per tile pair.
+template <typename T>
+__global__ void __launch_bounds__(256) k_mirror_upper(T* __restrict__ C, int r, long long stride) {
+  __shared__ float tile[32][33];
+  const int bi = blockIdx.y, bj = blockIdx.x;   // destination tile (rows bi, cols bj), bi >= bj
+  if (bj > bi) return;
+  T* M = C + (long long)blockIdx.z * stride;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int y = ty; y < 32; y += 8) {            // source tile: rows bj*32.., cols bi*32..
+    const int sr = bj * 32 + y, sc = bi * 32 + tx;
+    tile[y][tx] = (sr < r && sc < r) ? to_f<T>(M[(long long)sr * r + sc]) : 0.f;
+  }
+  __syncthreads();
+  for (int y = ty; y < 32; y += 8) {
+    const int dr = bi * 32 + y, dc = bj * 32 + tx;
+    if (dr < r && dc < r && dr > dc) M[(long long)dr * r + dc] = from_f<T>(tile[tx][y]);
+  }
+}
+template <typename T> int mirror_upper(T* C, int r, long long stride, int k, cudaStream_t s) {
+  const int nb = cdiv(r, 32);
+  k_mirror_upper<T><<<dim3(nb, nb, k), 256, 0, s>>>(C, r, stride);
+  KERNEL_CHECK();
+  return 0;
+}
+
 // Polar Express on a stack S[k][in][out] of type T, in place (result left in S).  scratch: S2 like S,
 // A and B2 [k][r][r].
 template <typename T>
@@ -219,14 +245,18 @@ int newton_schulz_t(T* S, T* S2, T* A, T* B2, int k, int in, int out, const floa
     g.A = cur; g.B = cur; g.lda = out; g.ldb = out; g.strideA = per; g.strideB = per;
     g.a_kmajor = tall; g.b_kmajor = tall;
     g.C = A; g.ldc = r; g.strideC = rr; g.M = r; g.N = r; g.K = tall ? out : in; g.epi = EPI_STORE;
+    g.upper_only = true;   // X X^T is symmetric: compute the tiles on and above the diagonal, mirror the rest
     FEMTO_TRY(gemm<T>(g, s));
+    FEMTO_TRY(mirror_upper<T>(A, r, rr, k, s));
     // B2 = b A + c A A
     GemmArgs g2;
     g2.ws = ws; g2.ws_bytes = ws_bytes; g2.status = status; g2.batch = k;
     g2.A = A; g2.B = A; g2.lda = r; g2.ldb = r; g2.strideA = rr; g2.strideB = rr; g2.a_kmajor = true; g2.b_kmajor = true;
     g2.C = B2; g2.ldc = r; g2.strideC = rr; g2.M = r; g2.N = r; g2.K = r;
     g2.epi = EPI_AXPBY; g2.aux = A; g2.ldaux = r; g2.strideAux = rr; g2.alpha = b; g2.beta = c;
+    g2.upper_only = true;  // a polynomial of a symmetric matrix is symmetric
     FEMTO_TRY(gemm<T>(g2, s));
+    FEMTO_TRY(mirror_upper<T>(B2, r, rr, k, s));
     // X' = a X + B2 X   (stored orientation: S' = a S + B2 S when tall, S' = a S + S B2 otherwise)
     GemmArgs g3;
     g3.ws = ws; g3.ws_bytes = ws_bytes; g3.status = status; g3.batch = k;

@@ -76,7 +76,7 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   size_t total = al(need_f32 ? 4 * (size_t)chunk * ldw : 0) + al(sizeof(float2) * (size_t)chunk * (2 * ((V + 255) / 256) + 2)) +
                  3 * al(4 * (size_t)N) + al(es * (size_t)chunk * ldw) + wsb + 1024;
   char* buf = nullptr;
-  CUDA_TRY(cudaMalloc(&buf, total));
+  FEMTO_TRY(standalone_scratch(total, &buf));
   char* p = buf;
   XentArgs a;
   a.x = x; a.W = W; a.ldw = ldw; a.targets0 = targets0; a.N = N; a.D = D; a.V = V; a.scale = scale;
@@ -91,7 +91,6 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   int r = dtype == FEMTO_BF16 ? xent_tail<bf16>(a, s) : xent_tail<float>(a, s);
   if (!r) r = sum_rows_to_scalar(a.loss_rows, N, loss_out, targets0, n_valid_out, 0.f, s);
   cudaStreamSynchronize(s);
-  cudaFree(buf);
   return r;
 }
 
@@ -160,14 +159,14 @@ extern "C" int32_t femto_cross_entropy(const float* logits, int64_t ldl, const i
     if (n_valid_out) { k_count_valid<<<1, 1024, 0, s>>>(targets0, N, n_valid_out); KERNEL_CHECK(); }
     return 0;
   }
-  float* rows = nullptr;
-  CUDA_TRY(cudaMalloc(&rows, sizeof(float) * (size_t)N));
+  char* scratch = nullptr;
+  FEMTO_TRY(standalone_scratch(sizeof(float) * (size_t)N, &scratch));
+  float* rows = reinterpret_cast<float*>(scratch);
   k_ce_rows<false><<<N, 256, 0, s>>>(logits, ldl, targets0, V, rows, nullptr, 0, 0.f, nullptr, nullptr);
   int r = 0;
   { cudaError_t e = cudaGetLastError(); if (e != cudaSuccess) r = femto_fail((int)e, "cross-entropy kernel launch failed: %s", cudaGetErrorString(e)); }
   if (!r) r = sum_rows_to_scalar(rows, N, out, targets0, n_valid_out, reduction == FEMTO_REDUCTION_MEAN ? 1.f : 0.f, s);
   cudaStreamSynchronize(s);
-  cudaFree(rows);
   return r;
 }
 
@@ -180,13 +179,15 @@ extern "C" int32_t femto_cross_entropy_gradient(float* delta, int64_t ldd, const
   cudaStream_t s = (cudaStream_t)stream;
   int* nv = nullptr;
   if (reduction == FEMTO_REDUCTION_MEAN) {
-    CUDA_TRY(cudaMalloc(&nv, sizeof(int)));
+    char* scratch = nullptr;
+    FEMTO_TRY(standalone_scratch(256, &scratch));
+    nv = reinterpret_cast<int*>(scratch);
     k_count_valid<<<1, 1024, 0, s>>>(targets0, N, nv);
   }
   k_ce_rows<true><<<N, 256, 0, s>>>(logits, ldl, targets0, V, nullptr, delta, ldd, dy,
                                     reduction == FEMTO_REDUCTION_NONE ? dy_rows : nullptr, nv);
   int r = 0;
   { cudaError_t e = cudaGetLastError(); if (e != cudaSuccess) r = femto_fail((int)e, "cross-entropy gradient launch failed: %s", cudaGetErrorString(e)); }
-  if (nv) { cudaStreamSynchronize(s); cudaFree(nv); }
+  if (nv) cudaStreamSynchronize(s);
   return r;
 }

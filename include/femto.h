@@ -197,7 +197,7 @@ int32_t femto_embedding_gradient(int32_t dtype, float* delta_table, const void* 
 /* cross_entropy(logits, targets, ignore, reduction) on materialised logits (src/gpt.jl:175-193; the
  * reference's GPU method ext/FemtoChatCUDAExt.jl:49-55): logits fp32 [N][ldl] (the (V,T,B) array, first V
  * columns used), targets0 0-based or -1.  out: one float (sum / mean over valid targets) or [N] floats
- * (FEMTO_REDUCTION_NONE, ignored rows 0).  Synchronises for sum / mean (scratch is allocated per call). */
+ * (FEMTO_REDUCTION_NONE, ignored rows 0).  Synchronises for sum / mean (its scratch is a grow-only buffer that the library keeps per device). */
 int32_t femto_cross_entropy(const float* logits, int64_t ldl, const int32_t* targets0, int32_t N, int32_t V,
                             int32_t reduction, float* out, int32_t* n_valid_out, void* stream);
 /* cross_entropy_gradient!(delta, logits, targets, dy, ignore, reduction) (src/kernels.jl:16-28; GPU method
