@@ -202,27 +202,64 @@ int adamw_launch(float* theta, const float* delta, float* m, float* v, long long
 }
 
 // C[b][i][j] = C[b][j][i] for i > j on a stack of r x r matrices: completes a symmetric product of which only the
-// tiles touching the upper triangle were computed.  32 x 32 tiles through shared memory, one block per tile pair.
+// tiles touching the upper triangle were computed.  64 x 64 tiles through shared memory, one block per tile pair.
 template <typename T>
-__global__ void __launch_bounds__(256) k_mirror_upper(T* __restrict__ C, int r, long long stride) {
-  __shared__ float tile[32][33];
-  const int bi = blockIdx.y, bj = blockIdx.x;   // destination tile (rows bi, cols bj), bi >= bj
-  if (bj > bi) return;
-  T* M = C + (long long)blockIdx.z * stride;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  for (int y = ty; y < 32; y += 8) {            // source tile: rows bj*32.., cols bi*32..
-    const int sr = bj * 32 + y, sc = bi * 32 + tx;
+__global__ void __launch_bounds__(256) k_mirror_upper(T* __restrict__ C, int r, long long stride, int nb) {
+  __shared__ float tile[64][65];
+  // blockIdx.x enumerates the tile pairs (bi >= bj) of the lower triangle, 64 x 64 elements each
+  int bi = (int)((sqrtf(8.f * blockIdx.x + 1.f) - 1.f) * 0.5f);
+  while ((bi + 1) * (bi + 2) / 2 <= (int)blockIdx.x) bi++;
+  while (bi * (bi + 1) / 2 > (int)blockIdx.x) bi--;
+  const int bj = blockIdx.x - bi * (bi + 1) / 2;
+  if (bi >= nb) return;
+  T* M = C + (long long)blockIdx.y * stride;
+  if ((r & 1) == 0) {
+    // two adjacent columns per thread: a warp moves one 64-element row (128 bytes of bf16) per access
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int y = w; y < 64; y += 8) {            // source tile: rows bj*64.., cols bi*64..
+      const int sr = bj * 64 + y, sc = bi * 64 + 2 * lane;
+      float a = 0.f, b = 0.f;
+      if (sr < r && sc < r) {                    // r even: sc + 1 < r as well
+        const T* src = M + (long long)sr * r + sc;
+        if constexpr (sizeof(T) == 2) {
+          const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(src);
+          a = __bfloat162float(v.x); b = __bfloat162float(v.y);
+        } else {
+          const float2 v = *reinterpret_cast<const float2*>(src);
+          a = v.x; b = v.y;
+        }
+      }
+      tile[y][2 * lane] = a; tile[y][2 * lane + 1] = b;
+    }
+    __syncthreads();
+    for (int y = w; y < 64; y += 8) {
+      const int dr = bi * 64 + y, dc = bj * 64 + 2 * lane;
+      if (dr >= r || dc >= r || dr <= dc) continue;      // on or above the diagonal: keep what the GEMM wrote
+      T* dst = M + (long long)dr * r + dc;
+      const float a = tile[2 * lane][y], b = tile[2 * lane + 1][y];
+      if (dr > dc + 1) {
+        if constexpr (sizeof(T) == 2) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
+        else *reinterpret_cast<float2*>(dst) = make_float2(a, b);
+      } else {
+        dst[0] = from_f<T>(a);                            // dr == dc + 1: the second column is the diagonal
+      }
+    }
+    return;
+  }
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  for (int y = ty; y < 64; y += 4) {            // source tile: rows bj*64.., cols bi*64..
+    const int sr = bj * 64 + y, sc = bi * 64 + tx;
     tile[y][tx] = (sr < r && sc < r) ? to_f<T>(M[(long long)sr * r + sc]) : 0.f;
   }
   __syncthreads();
-  for (int y = ty; y < 32; y += 8) {
-    const int dr = bi * 32 + y, dc = bj * 32 + tx;
+  for (int y = ty; y < 64; y += 4) {
+    const int dr = bi * 64 + y, dc = bj * 64 + tx;
     if (dr < r && dc < r && dr > dc) M[(long long)dr * r + dc] = from_f<T>(tile[tx][y]);
   }
 }
 template <typename T> int mirror_upper(T* C, int r, long long stride, int k, cudaStream_t s) {
-  const int nb = cdiv(r, 32);
-  k_mirror_upper<T><<<dim3(nb, nb, k), 256, 0, s>>>(C, r, stride);
+  const int nb = cdiv(r, 64);
+  k_mirror_upper<T><<<dim3(nb * (nb + 1) / 2, k), 256, 0, s>>>(C, r, stride, nb);
   KERNEL_CHECK();
   return 0;
 }
