@@ -32,6 +32,7 @@ struct TcParams {
   int tiles_m, tiles_n, kblocks, splits, kb_per_split, total_units;
   float* partial;  // [unit][8 chunks][128 rows][32 cols] when splits > 1
   int tma_store;   // bf16 results leave through shared memory and TMA tiled stores
+  int a_slabs, b_slabs;  // an M/N-contiguous operand arrives with one 4-d copy per k-block instead of one per 64-wide slab
 };
 
 // Tile rasterisation: groups of GROUP_M row-tiles are walked column by column, so one wave of CTAs
@@ -223,12 +224,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           if (A_K) {
             tma_load_3d(sa, &tmA, &full[stage], kb * BK, mt * BM, bz);
+          } else if (p.a_slabs) {
+            tma_load_4d(sa, &tmA, &full[stage], 0, kb * BK, mt * (BM / 64), bz);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; j++) tma_load_3d(sa + j * 8192, &tmA, &full[stage], mt * BM + j * 64, kb * BK, bz);
           }
           if (B_K) {
             tma_load_3d(sb, &tmB, &full[stage], kb * BK, nt * BN, bz);
+          } else if (p.b_slabs) {
+            tma_load_4d(sb, &tmB, &full[stage], 0, kb * BK, nt * (BN / 64), bz);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; j++) tma_load_3d(sb + j * 8192, &tmB, &full[stage], nt * BN + j * 64, kb * BK, bz);
@@ -505,6 +510,20 @@ int make_tmap_3d_bf16_sw(CUtensorMap* out, const void* base, uint64_t dim0, uint
   return 0;
 }
 
+int make_tmap_4d_slabs_bf16(CUtensorMap* out, const void* base, uint64_t extent, uint64_t K, uint64_t batch, uint64_t ld_elems,
+                            uint64_t batch_stride_elems, uint32_t box_k, uint32_t slabs) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc || (extent & 63)) return 1;
+  cuuint64_t dims[4] = {64, K, extent / 64, batch ? batch : 1};
+  cuuint64_t strides[3] = {ld_elems * 2, 128, (batch > 1 ? batch_stride_elems : ld_elems * K) * 2};
+  cuuint32_t box[4] = {64, box_k, slabs, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1;
+}
+
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_elems,
                       uint32_t box0, uint32_t box1) {
   PFN_encodeTiled enc = get_encode();
@@ -612,9 +631,12 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
 
   CUtensorMap tmA, tmB;
   const int nb = g.batch;
+  p.a_slabs = p.b_slabs = 0;
   if (g.a_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.K, g.M, nb, g.lda, g.strideA, 64, BM));
+  else if (make_tmap_4d_slabs_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, BK, BM / 64) == 0) p.a_slabs = 1;
   else FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, 64, BK));
   if (g.b_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.K, g.N, nb, g.ldb, g.strideB, 64, BN));
+  else if (make_tmap_4d_slabs_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, BK, BN / 64) == 0) p.b_slabs = 1;
   else FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, 64, BK));
 
   CUtensorMap tmC = tmA;
