@@ -363,6 +363,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 *reinterpret_cast<float4*>(dst + j) = o;
               }
+            } else if (g.nseg == 0 && full_chunk && (reinterpret_cast<uintptr_t>(dst) & 15) == 8) {
+              // delta ranges start at even element offsets: an 8-byte aligned row is handled as 2 + 7 x 4 + 2 floats
+              auto rmw2 = [&](int j) {
+                float2 o = make_float2(g.alpha * v[j], g.alpha * v[j + 1]);
+                if (g.beta != 0.f) { const float2 q = *reinterpret_cast<const float2*>(dst + j); o.x += q.x; o.y += q.y; }
+                *reinterpret_cast<float2*>(dst + j) = o;
+              };
+              rmw2(0);
+#pragma unroll
+              for (int j = 2; j < 30; j += 4) {
+                float4 o = make_float4(g.alpha * v[j], g.alpha * v[j + 1], g.alpha * v[j + 2], g.alpha * v[j + 3]);
+                if (g.beta != 0.f) {
+                  float4 q = *reinterpret_cast<const float4*>(dst + j);
+                  o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
+              rmw2(30);
             } else {
 #pragma unroll
               for (int j = 0; j < 32; j++) {
@@ -445,23 +463,34 @@ __global__ void __launch_bounds__(256) gemm_tc_reduce_kernel(const TcParams p) {
       const float4 q = *reinterpret_cast<const float4*>(src + s * sstride);
       acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
     }
-    float* dst4 = reinterpret_cast<float*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + n;
-    // delta ranges start at arbitrary element offsets: vector access only when the address is 16-byte aligned
-    if (g.nseg == 0 && n + 3 < g.N && (reinterpret_cast<uintptr_t>(dst4) & 15) == 0) {
-      float* dst = dst4;
-      float4 o = make_float4(g.alpha * acc.x, g.alpha * acc.y, g.alpha * acc.z, g.alpha * acc.w);
+    // destination of the four columns: one range of delta, or one of the segments of a fused product (segment
+    // boundaries are multiples of 4 in practice, checked here).  delta ranges start at even element offsets, so the
+    // address is 16-byte aligned or 8-byte aligned; both get vector accesses.
+    float* dst = g.nseg == 0 ? reinterpret_cast<float*>(g.C) + (long long)bz * g.strideC + (long long)m * g.ldc + n
+                             : f32_dst(g, bz, m, n);
+    const bool contiguous = dst != nullptr && n + 3 < g.N && (g.nseg == 0 || f32_dst(g, bz, m, n + 3) == dst + 3);
+    const uintptr_t ph = reinterpret_cast<uintptr_t>(dst) & 15;
+    float4 o = make_float4(g.alpha * acc.x, g.alpha * acc.y, g.alpha * acc.z, g.alpha * acc.w);
+    if (contiguous && ph == 0) {
       if (g.beta != 0.f) {
         const float4 q = *reinterpret_cast<const float4*>(dst);
         o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w;
       }
       *reinterpret_cast<float4*>(dst) = o;
+    } else if (contiguous && ph == 8) {
+      if (g.beta != 0.f) {
+        const float2 q0 = *reinterpret_cast<const float2*>(dst), q1 = *reinterpret_cast<const float2*>(dst + 2);
+        o.x += q0.x; o.y += q0.y; o.z += q1.x; o.w += q1.y;
+      }
+      *reinterpret_cast<float2*>(dst) = make_float2(o.x, o.y);
+      *reinterpret_cast<float2*>(dst + 2) = make_float2(o.z, o.w);
     } else {
       const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         if (n + j < g.N) {
-          float* dst = f32_dst(g, bz, m, n + j);
-          if (dst) *dst = (g.beta != 0.f ? *dst : 0.f) + g.alpha * vals[j];
+          float* d1 = f32_dst(g, bz, m, n + j);
+          if (d1) *d1 = (g.beta != 0.f ? *d1 : 0.f) + g.alpha * vals[j];
         }
       }
     }
