@@ -195,6 +195,8 @@ def run_ours(args):
     if world > 1 and args.overlap:
         _lib.check(_lib.lib().femto_set_overlap(st.h, 1))   # one micro-step per update: reduce delta while the reverse pass runs
     opt = fb.MuonAdamW(params, lay, st, compute_type="bfloat16", weight_decay=0.01)
+    if world > 1 and args.shard_optimizer:
+        opt.shard(rank, world)   # each rank updates its share of Theta, then the shares are exchanged
     total = args.steps + args.warmup
     pk = fb.PackedBatches(cfg.vocab_size, T, B, max_document_tokens=cfg.max_document_tokens, rank=rank)
     host = []
@@ -272,6 +274,14 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
     status = st.status_word()
+    # Theta must still be the same on every rank (the sharded update exchanges each rank's share)
+    replicated = True
+    if world > 1:
+        cs = torch.stack([params.theta.sum(dtype=torch.float64), params.theta.abs().sum(dtype=torch.float64)])
+        hi, lo = cs.clone(), cs.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        replicated = bool((hi == lo).all().item())
     if rank == 0:
         tokens = B * T * world * args.steps
         value = tokens / (ms / 1e3)
@@ -285,7 +295,9 @@ def run_ours(args):
             config=dict(workload=f"{args.config} GPT training step (forward, reverse, grad sync, Muon+AdamW), "
                                  f"B={B} x T={T} per GPU, short window {spec['short_window'] or 'reference rule'}, "
                                  f"document mask on",
-                        parallelism=f"dp{world}", l2="inputs and activations per step far exceed the 126 MB L2",
+                        parallelism=f"dp{world}",
+                        optimizer=("owner-sharded" if world > 1 and args.shard_optimizer else "replicated"),
+                        theta_replicated=replicated, l2="inputs and activations per step far exceed the 126 MB L2",
                         mfu_nominal_2p25e15=value * flops_tok / (world * 2.25e15), flops_per_token=flops_tok,
                         loss_per_token=final_loss, device_status=status),
             e2e=dict(value=tokens / (ms_e2e / 1e3), unit="tokens/s", h2d_bytes_per_step=3 * 4 * B * T,
@@ -323,6 +335,9 @@ def main():
                          "(measured equal or slightly slower on 2 and 8 B200: NCCL's CTAs only run between the "
                          "persistent GEMM launches)")
     ap.add_argument("--no-overlap", dest="overlap", action="store_false", help="the default")
+    ap.add_argument("--replicated-optimizer", dest="shard_optimizer", action="store_false",
+                    help="N > 1: every rank repeats the whole Muon/AdamW update instead of updating its share of "
+                         "Theta and exchanging the shares (the default)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

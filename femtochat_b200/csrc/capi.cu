@@ -15,6 +15,8 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
                    int has_lambda, float lambda, float n_tokens, cudaStream_t s);
 int optimizer_get_t(femto_optimizer* o, int* t, int cap);
 int optimizer_set_t(femto_optimizer* o, const int* t, int count);
+int optimizer_set_shard(femto_optimizer* o, int rank, int world);
+int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap);
 int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
                  float eps, float lam, int t, float n_tokens, cudaStream_t s);
 template <typename T>
@@ -205,6 +207,12 @@ int32_t femto_optimizer_destroy(femto_optimizer* o) { return optimizer_destroy(o
 int32_t femto_optimizer_step(femto_optimizer* o, float* theta, const float* delta, float eta, int32_t has_mu, float mu,
                              int32_t has_lambda, float lambda, float n_tokens, void* stream) {
   return optimizer_step(o, theta, delta, eta, has_mu, mu, has_lambda, lambda, n_tokens, (cudaStream_t)stream);
+}
+int32_t femto_optimizer_set_shard(femto_optimizer* o, int32_t rank, int32_t world) { return optimizer_set_shard(o, rank, world); }
+int32_t femto_optimizer_shard_ranges(femto_optimizer* o, int64_t* h_out, int32_t capacity) {
+  if (!o || (capacity > 0 && !h_out)) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  static_assert(sizeof(long long) == sizeof(int64_t), "int64_t");
+  return optimizer_shard_ranges(o, (long long*)h_out, capacity);
 }
 int32_t femto_optimizer_get_t(femto_optimizer* o, int32_t* t, int32_t cap) {
   if (!o || !t) return femto_fail(FEMTO_ERR_ARG, "NULL argument");

@@ -10,9 +10,11 @@
 #include "model.cuh"
 #include "streaming.cuh"
 
-struct AdamGroup { long long off, n, moff; float alpha, b1, b2, eps, lam; int t; };
+struct AdamGroup { long long off, n, moff; float alpha, b1, b2, eps, lam; int t; bool shard = false; };
 struct MuonGroup {
   std::vector<long long> offs;
+  std::vector<int> layers;      // block of each matrix (ascending)
+  int k0 = 0, k1 = 0;           // the matrices this rank updates (all of them unless sharded)
   int out = 0, in = 0;          // Julia shape (m, n) = (out, in); stored row-major [in][out]
   long long moff = 0, voff = 0; // into muon_m / muon_v
   float alpha, mu, b2, lam;
@@ -28,6 +30,10 @@ struct femto_optimizer {
   char* ws = nullptr;  // X fp32 stack, two compute-type stacks, A, B2, small vectors
   float* X = nullptr; void *Xa = nullptr, *Xb = nullptr, *A = nullptr, *B2 = nullptr;
   float *vec = nullptr, *fac = nullptr, *tot = nullptr;
+  // owner-sharded update (data parallel): which part of every group this rank updates, and the ranges to publish
+  int shard_rank = 0, shard_world = 1;
+  std::vector<long long> gathers;   // (offset, count per rank)
+  std::vector<long long> bcasts;    // (offset, count, owner)
 };
 
 namespace {
@@ -322,12 +328,14 @@ template int newton_schulz_t<bf16>(bf16*, bf16*, bf16*, bf16*, int, int, int, co
 template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& g, float* theta, const float* delta,
                                                   float alpha, float mu, float lam, float nt, cudaStream_t s) {
   femto_handle* h = o->h;
-  const int k = (int)g.offs.size(), in = g.in, out = g.out;
+  const int k = g.k1 - g.k0, in = g.in, out = g.out;
+  if (k <= 0) return 0;
   const long long per = (long long)in * out;
-  float* mom = o->muon_m + g.moff;
-  float* v = o->muon_v + g.voff;
+  const long long* d_offs = g.d_offs + g.k0;
+  float* mom = o->muon_m + g.moff + (long long)g.k0 * per;
+  float* v = o->muon_v + g.voff + (long long)g.k0 * (out >= in ? out : in);
   dim3 eg(egrid(per), k);
-  k_muon_momentum<<<eg, 256, 0, s>>>(delta, g.d_offs, mom, o->X, per, mu, 1.f / nt);
+  k_muon_momentum<<<eg, 256, 0, s>>>(delta, d_offs, mom, o->X, per, mu, 1.f / nt);
   KERNEL_CHECK();
   k_sumsq_cols<float><<<dim3(cdiv(out, 256), k), 256, 0, s>>>(o->X, in, out, o->vec);
   KERNEL_CHECK();
@@ -346,7 +354,7 @@ template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& 
   k_normuon_factors<<<k, 256, 0, s>>>(o->vec, dim, dsize, std::min(in, out), g.b2, v, o->fac);
   KERNEL_CHECK();
   const float eta = alpha * sqrtf(std::max(1.f, (float)out / (float)in));
-  k_muon_update<T><<<eg, 256, 0, s>>>(theta, g.d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam);
+  k_muon_update<T><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam);
   KERNEL_CHECK();
   return 0;
 }
@@ -395,13 +403,13 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
   add(h->off_lam_s, 1, cfg->smear_lr, 0.8f, 0.95f, 0.f);
   add(h->off_lam_y, 1, cfg->smear_lr, 0.8f, 0.95f, 0.f);
   // Muon groups by shape, in order of first appearance (src/optim.jl:405-425)
-  struct Spec { long long off; int out, in; };
+  struct Spec { long long off; int out, in, layer; };
   std::vector<Spec> specs;
   for (int i = 0; i < h->L; i++) {
     const LayerP& p = h->lp[i];
-    specs.push_back({p.wq, h->d, h->d}); specs.push_back({p.wk, h->kv, h->d}); specs.push_back({p.wv, h->kv, h->d});
-    specs.push_back({p.wo, h->d, h->d}); specs.push_back({p.fc, 4 * h->d, h->d}); specs.push_back({p.proj, h->d, 4 * h->d});
-    if (p.ve) specs.push_back({p.ve_gate, h->Hkv, 12});
+    specs.push_back({p.wq, h->d, h->d, i}); specs.push_back({p.wk, h->kv, h->d, i}); specs.push_back({p.wv, h->kv, h->d, i});
+    specs.push_back({p.wo, h->d, h->d, i}); specs.push_back({p.fc, 4 * h->d, h->d, i}); specs.push_back({p.proj, h->d, 4 * h->d, i});
+    if (p.ve) specs.push_back({p.ve_gate, h->Hkv, 12, i});
   }
   long long mo = 0, vo = 0;
   size_t max_stack = 0, max_rr = 0, max_vec = 0;
@@ -414,9 +422,11 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
       g = &o->muon.back();
     }
     g->offs.push_back(sp.off);
+    g->layers.push_back(sp.layer);
   }
   for (auto& g : o->muon) {
     const size_t k = g.offs.size();
+    g.k0 = 0; g.k1 = (int)k;
     g.moff = mo; g.voff = vo;
     mo += (long long)k * g.in * g.out;
     vo += (long long)k * (g.out >= g.in ? g.out : g.in);
@@ -455,10 +465,13 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
                    int has_lambda, float lambda, float n_tokens, cudaStream_t s) {
   if (!o || !theta || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   if (!(n_tokens > 0.f)) return femto_fail(FEMTO_ERR_ARG, "n_tokens must be positive");
+  const bool sharded = o->shard_world > 1;
   for (auto& g : o->adam) {  // src/optim.jl:431-433
     g.t += 1;
-    FEMTO_TRY(adamw_launch(theta + g.off, delta + g.off, o->adam_m + g.moff, o->adam_v + g.moff, g.n, eta * g.alpha,
-                           g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, s));
+    // a sharded table: this rank updates slice shard_rank of shard_world equal slices
+    const long long n = g.shard ? g.n / o->shard_world : g.n, o0 = g.shard ? n * o->shard_rank : 0;
+    FEMTO_TRY(adamw_launch(theta + g.off + o0, delta + g.off + o0, o->adam_m + g.moff + o0, o->adam_v + g.moff + o0, n,
+                           eta * g.alpha, g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, s));
   }
   for (auto& g : o->muon) {  // src/optim.jl:434-438
     const float m_ = has_mu ? mu : g.mu, l_ = has_lambda ? lambda : g.lam;
@@ -467,6 +480,11 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
     else
       FEMTO_TRY(muon_group_step<float>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s));
   }
+  // every rank now holds the new values of the ranges it owns; fetch the others' (a handle without a
+  // communicator skips this: the caller merges the ranges itself, as the single-GPU emulation test does)
+  if (sharded && o->h->dp)
+    FEMTO_TRY(dp_exchange_ranges(o->h->dp, theta, o->gathers.data(), (int)o->gathers.size() / 2, o->bcasts.data(),
+                                 (int)o->bcasts.size() / 3, s));
   return model_refresh(o->h, theta, s);
 }
 
@@ -479,4 +497,59 @@ int optimizer_set_t(femto_optimizer* o, const int* t, int count) {
   if (count != (int)o->adam.size()) return femto_fail(FEMTO_ERR_SHAPE, "expected %d step counters", (int)o->adam.size());
   for (int i = 0; i < count; i++) o->adam[i].t = t[i];
   return 0;
+}
+
+// Owner-sharded update for data parallelism.  Gradients are identical on every rank after the all-reduce, so
+// instead of repeating the whole update on each of them, rank r updates only
+//   * slice r of `world` equal slices of every large AdamW table (embeddings, lm_head, value embeddings), and
+//   * the Muon matrices of the blocks [r L / world, (r+1) L / world),
+// and the new values are exchanged (in-place all-gather per table, one broadcast per block's contiguous run of
+// matrices).  Small AdamW groups (scalars, gates) stay replicated.  The moments of ranges a rank does not own
+// are not advanced on that rank: a checkpoint of the optimiser state has to collect every range from its owner.
+int optimizer_set_shard(femto_optimizer* o, int rank, int world) {
+  if (!o) return femto_fail(FEMTO_ERR_ARG, "NULL optimizer");
+  if (world < 1 || rank < 0 || rank >= world) return femto_fail(FEMTO_ERR_ARG, "need 0 <= rank < world");
+  femto_handle* h = o->h;
+  if (world > 1 && h->dp && (dp_world(h->dp) != world || dp_rank(h->dp) != rank))
+    return femto_fail(FEMTO_ERR_ARG, "rank / world differ from the handle's communicator (%d / %d)", dp_rank(h->dp),
+                      dp_world(h->dp));
+  o->shard_rank = rank; o->shard_world = world;
+  o->gathers.clear(); o->bcasts.clear();
+  for (auto& g : o->adam) {
+    g.shard = world > 1 && g.n >= (1ll << 20) && g.n % (4ll * world) == 0;
+    if (g.shard) { o->gathers.push_back(g.off); o->gathers.push_back(g.n / world); }
+  }
+  struct R { long long off, n; int owner; };
+  std::vector<R> rs;
+  for (auto& g : o->muon) {
+    const int k = (int)g.offs.size();
+    g.k0 = 0; g.k1 = k;
+    if (world == 1) continue;
+    g.k0 = k; g.k1 = k;
+    for (int i = 0; i < k; i++) {
+      const int owner = (int)((long long)g.layers[i] * world / h->L);
+      if (owner == rank) { g.k0 = std::min(g.k0, i); g.k1 = i + 1; }
+      rs.push_back({g.offs[i], (long long)g.in * g.out, owner});
+    }
+    if (g.k0 > g.k1) g.k0 = g.k1;
+  }
+  std::sort(rs.begin(), rs.end(), [](const R& a, const R& b) { return a.off < b.off; });
+  for (size_t i = 0; i < rs.size(); i++) {
+    const size_t m = o->bcasts.size();
+    if (m && o->bcasts[m - 1] == rs[i].owner && o->bcasts[m - 3] + o->bcasts[m - 2] == rs[i].off) o->bcasts[m - 2] += rs[i].n;
+    else { o->bcasts.push_back(rs[i].off); o->bcasts.push_back(rs[i].n); o->bcasts.push_back(rs[i].owner); }
+  }
+  return 0;
+}
+// (offset, count, owner) of every range that one rank alone updates; returns the number of triplets.
+int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap) {
+  int n = 0;
+  auto put = [&](long long off, long long cnt, long long owner) {
+    if (n < cap) { out[3 * n] = off; out[3 * n + 1] = cnt; out[3 * n + 2] = owner; }
+    n++;
+  };
+  for (size_t i = 0; i + 1 < o->gathers.size(); i += 2)
+    for (int r = 0; r < o->shard_world; r++) put(o->gathers[i] + r * o->gathers[i + 1], o->gathers[i + 1], r);
+  for (size_t i = 0; i + 2 < o->bcasts.size(); i += 3) put(o->bcasts[i], o->bcasts[i + 1], o->bcasts[i + 2]);
+  return n;
 }

@@ -106,6 +106,19 @@ class MuonAdamW:
 
     __call__ = step
 
+    def shard(self, rank: int, world: int):
+        """Owner-sharded update for data parallelism (the reference is single-GPU, scripts/train.jl:13): this rank
+        updates slice `rank` of every large AdamW table and the Muon matrices of its share of the blocks, and `step`
+        exchanges the results over the handle's communicator.  `world == 1` restores the full update."""
+        _lib.check(_lib.lib().femto_optimizer_set_shard(self.o, int(rank), int(world)))
+
+    def shard_ranges(self):
+        """(offset, count, owner) of every range of Theta that a single rank updates under the current sharding."""
+        n = _lib.lib().femto_optimizer_shard_ranges(self.o, None, 0)
+        buf = (C.c_int64 * (3 * max(n, 1)))()
+        _lib.lib().femto_optimizer_shard_ranges(self.o, buf, n)
+        return [(int(buf[3 * i]), int(buf[3 * i + 1]), int(buf[3 * i + 2])) for i in range(n)]
+
     def get_t(self):
         n = len(self.adamw)
         buf = (C.c_int32 * n)()

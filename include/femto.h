@@ -154,6 +154,18 @@ int32_t femto_optimizer_destroy(femto_optimizer* o);
  * Reads delta, updates Theta and the moments, then refreshes the compute-type weights. */
 int32_t femto_optimizer_step(femto_optimizer* o, float* theta, const float* delta, float eta, int32_t has_mu,
                              float mu, int32_t has_lambda, float lambda, float n_tokens, void* stream);
+/* Owner-sharded update for data parallelism (no counterpart in the reference, which is single-GPU:
+ * scripts/train.jl:13).  After femto_grad_sync every rank holds the same delta, so rank `rank` of `world`
+ * updates only slice `rank` of every large AdamW table (:333-390) and the Muon matrices (:405-425) of the
+ * blocks [rank L / world, (rank+1) L / world); femto_optimizer_step then exchanges the new values over the
+ * handle's communicator (in-place all-gather per table, one broadcast per block), so Theta stays replicated.
+ * Small AdamW groups (scalars, gates) stay replicated.  The moments of ranges a rank does not own are not
+ * advanced on that rank.  world == 1 restores the full update.  On a handle without a communicator the
+ * exchange is skipped and the caller merges the ranges itself (femto_optimizer_shard_ranges). */
+int32_t femto_optimizer_set_shard(femto_optimizer* o, int32_t rank, int32_t world);
+/* (offset, count, owner rank) triplets, in floats, of every range of Theta that one rank alone updates under
+ * the current sharding; returns their number (h_out receives at most `capacity` of them). */
+int32_t femto_optimizer_shard_ranges(femto_optimizer* o, int64_t* h_out, int32_t capacity);
 /* Step counters t of the AdamW groups (:17,35), for checkpoints (src/checkpoints.jl:9-12). */
 int32_t femto_optimizer_get_t(femto_optimizer* o, int32_t* h_t, int32_t capacity);
 int32_t femto_optimizer_set_t(femto_optimizer* o, const int32_t* h_t, int32_t count);

@@ -206,3 +206,61 @@ def test_model_call_reduction_none_returns_token_losses():
     assert torch.equal(got == 0, (tgt == -1) | (ref.float() == 0))          # ignored slots are exactly zero
     assert torch.allclose(got.double(), ref.reshape(got.shape), rtol=1e-5, atol=1e-5)
     assert float(got.sum()) == pytest.approx(model(tok, tgt, positions=pos, reduction="sum"), rel=1e-6)
+
+
+SHARD = dict(sequence_len=32, max_document_tokens=64, vocab_size=8192, n_layer=5, n_head=2, n_kv_head=1, n_embed=128,
+             window_pattern="SL")
+
+
+@pytest.mark.parametrize("cfgkw,ctype,world,tol", [(SHARD, "float32", 2, 1e-6), (SHARD, "float32", 3, 1e-6),
+                                                   (TC, "bfloat16", 2, 2e-3)])
+def test_owner_sharded_update_matches_full_update(cfgkw, ctype, world, tol):
+    """Data-parallel owner-sharded MuonAdamW, emulated on one GPU: every rank updates only its share of Theta from the
+    same delta; merging the shares by their owner must give the full update (src/optim.jl:430-440), the shares must
+    be disjoint, and what no rank owns alone must come out the same on every rank."""
+    cfg = fb.GPTConfig(**cfgkw)
+    lay = fb.parameter_layout(cfg)
+    theta0 = torch.empty(lay.nparams, dtype=torch.float32, device="cuda")
+    fb.initialize_(theta0, lay, seed=5, all_nonzero=True)
+    st = fb.GradientState(cfg, max_batch=1, compute_type=ctype)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    deltas = [torch.randn(lay.nparams, generator=g, device="cuda") * 0.3 for _ in range(2)]
+
+    full = fb.Params(theta0.clone())
+    opt_full = fb.MuonAdamW(full, lay, st, compute_type=ctype, weight_decay=0.1)
+    ranks = [fb.Params(theta0.clone()) for _ in range(world)]
+    opts = [fb.MuonAdamW(p, lay, st, compute_type=ctype, weight_decay=0.1) for p in ranks]
+    for r, o in enumerate(opts):
+        o.shard(r, world)
+    ranges = opts[0].shard_ranges()
+    assert ranges == opts[world - 1].shard_ranges()
+    owned = torch.zeros(lay.nparams, dtype=torch.int32)
+    for off, n, owner in ranges:
+        assert 0 <= owner < world and n > 0
+        owned[off:off + n] += 1
+    assert int(owned.max()) == 1                       # disjoint
+    muon_elems = sum(sp.size for grp in opt_full.muon for sp in grp.specs)
+    big_tables = sum(gv.spec.size for gv in opt_full.adamw if gv.spec.size >= 1 << 20 and gv.spec.size % (4 * world) == 0)
+    assert int(owned.sum()) == muon_elems + big_tables  # every Muon matrix and every divisible large table has one owner
+    assert {o for _, _, o in ranges} == set(range(world))
+
+    for i, d in enumerate(deltas):
+        kw = dict(eta=0.5 + 0.25 * i, mu=0.9, lam=0.05, Nt=64.0)
+        full.delta.copy_(d)
+        opt_full.step(**kw)
+        for p, o in zip(ranks, opts):
+            p.delta.copy_(d)
+            o.step(**kw)
+        merged = ranks[0].theta.clone()
+        shared = owned.cuda() == 0
+        for p in ranks[1:]:
+            assert torch.equal(p.theta[shared], merged[shared])      # replicated groups agree bit for bit
+        for off, n, owner in ranges:
+            merged[off:off + n] = ranks[owner].theta[off:off + n]
+        err = float((merged - full.theta).abs().max())
+        assert err <= tol, (i, err)
+        for p in ranks:
+            p.theta.copy_(merged)
+    assert all(o.get_t() == opt_full.get_t() for o in opts)
+    opts[0].shard(0, 1)                                # back to the full update
+    assert opts[0].shard_ranges() == []
