@@ -208,7 +208,7 @@ def run_ours(args):
 
     def sync_and_update(loss_dev, nv_dev, step):
         if world > 1:
-            _lib.check(L.femto_grad_sync(st.h, _lib.ptr(params.delta), _lib.ptr(loss_dev), _lib.ptr(nv_dev), sp()))
+            opt.grad_sync(loss_dev, nv_dev)   # femto_grad_sync, or its reduce-to-owner form under the sharded update
         sch = fb.training_schedule(step, 1000)
         opt.step(eta=sch["eta"], mu=sch["mu"], lam=sch["lam"] * 0.01, Nt=float(B * T * world))
 

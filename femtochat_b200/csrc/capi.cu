@@ -17,6 +17,8 @@ int optimizer_get_t(femto_optimizer* o, int* t, int cap);
 int optimizer_set_t(femto_optimizer* o, const int* t, int count);
 int optimizer_set_shard(femto_optimizer* o, int rank, int world);
 int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap);
+int optimizer_grad_sync(femto_optimizer* o, float* delta, cudaStream_t s);
+femto_handle* optimizer_handle(femto_optimizer* o);
 int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
                  float eps, float lam, int t, float n_tokens, cudaStream_t s);
 template <typename T>
@@ -213,6 +215,18 @@ int32_t femto_optimizer_shard_ranges(femto_optimizer* o, int64_t* h_out, int32_t
   if (!o || (capacity > 0 && !h_out)) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   static_assert(sizeof(long long) == sizeof(int64_t), "int64_t");
   return optimizer_shard_ranges(o, (long long*)h_out, capacity);
+}
+int32_t femto_optimizer_grad_sync(femto_optimizer* o, float* delta, float* loss_inout, int32_t* n_valid_inout, void* stream) {
+  if (!o || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  femto_handle* h = optimizer_handle(o);
+  if (h->world <= 1) return 0;
+  // buckets already summed during the reverse pass (femto_set_overlap) are complete on every rank
+  if (h->delta_synced) return femto_grad_sync(h, delta, loss_inout, n_valid_inout, stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  FEMTO_TRY(optimizer_grad_sync(o, delta, s));
+  if (loss_inout) FEMTO_TRY(dp_allreduce_sum_f32(h->dp, loss_inout, 1, s));
+  if (n_valid_inout) FEMTO_TRY(dp_allreduce_sum_i32(h->dp, n_valid_inout, 1, s));
+  return 0;
 }
 int32_t femto_optimizer_get_t(femto_optimizer* o, int32_t* t, int32_t cap) {
   if (!o || !t) return femto_fail(FEMTO_ERR_ARG, "NULL argument");

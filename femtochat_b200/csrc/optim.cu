@@ -34,6 +34,7 @@ struct femto_optimizer {
   int shard_rank = 0, shard_world = 1;
   std::vector<long long> gathers;   // (offset, count per rank)
   std::vector<long long> bcasts;    // (offset, count, owner)
+  std::vector<long long> gaps;      // (offset, count): what lies between them, replicated
 };
 
 namespace {
@@ -514,7 +515,7 @@ int optimizer_set_shard(femto_optimizer* o, int rank, int world) {
     return femto_fail(FEMTO_ERR_ARG, "rank / world differ from the handle's communicator (%d / %d)", dp_rank(h->dp),
                       dp_world(h->dp));
   o->shard_rank = rank; o->shard_world = world;
-  o->gathers.clear(); o->bcasts.clear();
+  o->gathers.clear(); o->bcasts.clear(); o->gaps.clear();
   for (auto& g : o->adam) {
     g.shard = world > 1 && g.n >= (1ll << 20) && g.n % (4ll * world) == 0;
     if (g.shard) { o->gathers.push_back(g.off); o->gathers.push_back(g.n / world); }
@@ -539,7 +540,27 @@ int optimizer_set_shard(femto_optimizer* o, int rank, int world) {
     if (m && o->bcasts[m - 1] == rs[i].owner && o->bcasts[m - 3] + o->bcasts[m - 2] == rs[i].off) o->bcasts[m - 2] += rs[i].n;
     else { o->bcasts.push_back(rs[i].off); o->bcasts.push_back(rs[i].n); o->bcasts.push_back(rs[i].owner); }
   }
+  // the replicated remainder of [0, nparams)
+  std::vector<std::pair<long long, long long>> cover;
+  for (size_t i = 0; i + 1 < o->gathers.size(); i += 2) cover.push_back({o->gathers[i], o->gathers[i + 1] * world});
+  for (size_t i = 0; i + 2 < o->bcasts.size(); i += 3) cover.push_back({o->bcasts[i], o->bcasts[i + 1]});
+  std::sort(cover.begin(), cover.end());
+  long long at = 0;
+  for (const auto& c : cover) {
+    if (c.first > at) { o->gaps.push_back(at); o->gaps.push_back(c.first - at); }
+    at = c.first + c.second;
+  }
+  if (world > 1 && at < h->nparams) { o->gaps.push_back(at); o->gaps.push_back(h->nparams - at); }
   return 0;
+}
+// Sum delta over ranks for this sharding: a range that one rank alone consumes is summed only onto that rank (on
+// the others it keeps the local gradient), the rest is all-reduced.
+int optimizer_grad_sync(femto_optimizer* o, float* delta, cudaStream_t s) {
+  femto_handle* h = o->h;
+  if (!h->dp) return 0;
+  if (o->shard_world <= 1) return dp_allreduce_sum_f32(h->dp, delta, h->nparams, s);
+  return dp_reduce_ranges(h->dp, delta, o->gathers.data(), (int)o->gathers.size() / 2, o->bcasts.data(),
+                          (int)o->bcasts.size() / 3, o->gaps.data(), (int)o->gaps.size() / 2, s);
 }
 // (offset, count, owner) of every range that one rank alone updates; returns the number of triplets.
 int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap) {
@@ -553,3 +574,4 @@ int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap) {
   for (size_t i = 0; i + 2 < o->bcasts.size(); i += 3) put(o->bcasts[i], o->bcasts[i + 1], o->bcasts[i + 2]);
   return n;
 }
+femto_handle* optimizer_handle(femto_optimizer* o) { return o->h; }

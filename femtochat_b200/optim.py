@@ -112,6 +112,13 @@ class MuonAdamW:
         exchanges the results over the handle's communicator.  `world == 1` restores the full update."""
         _lib.check(_lib.lib().femto_optimizer_set_shard(self.o, int(rank), int(world)))
 
+    def grad_sync(self, loss=None, n_valid=None):
+        """Sum `params.delta` (and the device scalars `loss`, `n_valid`) over the ranks before `step`.  Under `shard`
+        a range that one rank alone consumes is summed only onto that rank (half the bytes of an all-reduce)."""
+        _lib.check(_lib.lib().femto_optimizer_grad_sync(
+            self.o, _lib.ptr(self.params.delta), None if loss is None else _lib.ptr(loss),
+            None if n_valid is None else _lib.ptr(n_valid), _lib.stream_ptr()))
+
     def shard_ranges(self):
         """(offset, count, owner) of every range of Theta that a single rank updates under the current sharding."""
         n = _lib.lib().femto_optimizer_shard_ranges(self.o, None, 0)

@@ -163,6 +163,12 @@ int32_t femto_optimizer_step(femto_optimizer* o, float* theta, const float* delt
  * advanced on that rank.  world == 1 restores the full update.  On a handle without a communicator the
  * exchange is skipped and the caller merges the ranges itself (femto_optimizer_shard_ranges). */
 int32_t femto_optimizer_set_shard(femto_optimizer* o, int32_t rank, int32_t world);
+/* femto_grad_sync for a sharded optimiser: a range of delta that one rank alone consumes is summed only onto
+ * that rank (in-place reduce-scatter per table, reduce to the owner per block), which moves half the bytes of
+ * the all-reduce; on the other ranks such a range keeps the local gradient.  Everything else, the loss and
+ * n_valid are all-reduced.  Without sharding it equals femto_grad_sync. */
+int32_t femto_optimizer_grad_sync(femto_optimizer* o, float* delta, float* loss_inout, int32_t* n_valid_inout,
+                                  void* stream);
 /* (offset, count, owner rank) triplets, in floats, of every range of Theta that one rank alone updates under
  * the current sharding; returns their number (h_out receives at most `capacity` of them). */
 int32_t femto_optimizer_shard_ranges(femto_optimizer* o, int64_t* h_out, int32_t capacity);
