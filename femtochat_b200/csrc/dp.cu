@@ -16,7 +16,6 @@ typedef int (*fn_destroy)(nccl_comm);
 typedef int (*fn_allreduce)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_reduce_scatter)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_allgather)(const void*, void*, size_t, int, nccl_comm, cudaStream_t);
-typedef int (*fn_broadcast)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_reduce)(const void*, void*, size_t, int, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_group)(void);
 typedef const char* (*fn_errstr)(int);
@@ -25,7 +24,7 @@ struct Nccl {
   void* lib = nullptr;
   fn_get_uid get_uid = nullptr; fn_init_rank init_rank = nullptr; fn_destroy destroy = nullptr;
   fn_allreduce allreduce = nullptr; fn_reduce_scatter reduce_scatter = nullptr; fn_allgather allgather = nullptr;
-  fn_broadcast broadcast = nullptr; fn_reduce reduce = nullptr; fn_group group_start = nullptr, group_end = nullptr;
+  fn_reduce reduce = nullptr; fn_group group_start = nullptr, group_end = nullptr;
   fn_errstr errstr = nullptr;
 };
 Nccl g_nccl;
@@ -44,13 +43,12 @@ int nccl_load() {
   g_nccl.allreduce = (fn_allreduce)dlsym(g_nccl.lib, "ncclAllReduce");
   g_nccl.reduce_scatter = (fn_reduce_scatter)dlsym(g_nccl.lib, "ncclReduceScatter");
   g_nccl.allgather = (fn_allgather)dlsym(g_nccl.lib, "ncclAllGather");
-  g_nccl.broadcast = (fn_broadcast)dlsym(g_nccl.lib, "ncclBroadcast");
   g_nccl.reduce = (fn_reduce)dlsym(g_nccl.lib, "ncclReduce");
   g_nccl.group_start = (fn_group)dlsym(g_nccl.lib, "ncclGroupStart");
   g_nccl.group_end = (fn_group)dlsym(g_nccl.lib, "ncclGroupEnd");
   g_nccl.errstr = (fn_errstr)dlsym(g_nccl.lib, "ncclGetErrorString");
   if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.reduce_scatter || !g_nccl.allgather ||
-      !g_nccl.broadcast || !g_nccl.reduce || !g_nccl.group_start || !g_nccl.group_end)
+      !g_nccl.reduce || !g_nccl.group_start || !g_nccl.group_end)
     return femto_fail(FEMTO_ERR_UNSUPPORTED, "libnccl is missing required symbols");
   return 0;
 }
@@ -143,28 +141,7 @@ int dp_allgather_bytes(DpState* d, const void* send, void* recv, long long bytes
   return nccl_check(g_nccl.allgather(send, recv, (size_t)bytes_per_rank, NCCL_INT8, d->comm, s), "ncclAllGather");
 }
 
-// Publish the parameter ranges that each rank updated on its own (owner-sharded optimiser): `gathers` holds
-// (offset, count per rank) pairs of ranges cut into `world` equal slices, slice r written by rank r (in-place
-// all-gather); `bcasts` holds (offset, count, owner) triplets.  All of it is one NCCL group on `s`.
-int dp_exchange_ranges(DpState* d, float* theta, const long long* gathers, int n_gathers, const long long* bcasts,
-                       int n_bcasts, cudaStream_t s) {
-  if (!d) return 0;
-  FEMTO_TRY(nccl_check(g_nccl.group_start(), "ncclGroupStart"));
-  int r = 0;
-  for (int i = 0; i < n_gathers && !r; i++) {
-    float* base = theta + gathers[2 * i];
-    const long long c = gathers[2 * i + 1];
-    r = g_nccl.allgather(base + (long long)d->rank * c, base, (size_t)c, NCCL_FLOAT32, d->comm, s);
-  }
-  for (int i = 0; i < n_bcasts && !r; i++) {
-    float* p = theta + bcasts[3 * i];
-    r = g_nccl.broadcast(p, p, (size_t)bcasts[3 * i + 1], NCCL_FLOAT32, (int)bcasts[3 * i + 2], d->comm, s);
-  }
-  const int e = g_nccl.group_end();
-  FEMTO_TRY(nccl_check(r, "ncclAllGather / ncclBroadcast"));
-  return nccl_check(e, "ncclGroupEnd");
-}
-// The gradient side of the same sharding: every range of delta is summed over ranks, but a range that one rank alone
+// Gradient sum for the owner-sharded update: every range of delta is summed over ranks, but a range that one rank alone
 // will consume is summed only onto that rank (in-place reduce-scatter of the sliced tables, reduce to the owner of
 // each (offset, count, owner) run), which moves half the bytes of an all-reduce; `gaps` (offset, count) are the
 // replicated ranges in between and get a plain all-reduce.  One NCCL group on `s`.

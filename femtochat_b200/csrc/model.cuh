@@ -82,8 +82,6 @@ int dp_reduce_scatter_f32(DpState* d, const float* send, float* recv, long long 
 int dp_allgather_bytes(DpState* d, const void* send, void* recv, long long bytes_per_rank, cudaStream_t s);
 int dp_bucket_allreduce(DpState* d, float* buf, long long n, cudaStream_t compute);
 int dp_join(DpState* d, cudaStream_t compute);
-int dp_exchange_ranges(DpState* d, float* theta, const long long* gathers, int n_gathers, const long long* bcasts,
-                       int n_bcasts, cudaStream_t s);
 int dp_reduce_ranges(DpState* d, float* delta, const long long* gathers, int n_gathers, const long long* bcasts,
                      int n_bcasts, const long long* gaps, int n_gaps, cudaStream_t s);
 int dp_world(const DpState* d);

@@ -158,7 +158,8 @@ int32_t femto_optimizer_step(femto_optimizer* o, float* theta, const float* delt
  * scripts/train.jl:13).  After femto_grad_sync every rank holds the same delta, so rank `rank` of `world`
  * updates only slice `rank` of every large AdamW table (:333-390) and the Muon matrices (:405-425) of the
  * blocks [rank L / world, (rank+1) L / world); femto_optimizer_step then exchanges the new values over the
- * handle's communicator (in-place all-gather per table, one broadcast per block), so Theta stays replicated.
+ * handle's communicator (each rank clears what it does not own, then one all-reduce of Theta), so Theta stays
+ * replicated.
  * Small AdamW groups (scalars, gates) stay replicated.  The moments of ranges a rank does not own are not
  * advanced on that rank.  world == 1 restores the full update.  On a handle without a communicator the
  * exchange is skipped and the caller merges the ranges itself (femto_optimizer_shard_ranges). */
