@@ -20,6 +20,44 @@ POLAR_EXPRESS_COEFFS = (                       # src/optim.jl:90-96
 QUINTIC_COEFFS = tuple((3.4445, -4.7750, 2.0315) for _ in range(5))
 
 
+SHARD_MIN_TABLE = 1 << 20
+
+
+def shard_plan(layout, world: int, min_table: int = SHARD_MIN_TABLE):
+    """The partition `MuonAdamW.shard` uses, as sorted (offset, count, owner) triplets: every AdamW table of at
+    least 2^20 elements whose size divides by 4*world is cut into `world` equal slices (slice r to rank r); the Muon
+    matrices of block i belong to rank i*world // n_layer, adjacent matrices of one owner merged into one range.
+    Everything else (scalars, gates, small or indivisible tables) is updated by every rank (`min_table` is the
+    library's fixed 2^20; tests lower it to cut small tables).  The reference has no
+    data-parallel path (scripts/train.jl:13); the ranges follow its parameter layout (src/parameters.jl:219-337)."""
+    if world <= 1:
+        return []
+    def size(sp):
+        n = 1
+        for x in sp.shape:
+            n *= int(x)
+        return n
+    out = []
+    tables = [layout.lm_head, layout.embedding] + [b["ve_table"] for b in layout.blocks if b["ve_table"] is not None]
+    for sp in tables:
+        n = size(sp)
+        if n >= min_table and n % (4 * world) == 0:
+            out += [(int(sp.offset) + r * (n // world), n // world, r) for r in range(world)]
+    L = len(layout.blocks)
+    mats = []
+    for i, b in enumerate(layout.blocks):
+        for k in ("wq", "wk", "wv", "wo", "fc", "proj", "ve_gate"):
+            if b[k] is not None:
+                mats.append((int(b[k].offset), size(b[k]), i * world // L))
+    merged = []
+    for off, n, owner in sorted(mats):
+        if merged and merged[-1][2] == owner and merged[-1][0] + merged[-1][1] == off:
+            merged[-1] = (merged[-1][0], merged[-1][1] + n, owner)
+        else:
+            merged.append((off, n, owner))
+    return sorted(out + merged)
+
+
 class _AdamGroupView:
     def __init__(self, owner, index, spec, m, v):
         self._owner, self._index, self.spec, self.m, self.v = owner, index, spec, m, v

@@ -234,6 +234,7 @@ def test_owner_sharded_update_matches_full_update(cfgkw, ctype, world, tol):
         o.shard(r, world)
     ranges = opts[0].shard_ranges()
     assert ranges == opts[world - 1].shard_ranges()
+    assert sorted(ranges) == fb.shard_plan(lay, world)  # the library's partition is the documented one
     owned = torch.zeros(lay.nparams, dtype=torch.int32)
     for off, n, owner in ranges:
         assert 0 <= owner < world and n > 0
