@@ -72,6 +72,8 @@ SIGNATURES = {
     "femto_optimizer_step": (I32, [P, P, P, F, I32, F, I32, F, F, P]),
     "femto_optimizer_set_shard": (I32, [P, I32, I32]),
     "femto_optimizer_grad_sync": (I32, [P, P, P, P, P]),
+    "femto_optimizer_state_ranges": (I32, [P, I32, C.POINTER(I64), I32]),
+    "femto_optimizer_gather_state": (I32, [P, P]),
     "femto_optimizer_shard_ranges": (I32, [P, C.POINTER(I64), I32]),
     "femto_optimizer_get_t": (I32, [P, C.POINTER(I32), I32]),
     "femto_optimizer_set_t": (I32, [P, C.POINTER(I32), I32]),

@@ -19,6 +19,8 @@ int optimizer_set_shard(femto_optimizer* o, int rank, int world);
 int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap);
 int optimizer_grad_sync(femto_optimizer* o, float* delta, cudaStream_t s);
 femto_handle* optimizer_handle(femto_optimizer* o);
+int optimizer_state_ranges(femto_optimizer* o, int which, long long* out, int cap);
+int optimizer_gather_state(femto_optimizer* o, cudaStream_t s);
 int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
                  float eps, float lam, int t, float n_tokens, cudaStream_t s);
 template <typename T>
@@ -215,6 +217,14 @@ int32_t femto_optimizer_shard_ranges(femto_optimizer* o, int64_t* h_out, int32_t
   if (!o || (capacity > 0 && !h_out)) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   static_assert(sizeof(long long) == sizeof(int64_t), "int64_t");
   return optimizer_shard_ranges(o, (long long*)h_out, capacity);
+}
+int32_t femto_optimizer_state_ranges(femto_optimizer* o, int32_t which, int64_t* h_out, int32_t capacity) {
+  if (!o || (capacity > 0 && !h_out)) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  return optimizer_state_ranges(o, which, (long long*)h_out, capacity);
+}
+int32_t femto_optimizer_gather_state(femto_optimizer* o, void* stream) {
+  if (!o) return femto_fail(FEMTO_ERR_ARG, "NULL optimizer");
+  return optimizer_gather_state(o, (cudaStream_t)stream);
 }
 int32_t femto_optimizer_grad_sync(femto_optimizer* o, float* delta, float* loss_inout, int32_t* n_valid_inout, void* stream) {
   if (!o || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");

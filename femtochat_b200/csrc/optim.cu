@@ -595,3 +595,54 @@ int optimizer_shard_ranges(femto_optimizer* o, long long* out, int cap) {
   return n;
 }
 femto_handle* optimizer_handle(femto_optimizer* o) { return o->h; }
+
+// Which rank holds the current moments of which part of a state buffer under the sharding (which: 0 adam_m,
+// 1 adam_v, 2 muon_m, 3 muon_v): sorted (offset, count, owner) triplets covering the whole buffer.  Replicated
+// groups are listed with owner 0 (every rank holds the same values).
+static void state_cover(femto_optimizer* o, int which, std::vector<long long>& out) {
+  const int world = o->shard_world, L = o->h->L;
+  auto put = [&](long long off, long long n, long long owner) {
+    const size_t m = out.size();
+    if (m && out[m - 1] == owner && out[m - 3] + out[m - 2] == off) out[m - 2] += n;
+    else { out.push_back(off); out.push_back(n); out.push_back(owner); }
+  };
+  if (which < 2) {
+    for (const auto& g : o->adam) {
+      if (g.shard) for (int r = 0; r < world; r++) put(g.moff + r * (g.n / world), g.n / world, r);
+      else put(g.moff, g.n, 0);
+    }
+  } else {
+    for (const auto& g : o->muon) {
+      const long long per = which == 2 ? (long long)g.in * g.out : (long long)(g.out >= g.in ? g.out : g.in);
+      const long long base = which == 2 ? g.moff : g.voff;
+      for (size_t i = 0; i < g.offs.size(); i++)
+        put(base + (long long)i * per, per, world > 1 ? (long long)g.layers[i] * world / L : 0);
+    }
+  }
+}
+int optimizer_state_ranges(femto_optimizer* o, int which, long long* out, int cap) {
+  if (which < 0 || which > 3) return femto_fail(FEMTO_ERR_ARG, "which must be 0..3");
+  std::vector<long long> c;
+  state_cover(o, which, c);
+  const int n = (int)c.size() / 3;
+  for (int i = 0; i < n && i < cap; i++) { out[3 * i] = c[3 * i]; out[3 * i + 1] = c[3 * i + 1]; out[3 * i + 2] = c[3 * i + 2]; }
+  return n;
+}
+// Make the four state buffers complete on every rank (before a checkpoint, or before changing the sharding): each
+// rank clears the parts whose current values live elsewhere and one all-reduce per buffer adds the owners' values
+// to zeros (src/checkpoints.jl:9-12 reads the moments group by group from one process).
+int optimizer_gather_state(femto_optimizer* o, cudaStream_t s) {
+  femto_handle* h = o->h;
+  if (o->shard_world <= 1 || !h->dp) return 0;
+  long long sizes[4];
+  FEMTO_TRY(optimizer_state_sizes(h, sizes));
+  float* bufs[4] = {o->adam_m, o->adam_v, o->muon_m, o->muon_v};
+  for (int w = 0; w < 4; w++) {
+    std::vector<long long> c;
+    state_cover(o, w, c);
+    for (size_t i = 0; i + 2 < c.size(); i += 3)
+      if (c[i + 2] != o->shard_rank) CUDA_TRY(cudaMemsetAsync(bufs[w] + c[i], 0, sizeof(float) * (size_t)c[i + 1], s));
+    FEMTO_TRY(dp_allreduce_sum_f32(h->dp, bufs[w], sizes[w], s));
+  }
+  return 0;
+}

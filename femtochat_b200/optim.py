@@ -157,6 +157,18 @@ class MuonAdamW:
             self.o, _lib.ptr(self.params.delta), None if loss is None else _lib.ptr(loss),
             None if n_valid is None else _lib.ptr(n_valid), _lib.stream_ptr()))
 
+    def gather_state(self):
+        """Under `shard`: make the moment buffers complete on every rank (before `optimizer_state` for a checkpoint,
+        src/checkpoints.jl:9-12, or before changing the sharding)."""
+        _lib.check(_lib.lib().femto_optimizer_gather_state(self.o, _lib.stream_ptr()))
+
+    def state_ranges(self, which: int):
+        """(offset, count, owner) cover of a state buffer: 0 adam_m, 1 adam_v, 2 muon_m, 3 muon_v."""
+        n = _lib.lib().femto_optimizer_state_ranges(self.o, int(which), None, 0)
+        buf = (C.c_int64 * (3 * max(n, 1)))()
+        _lib.lib().femto_optimizer_state_ranges(self.o, int(which), buf, n)
+        return [(int(buf[3 * i]), int(buf[3 * i + 1]), int(buf[3 * i + 2])) for i in range(n)]
+
     def shard_ranges(self):
         """(offset, count, owner) of every range of Theta that a single rank updates under the current sharding."""
         n = _lib.lib().femto_optimizer_shard_ranges(self.o, None, 0)

@@ -173,6 +173,14 @@ int32_t femto_optimizer_grad_sync(femto_optimizer* o, float* delta, float* loss_
 /* (offset, count, owner rank) triplets, in floats, of every range of Theta that one rank alone updates under
  * the current sharding; returns their number (h_out receives at most `capacity` of them). */
 int32_t femto_optimizer_shard_ranges(femto_optimizer* o, int64_t* h_out, int32_t capacity);
+/* Which rank holds the current moments of which part of a state buffer under the sharding (which: 0 adam_m,
+ * 1 adam_v, 2 muon_m, 3 muon_v): sorted (offset, count, owner) triplets in floats covering the whole buffer;
+ * replicated groups are listed with owner 0.  Returns their number. */
+int32_t femto_optimizer_state_ranges(femto_optimizer* o, int32_t which, int64_t* h_out, int32_t capacity);
+/* Make the four state buffers complete on every rank, so that `optimizer_state` (src/checkpoints.jl:9-12) can be
+ * taken from any one of them and the sharding (or the number of ranks) may change afterwards: each rank clears
+ * the parts held elsewhere, then one all-reduce per buffer.  No-op without sharding.  Asynchronous on `stream`. */
+int32_t femto_optimizer_gather_state(femto_optimizer* o, void* stream);
 /* Step counters t of the AdamW groups (:17,35), for checkpoints (src/checkpoints.jl:9-12). */
 int32_t femto_optimizer_get_t(femto_optimizer* o, int32_t* h_t, int32_t capacity);
 int32_t femto_optimizer_set_t(femto_optimizer* o, const int32_t* h_t, int32_t count);

@@ -263,5 +263,21 @@ def test_owner_sharded_update_matches_full_update(cfgkw, ctype, world, tol):
         for p in ranks:
             p.theta.copy_(merged)
     assert all(o.get_t() == opt_full.get_t() for o in opts)
+    # the moments: each part of each state buffer is current on the rank that state_ranges names (what
+    # gather_state collects before a checkpoint), and the covers tile the buffers
+    for which, name in enumerate(["adam_m", "adam_v", "muon_m", "muon_v"]):
+        cover = opts[0].state_ranges(which)
+        want = getattr(opt_full, name)
+        at = 0
+        merged = torch.empty_like(want)
+        for off, n, owner in cover:
+            assert off == at and n > 0 and 0 <= owner < world
+            merged[off:off + n] = getattr(opts[owner], name)[off:off + n]
+            at += n
+        assert at == want.numel()
+        if which >= 2:                                 # every rank owns some block's matrices
+            assert {o for _, _, o in cover} == set(range(world))
+        err = float((merged - want).abs().max())
+        assert err <= tol * max(1.0, float(want.abs().max())), (name, err)
     opts[0].shard(0, 1)                                # back to the full update
     assert opts[0].shard_ranges() == []
