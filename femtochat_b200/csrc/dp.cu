@@ -15,7 +15,6 @@ typedef int (*fn_init_rank)(nccl_comm*, int, nccl_uid, int);
 typedef int (*fn_destroy)(nccl_comm);
 typedef int (*fn_allreduce)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_reduce_scatter)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t);
-typedef int (*fn_allgather)(const void*, void*, size_t, int, nccl_comm, cudaStream_t);
 typedef int (*fn_reduce)(const void*, void*, size_t, int, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_group)(void);
 typedef const char* (*fn_errstr)(int);
@@ -23,7 +22,7 @@ typedef const char* (*fn_errstr)(int);
 struct Nccl {
   void* lib = nullptr;
   fn_get_uid get_uid = nullptr; fn_init_rank init_rank = nullptr; fn_destroy destroy = nullptr;
-  fn_allreduce allreduce = nullptr; fn_reduce_scatter reduce_scatter = nullptr; fn_allgather allgather = nullptr;
+  fn_allreduce allreduce = nullptr; fn_reduce_scatter reduce_scatter = nullptr;
   fn_reduce reduce = nullptr; fn_group group_start = nullptr, group_end = nullptr;
   fn_errstr errstr = nullptr;
 };
@@ -42,18 +41,17 @@ int nccl_load() {
   g_nccl.destroy = (fn_destroy)dlsym(g_nccl.lib, "ncclCommDestroy");
   g_nccl.allreduce = (fn_allreduce)dlsym(g_nccl.lib, "ncclAllReduce");
   g_nccl.reduce_scatter = (fn_reduce_scatter)dlsym(g_nccl.lib, "ncclReduceScatter");
-  g_nccl.allgather = (fn_allgather)dlsym(g_nccl.lib, "ncclAllGather");
   g_nccl.reduce = (fn_reduce)dlsym(g_nccl.lib, "ncclReduce");
   g_nccl.group_start = (fn_group)dlsym(g_nccl.lib, "ncclGroupStart");
   g_nccl.group_end = (fn_group)dlsym(g_nccl.lib, "ncclGroupEnd");
   g_nccl.errstr = (fn_errstr)dlsym(g_nccl.lib, "ncclGetErrorString");
-  if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.reduce_scatter || !g_nccl.allgather ||
+  if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.reduce_scatter ||
       !g_nccl.reduce || !g_nccl.group_start || !g_nccl.group_end)
     return femto_fail(FEMTO_ERR_UNSUPPORTED, "libnccl is missing required symbols");
   return 0;
 }
 // ncclDataType_t / ncclRedOp_t values of the public nccl.h
-constexpr int NCCL_INT8 = 0, NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_SUM = 0;
+constexpr int NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_SUM = 0;
 int nccl_check(int r, const char* what) {
   if (r == 0) return 0;
   return femto_fail(200000 + r, "%s failed: %s", what, g_nccl.errstr ? g_nccl.errstr(r) : "nccl error");
@@ -131,16 +129,6 @@ int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s) {
   if (!d) return 0;
   return nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_INT32, NCCL_SUM, d->comm, s), "ncclAllReduce");
 }
-int dp_reduce_scatter_f32(DpState* d, const float* send, float* recv, long long n_per_rank, cudaStream_t s) {
-  if (!d) return 0;
-  return nccl_check(g_nccl.reduce_scatter(send, recv, (size_t)n_per_rank, NCCL_FLOAT32, NCCL_SUM, d->comm, s),
-                    "ncclReduceScatter");
-}
-int dp_allgather_bytes(DpState* d, const void* send, void* recv, long long bytes_per_rank, cudaStream_t s) {
-  if (!d) return 0;
-  return nccl_check(g_nccl.allgather(send, recv, (size_t)bytes_per_rank, NCCL_INT8, d->comm, s), "ncclAllGather");
-}
-
 // Gradient sum for the owner-sharded update: every range of delta is summed over ranks, but a range that one rank alone
 // will consume is summed only onto that rank (in-place reduce-scatter of the sliced tables, reduce to the owner of
 // each (offset, count, owner) run), which moves half the bytes of an all-reduce; `gaps` (offset, count) are the

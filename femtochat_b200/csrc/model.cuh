@@ -78,8 +78,6 @@ void dp_destroy(DpState* d);
 int dp_unique_id(void* id128);
 int dp_allreduce_sum_f32(DpState* d, float* buf, long long n, cudaStream_t s);
 int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s);
-int dp_reduce_scatter_f32(DpState* d, const float* send, float* recv, long long n_per_rank, cudaStream_t s);
-int dp_allgather_bytes(DpState* d, const void* send, void* recv, long long bytes_per_rank, cudaStream_t s);
 int dp_bucket_allreduce(DpState* d, float* buf, long long n, cudaStream_t compute);
 int dp_join(DpState* d, cudaStream_t compute);
 int dp_reduce_ranges(DpState* d, float* delta, const long long* gathers, int n_gathers, const long long* bcasts,
