@@ -316,6 +316,37 @@ def run_ours(args):
             except Exception as e:  # the GPU number stands even if the host baseline cannot run
                 line["cpu_baseline"] = dict(value=None, unit="tokens/s", cores=None, kind="port", sample=f"failed: {e}")
         print(json.dumps(line), flush=True)
+    if args.phases and world > 1:
+        # Per-phase device times of the data-parallel step, with a barrier between the phases so that one rank's
+        # wait for another is not booked to a collective: reverse pass | gradient sum | update (+ exchange), for
+        # the owner-sharded and the replicated update on the same ranks.  Printed on stderr (stdout keeps its one line).
+        tok, tgt, pos = dev[total - 1]
+        for mode in ("owner-sharded", "replicated"):
+            opt.shard(*((rank, world) if mode == "owner-sharded" else (0, 1)))
+            acc = [0.0, 0.0, 0.0]
+            for it in range(5):
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+                barrier()
+                ev[0].record()
+                loss_dev, nv_dev = fb.loss_and_gradient_(params, st, lay, tok, tgt, pos, reduction="sum", sync=False)
+                ev[1].record()
+                barrier()
+                ev[2].record()
+                opt.grad_sync(loss_dev, nv_dev)
+                ev[3].record()
+                barrier()
+                ev[4].record()
+                opt.step(eta=0.01, mu=0.95, lam=0.0, Nt=float(B * T * world))
+                ev[5].record()
+                torch.cuda.synchronize()
+                if it >= 2:
+                    for k in range(3):
+                        acc[k] += ev[2 * k].elapsed_time(ev[2 * k + 1]) / 3
+            t = torch.tensor(acc, dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                print(json.dumps(dict(phases=mode, n_gpus=world, forward_reverse_ms=float(t[0]),
+                                      gradient_sum_ms=float(t[1]), update_ms=float(t[2]))), file=sys.stderr, flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -338,6 +369,9 @@ def main():
     ap.add_argument("--replicated-optimizer", dest="shard_optimizer", action="store_false",
                     help="N > 1: every rank repeats the whole Muon/AdamW update instead of updating its share of "
                          "Theta and exchanging the shares (the default)")
+    ap.add_argument("--phases", action="store_true",
+                    help="N > 1: after the bench line, time reverse pass / gradient sum / update separately for the "
+                         "owner-sharded and the replicated update (stderr)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
