@@ -23,14 +23,15 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CONFIGS = {
-    # BASELINE.json configs[3]: d20, GQA, "SSSL" with a 1024-token short window, B=32 per GPU
+    # the headline model: d20, GQA 10/5, "SSSL" with a 1024-token short window, B=32 per GPU
     "d20": dict(cfg=dict(sequence_len=2048, max_document_tokens=8192, vocab_size=65536, n_layer=20, n_head=10,
                          n_kv_head=5, n_embed=1280, window_pattern="SSSL"), batch=32, short_window=1024),
-    # configs[2]: d12, full windows
+    # d12, full windows, one GPU
     "d12": dict(cfg=dict(sequence_len=2048, max_document_tokens=8192, vocab_size=65536, n_layer=12, n_head=6,
                          n_kv_head=6, n_embed=768, window_pattern="L"), batch=32, short_window=0),
+    # d26: B=16 per GPU x 2 gradient-accumulation micro-steps per update
     "d26": dict(cfg=dict(sequence_len=2048, max_document_tokens=8192, vocab_size=65536, n_layer=26, n_head=13,
-                         n_kv_head=13, n_embed=1664, window_pattern="SSSL"), batch=16, short_window=1024),
+                         n_kv_head=13, n_embed=1664, window_pattern="SSSL"), batch=16, short_window=1024, micro_steps=2),
     "small": dict(cfg=dict(sequence_len=256, max_document_tokens=512, vocab_size=4096, n_layer=4, n_head=4,
                            n_kv_head=2, n_embed=512, window_pattern="SL"), batch=8, short_window=128),
 }
@@ -86,12 +87,14 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------
 # CPU baseline: the oracle (restatement of the reference's CPU path) on a bounded sample
 # --------------------------------------------------------------------------------------------------
-def cpu_step_sample(name: str, sample_T: int, muon_layers: int = 1):
+def cpu_step_sample(name: str, sample_T: int, muon_layers: int = 1, warm: bool = True):
     """One bounded sample of a training step on the host cores: forward+reverse on one column of
     `sample_T` tokens, AdamW over every AdamW group, Muon over the matrices of `muon_layers`
     blocks (scaled to all blocks).  Returns tokens/s of a full step of B*T tokens per GPU."""
     import torch
     from oracle import femto_oracle as fo
+    # all host cores, whatever the launcher exported (torchrun sets OMP_NUM_THREADS=1 for its workers)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     spec = CONFIGS[name]
     full = spec["cfg"]
     cfg = fo.GPTConfig(**{**full, "sequence_len": sample_T})
@@ -102,6 +105,15 @@ def cpu_step_sample(name: str, sample_T: int, muon_layers: int = 1):
     pk = fb.PackedBatches(full["vocab_size"], sample_T, 1, max_document_tokens=full["max_document_tokens"])
     tok, tgt, pos = (torch.from_numpy(x) for x in pk.next())
     M = fo.Model(cfg, fo.StepOptions(eps=fo.EPS_BF16, short_window=spec["short_window"], doc_mask=True))
+    if warm:   # one untimed pass on a two-layer, 128-token copy of the model (thread pool and allocator start-up)
+        wcfg = fo.GPTConfig(**{**full, "sequence_len": 128, "n_layer": 2})
+        wlay = fo.parameter_layout(wcfg)
+        wth = torch.zeros(wlay.nparams, dtype=torch.float32)
+        fo.initialize(wth, wcfg, wlay, 1, all_nonzero=True)
+        wpk = fb.PackedBatches(full["vocab_size"], 128, 1, max_document_tokens=full["max_document_tokens"])
+        wtok, wtgt, wpos = (torch.from_numpy(x) for x in wpk.next())
+        fo.Model(wcfg, fo.StepOptions(eps=fo.EPS_BF16, short_window=spec["short_window"], doc_mask=True)).loss_and_gradient(
+            wth, wtok, wtgt, wpos)
     t0 = time.time()
     loss, delta, _ = M.loss_and_gradient(th, tok, tgt, pos)
     t_fb = time.time() - t0
@@ -124,7 +136,8 @@ def cpu_step_sample(name: str, sample_T: int, muon_layers: int = 1):
     tokens_full = spec["batch"] * full["sequence_len"]
     t_full = t_fb * tokens_full / sample_T + t_adam + t_muon
     return dict(tokens_per_s=tokens_full / t_full, t_fb=t_fb, t_adam=t_adam, t_muon=t_muon, loss=float(loss) / sample_T,
-                cores=torch.get_num_threads(),
+                cores=torch.get_num_threads(), measured_s=t_fb + t_adam + t_muon / cfg.n_layer * muon_layers,
+                step_s_extrapolated=t_full,
                 sample=(f"oracle fp32 on host: forward+reverse on 1 column of {sample_T} tokens ({t_fb:.1f}s, scaled to "
                         f"{tokens_full} tokens), AdamW on all groups ({t_adam:.1f}s), Polar Express on 1 of "
                         f"{cfg.n_layer} blocks ({t_muon / cfg.n_layer:.1f}s, scaled)"))
@@ -132,26 +145,26 @@ def cpu_step_sample(name: str, sample_T: int, muon_layers: int = 1):
 
 def run_reference(args):
     """`--impl reference`: the reference's own Julia CPU step cannot run (no Julia toolchain: unavailable
-    on this box); the timed arm is the CPU restatement in oracle/ (kind "port")."""
+    on this box); the timed arm is the CPU restatement in oracle/ (kind "port") on every host core.  A full step
+    (65 536 tokens at d20) takes minutes on a CPU, so ONE bounded sample is timed after one small warm-up pass:
+    forward + reverse on one column of 1024 tokens, AdamW over all groups, Polar Express on one block, and the
+    step time is extrapolated from it (the line says so and gives the seconds that were actually measured).
+    --steps / --warmup are echoed, not multiplied into more samples.  Under torchrun only rank 0 works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     spec = CONFIGS[args.config]
-    total = args.steps + args.warmup
-    sample_T = 256 if total <= 4 else 128
-    vals, last = [], None
-    for i in range(total):
-        last = cpu_step_sample(args.config, sample_T)
-        if i >= args.warmup:
-            vals.append(last["tokens_per_s"])
-    v = sum(vals) / len(vals)
+    c = cpu_step_sample(args.config, 1024)
+    v = c["tokens_per_s"]
     tokens_full = spec["batch"] * spec["cfg"]["sequence_len"]
     line = dict(metric="training tokens/sec", value=v, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
-                warmup=args.warmup, ms_per_step=1e3 * tokens_full / v, higher_is_better=True, scaling="weak",
-                vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                warmup=args.warmup, ms_per_step=1e3 * c["step_s_extrapolated"], higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic", impl="reference", extrapolated=True,
+                measured_seconds=c["measured_s"],
                 config=dict(workload=f"{args.config} GPT training step, B={spec['batch']} x T={spec['cfg']['sequence_len']} per GPU",
-                            note="reference Julia CPU path unavailable on this box (no Julia); CPU restatement timed"),
-                cpu_baseline=dict(value=v, unit="tokens/s", cores=last["cores"], kind="port", sample=last["sample"]),
+                            note="reference Julia CPU path unavailable on this box (no Julia); CPU restatement timed on one "
+                                 "bounded sample, ms_per_step extrapolated to the full batch"),
+                cpu_baseline=dict(value=v, unit="tokens/s", cores=c["cores"], kind="port", sample=c["sample"]),
                 e2e=dict(value=v, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
@@ -183,6 +196,7 @@ def run_ours(args):
 
     spec = CONFIGS[args.config]
     B = args.batch or spec["batch"]
+    micro = args.micro_steps or spec.get("micro_steps", 1)   # gradient-accumulation micro-steps per update
     cfg = fb.GPTConfig(**spec["cfg"])
     T = cfg.sequence_len
     lay = fb.parameter_layout(cfg)
@@ -192,15 +206,14 @@ def run_ours(args):
     st = fb.GradientState(cfg, max_batch=B, compute_type="bfloat16", short_window=spec["short_window"], doc_mask=True,
                           rank=rank, world=world, nccl_id=nccl_id)
     st.refresh_weights(params.theta)
-    if world > 1 and args.overlap:
-        _lib.check(_lib.lib().femto_set_overlap(st.h, 1))   # one micro-step per update: reduce delta while the reverse pass runs
+    use_overlap = world > 1 and args.overlap   # reduce delta while the LAST micro-step's reverse pass runs
     opt = fb.MuonAdamW(params, lay, st, compute_type="bfloat16", weight_decay=0.01)
     if world > 1 and args.shard_optimizer:
         opt.shard(rank, world)   # each rank updates its share of Theta, then the shares are exchanged
     total = args.steps + args.warmup
     pk = fb.PackedBatches(cfg.vocab_size, T, B, max_document_tokens=cfg.max_document_tokens, rank=rank)
     host = []
-    for _ in range(total):
+    for _ in range(total * micro):
         host.append(tuple(torch.from_numpy(x).pin_memory() for x in pk.next()))
     dev = [tuple(x.cuda() for x in h) for h in host]
     L = _lib.lib()
@@ -210,17 +223,26 @@ def run_ours(args):
         if world > 1:
             opt.grad_sync(loss_dev, nv_dev)   # femto_grad_sync, or its reduce-to-owner form under the sharded update
         sch = fb.training_schedule(step, 1000)
-        opt.step(eta=sch["eta"], mu=sch["mu"], lam=sch["lam"] * 0.01, Nt=float(B * T * world))
+        opt.step(eta=sch["eta"], mu=sch["mu"], lam=sch["lam"] * 0.01, Nt=float(B * T * world * micro))
 
+    # One update = `micro` micro-steps (scripts/train.jl:117-131: the first overwrites delta, the others add),
+    # then ONE gradient sum and ONE optimiser step.
     def step_resident(i):
-        tok, tgt, pos = dev[i]
-        loss_dev, nv_dev = fb.loss_and_gradient_(params, st, lay, tok, tgt, pos, reduction="sum", sync=False)
+        for ms in range(micro):
+            tok, tgt, pos = dev[i * micro + ms]
+            if use_overlap:
+                _lib.check(L.femto_set_overlap(st.h, 1 if ms == micro - 1 else 0))
+            loss_dev, nv_dev = fb.loss_and_gradient_(params, st, lay, tok, tgt, pos, reduction="sum", accumulate=ms > 0,
+                                                     sync=False)
         sync_and_update(loss_dev, nv_dev, i)
         return loss_dev
 
     def step_e2e(i):
-        tok, tgt, pos = host[i]
-        loss, nv = fb.loss_and_gradient_host_(params, st, tok, tgt, pos, reduction="sum")
+        for ms in range(micro):
+            tok, tgt, pos = host[i * micro + ms]
+            if use_overlap:
+                _lib.check(L.femto_set_overlap(st.h, 1 if ms == micro - 1 else 0))
+            loss, nv = fb.loss_and_gradient_host_(params, st, tok, tgt, pos, reduction="sum", accumulate=ms > 0)
         sync_and_update(st._loss, st._nvalid, i)
         return loss
 
@@ -248,7 +270,7 @@ def run_ours(args):
     barrier()
     ms = e0.elapsed_time(e1)
     launches = st.launch_count() - l0
-    final_loss = float(losses[-1].item()) / (B * T * world)   # the loss sum is all-reduced by femto_grad_sync
+    final_loss = float(losses[-1].item()) / (B * T * world)   # last micro-step's loss sum, all-reduced by femto_grad_sync
     clk = clocks.stop() if rank == 0 else None
 
     # ---- end to end: host buffers through the public call, H2D and D2H inside the timed region ----
@@ -283,7 +305,7 @@ def run_ours(args):
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         replicated = bool((hi == lo).all().item())
     if rank == 0:
-        tokens = B * T * world * args.steps
+        tokens = B * T * world * micro * args.steps
         value = tokens / (ms / 1e3)
         peaks = measured_peaks()
         peak_tf = peaks["bf16_tflops_sustained"]
@@ -293,22 +315,22 @@ def run_ours(args):
             ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
             data="synthetic",
             config=dict(workload=f"{args.config} GPT training step (forward, reverse, grad sync, Muon+AdamW), "
-                                 f"B={B} x T={T} per GPU, short window {spec['short_window'] or 'reference rule'}, "
+                                 f"B={B} x T={T} per GPU{f' x {micro} micro-steps' if micro > 1 else ''}, short window {spec['short_window'] or 'reference rule'}, "
                                  f"document mask on",
                         parallelism=f"dp{world}",
                         optimizer=("owner-sharded" if world > 1 and args.shard_optimizer else "replicated"),
                         theta_replicated=replicated, l2="inputs and activations per step far exceed the 126 MB L2",
                         mfu_nominal_2p25e15=value * flops_tok / (world * 2.25e15), flops_per_token=flops_tok,
                         loss_per_token=final_loss, device_status=status),
-            e2e=dict(value=tokens / (ms_e2e / 1e3), unit="tokens/s", h2d_bytes_per_step=3 * 4 * B * T,
-                     d2h_bytes_per_step=8),
+            e2e=dict(value=tokens / (ms_e2e / 1e3), unit="tokens/s", h2d_bytes_per_step=3 * 4 * B * T * micro,
+                     d2h_bytes_per_step=8 * micro),
             gpu_launches=int(launches),
             clocks=clk,
             roofline=dict(bound="tensor", achieved=ach, peak=peak_tf, unit="TFLOP/s", frac=ach / peak_tf if peak_tf else None,
                           traffic=None, kernel="gemm_tc_kernel", launches_per_step=gl.value,
                           kernel_ms_per_step=gms.value, peak_source=f"{peaks['source']} (sustained cuBLAS bf16)"),
         )
-        if args.cpu_baseline:
+        if args.cpu_baseline and world == 1:   # the host baseline belongs to the one-GPU line only
             try:
                 c = cpu_step_sample(args.config, 1024)
                 line["cpu_baseline"] = dict(value=c["tokens_per_s"], unit="tokens/s", cores=c["cores"], kind="port",
@@ -360,6 +382,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="d20", choices=sorted(CONFIGS))
     ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--micro-steps", type=int, default=0,
+                    help="gradient-accumulation micro-steps per update (default: the configuration's own, 2 for d26)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--overlap", dest="overlap", action="store_true",
                     help="sum delta over ranks bucket by bucket during the reverse pass instead of after it "

@@ -78,7 +78,7 @@ SIGNATURES = {
     "femto_optimizer_get_t": (I32, [P, C.POINTER(I32), I32]),
     "femto_optimizer_set_t": (I32, [P, C.POINTER(I32), I32]),
     "femto_attention_fwd": (I32, [I32, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, I32, P, P]),
-    "femto_attention_bwd": (I32, [I32, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, I32, P, P]),
+    "femto_attention_bwd": (I32, [I32, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, I32, P, I32, P]),
     "femto_attention_bwd_static": (I32, [I32, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, I32, P, P]),
     "femto_gemm_bf16": (I32, [P, I32, I64, P, I32, I64, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
     "femto_embedding_gradient": (I32, [I32, P, P, P, I32, I32, I32, P]),
@@ -87,6 +87,10 @@ SIGNATURES = {
     "femto_cross_entropy": (I32, [P, I64, P, I32, I32, I32, P, P, P]),
     "femto_cross_entropy_gradient": (I32, [P, I64, P, I64, P, I32, I32, I32, F, P, P]),
     "femto_adamw": (I32, [P, P, P, P, I64, F, F, F, F, F, I32, F, P]),
+    "femto_rmsnorm_fwd": (I32, [I32, P, P, P, I32, I32, F, P]),
+    "femto_rmsnorm_bwd": (I32, [I32, P, P, P, P, I32, I32, P]),
+    "femto_embed_gather": (I32, [I32, P, P, P, I32, I32, I32, P]),
+    "femto_muon_direction": (I32, [I32, P, P, P, P, I32, I32, I32, F, F, F, C.POINTER(F), I32, P]),
     "femto_status_word": (I32, [P, C.POINTER(I32)]),
     "femto_sync": (I32, [P, P]),
     "femto_launch_count": (I64, [P]),

@@ -32,6 +32,24 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// Eight results leave as one 16-byte store; with `accumulate` the eight bf16 values already there are added first
+// (Δattention!'s accumulate=true, ext/FemtoChatCUDAExt.jl:1775).
+__device__ __forceinline__ void store8(bf16* dst, const uint32_t* r, float scale, bool accumulate) {
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) v[e] = __uint_as_float(r[e]) * scale;
+  if (accumulate) {
+    const uint4 old = *reinterpret_cast<const uint4*>(dst);
+    const bf16* oh = reinterpret_cast<const bf16*>(&old);
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] += __bfloat162float(oh[e]);
+  }
+  uint4 q;
+  uint32_t* w = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+  for (int e = 0; e < 4; e++) w[e] = pack2(v[2 * e], v[2 * e + 1]);
+  *reinterpret_cast<uint4*>(dst) = q;
+}
 
 // D[b][h][t] = sum_d dO*O and L2 = lse * log2(e): 16 lanes per (token, head) slice of 128 channels, 16-byte loads.
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D, float* L2) {
@@ -290,14 +308,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tdQ + lane_off + cc * 32, rr);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 qv;
-          uint32_t* w = reinterpret_cast<uint32_t*>(&qv);
-#pragma unroll
-          for (int e = 0; e < 4; e++)
-            w[e] = pack2(__uint_as_float(rr[j + 2 * e]) * scale, __uint_as_float(rr[j + 2 * e + 1]) * scale);
-          *reinterpret_cast<uint4*>(dq + cc * 32 + j) = qv;
-        }
+        for (int j = 0; j < 32; j += 8) store8(dq + cc * 32 + j, rr + j, scale, a.accumulate);
       }
     }
   }
@@ -554,16 +565,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-          uint4 qk, qv;
-          uint32_t* wk = reinterpret_cast<uint32_t*>(&qk);
-          uint32_t* wv = reinterpret_cast<uint32_t*>(&qv);
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            wk[e] = pack2(__uint_as_float(rk[j + 2 * e]) * scale, __uint_as_float(rk[j + 2 * e + 1]) * scale);
-            wv[e] = pack2(__uint_as_float(rv[j + 2 * e]), __uint_as_float(rv[j + 2 * e + 1]));
-          }
-          *reinterpret_cast<uint4*>(dk + cc * 32 + j) = qk;
-          *reinterpret_cast<uint4*>(dv + cc * 32 + j) = qv;
+          store8(dk + cc * 32 + j, rk + j, scale, a.accumulate);
+          store8(dv + cc * 32 + j, rv + j, 1.f, a.accumulate);
         }
       }
     }
@@ -596,11 +599,12 @@ int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
   FEMTO_TRY(make_tmap_2d_bf16(&tmK, a.K, (uint64_t)a.Hkv * HD, N, a.kv_stride, 64, BT));
   FEMTO_TRY(make_tmap_2d_bf16(&tmV, a.V, (uint64_t)a.Hkv * HD, N, a.kv_stride, 64, BT));
   FEMTO_TRY(make_tmap_2d_bf16(&tmdO, a.dO, (uint64_t)a.H * HD, N, a.do_stride, 64, BT));
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDevice attr;
+  const int dev = PerDevice::current();
+  if (dev < 0 || !attr.done[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
     CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
-    attr_done = true;
+    if (dev >= 0) attr.done[dev] = true;
   }
   dim3 gq(a.T / BT, a.H, a.B);
   attn_bwd_dq_kernel<<<gq, 384, DQ_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);

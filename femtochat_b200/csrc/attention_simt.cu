@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(128) attn_bwd_dq_simt_kernel(AttnArgs a, float
 #pragma unroll
   for (int e = 0; e < EPL; e++) {
     int d = lane + 32 * e;
-    if (d < hd) dq[d] = from_f<T>(acc[e]);
+    if (d < hd) dq[d] = from_f<T>(a.accumulate ? to_f<T>(dq[d]) + acc[e] : acc[e]);
   }
 }
 
@@ -177,8 +177,8 @@ __global__ void __launch_bounds__(128) attn_bwd_dkv_simt_kernel(AttnArgs a, cons
   for (int e = 0; e < EPL; e++) {
     int d = lane + 32 * e;
     if (d < hd) {
-      dkp[d] = from_f<T>(dk[e]);
-      dvp[d] = from_f<T>(dv[e]);
+      dkp[d] = from_f<T>(a.accumulate ? to_f<T>(dkp[d]) + dk[e] : dk[e]);
+      dvp[d] = from_f<T>(a.accumulate ? to_f<T>(dvp[d]) + dv[e] : dv[e]);
     }
   }
 }

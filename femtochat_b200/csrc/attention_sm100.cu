@@ -322,10 +322,11 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
   FwdParams p;
   p.a = a;
   p.q_col0 = 0; p.k_col0 = 0; p.v_col0 = 0;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDevice attr;
+  const int dev = PerDevice::current();
+  if (dev < 0 || !attr.done[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
-    attr_done = true;
+    if (dev >= 0) attr.done[dev] = true;
   }
   dim3 grid(a.T / BQ, a.H, a.B);
   attn_fwd_tc_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);

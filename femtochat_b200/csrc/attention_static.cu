@@ -14,8 +14,16 @@ namespace {
 constexpr long long STATIC_SCRATCH_FLOATS = 2ll << 20;  // two floats per row: B*H*T <= 1 048 576 (e.g. 32 x 16 x 2048)
 static __device__ __align__(256) float g_attn_bwd_scratch[STATIC_SCRATCH_FLOATS];
 
+// Status word of this entry point (a bounded wait that ran out sets bit 2): like the scratch, part of the library
+// image, so that reporting needs no allocation either.
+static __device__ unsigned int g_attn_bwd_static_status = 0;
+
 constexpr int MAX_DEVICES = 64;
-float* g_scratch_ptr[MAX_DEVICES] = {nullptr};  // device address of the array above, per device
+// Device addresses of the two objects above, per device.  Looked up on the first call on each device; the cache is
+// not synchronised between host threads (two first calls at once look the address up twice, harmlessly) and is not
+// refreshed after cudaDeviceReset.
+float* g_scratch_ptr[MAX_DEVICES] = {nullptr};
+unsigned int* g_status_ptr[MAX_DEVICES] = {nullptr};
 
 // The array's name is only a host-side handle: the device address has to be asked for, once per
 // device, with that device current.
@@ -26,6 +34,9 @@ int scratch_for_current_device(float** out) {
   if (!g_scratch_ptr[dev]) {
     float* p = nullptr;
     CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_bwd_scratch));
+    unsigned int* st = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&st), g_attn_bwd_static_status));
+    g_status_ptr[dev] = st;
     g_scratch_ptr[dev] = p;
   }
   *out = g_scratch_ptr[dev];
@@ -33,6 +44,15 @@ int scratch_for_current_device(float** out) {
 }
 
 }  // namespace
+
+// Status word of the allocation-free entry point on the current device (0 before its first call there).
+unsigned int static_entry_status_word() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES || !g_status_ptr[dev]) return 0;
+  unsigned int w = 0;
+  if (cudaMemcpy(&w, g_status_ptr[dev], sizeof(w), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+  return w;
+}
 
 extern "C" int32_t femto_attention_bwd_static(int32_t dtype, void* dQ, void* dK, void* dV, const void* dO, const void* Q,
                                               const void* K, const void* V, const void* O, const float* lse, int32_t B,
@@ -58,5 +78,7 @@ extern "C" int32_t femto_attention_bwd_static(int32_t dtype, void* dQ, void* dK,
   // Every element of the scratch that the kernels read is written first by the same call, so nothing in
   // the shared array needs clearing between calls.
   a.ws = scratch; a.ws_bytes = sizeof(float) * (size_t)STATIC_SCRATCH_FLOATS;
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < MAX_DEVICES) a.status = g_status_ptr[dev];
   return dtype == FEMTO_BF16 ? attention_bwd<bf16>(a, (cudaStream_t)stream) : attention_bwd<float>(a, (cudaStream_t)stream);
 }

@@ -45,6 +45,38 @@ int standalone_scratch(size_t bytes, char** out) {
   return 0;
 }
 
+// Status word of the stand-alone kernel-level entry points (they have no handle): one word per device, allocated
+// on first use and kept until the process exits.  The entry points that synchronise read it back and report a
+// bounded wait that ran out as FEMTO_ERR_DEVICE_STATUS + word; femto_status_word(NULL, ..) reads it for the
+// asynchronous ones.
+static unsigned int* g_sa_status[64] = {nullptr};
+int standalone_status(unsigned int** out) {
+  int dev = -1;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return femto_fail(FEMTO_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  if (!g_sa_status[dev]) {
+    CUDA_TRY(cudaMalloc(&g_sa_status[dev], 256));
+    CUDA_TRY(cudaMemset(g_sa_status[dev], 0, 256));
+  }
+  *out = g_sa_status[dev];
+  return 0;
+}
+// Synchronise the stream and turn a raised status word into an error code (the word is cleared for the next call).
+static int standalone_finish(int rc, unsigned int* status, cudaStream_t s) {
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (rc) return rc;
+  if (e != cudaSuccess) return femto_fail((int)e, "stream synchronisation failed: %s", cudaGetErrorString(e));
+  if (!status) return 0;
+  unsigned int w = 0;
+  CUDA_TRY(cudaMemcpy(&w, status, sizeof(w), cudaMemcpyDeviceToHost));
+  if (w) {
+    CUDA_TRY(cudaMemset(status, 0, sizeof(w)));
+    return femto_fail(FEMTO_ERR_DEVICE_STATUS + (int)w, "device status word %u (2 = a bounded wait ran out: results are incomplete)", w);
+  }
+  return 0;
+}
+unsigned int static_entry_status_word();   // attention_static.cu: status of the allocation-free entry point
+
 static int require_device() {
   int n = 0;
   cudaError_t e = cudaGetDeviceCount(&n);
@@ -53,6 +85,34 @@ static int require_device() {
                       e != cudaSuccess ? cudaGetErrorString(e) : "device count 0");
   return 0;
 }
+
+// lse[i] = m[i] + log l[i]: the reference saves the row sum and the row max separately (src/kernels.jl:425-433)
+__global__ void k_lse_from_lm(const float* __restrict__ l, const float* __restrict__ m, float* __restrict__ lse, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lse[i] = m[i] + logf(l[i]);
+}
+
+// Plain row gather: out[n][:] = table[tokens0[n]][:] (one warp per row, 16-byte accesses when D allows)
+template <typename T, int V>
+__global__ void __launch_bounds__(256) k_embed_gather(const T* __restrict__ table, const int* __restrict__ tok0,
+                                                      T* __restrict__ out, int N, int D, int rows, unsigned int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= N) return;
+  int t = tok0[row];
+  if (t < 0 || t >= rows) { if (lane == 0 && status) atomicOr(status, ST_BAD_TOKEN); t = min(max(t, 0), rows - 1); }
+  const T* src = table + (long long)t * D;
+  T* dst = out + row * D;
+  for (int c = lane * V; c < D; c += 32 * V) {
+    float f[V];
+    load_vec<T, V>(src + c, f);
+    store_vec<T, V>(dst + c, f);
+  }
+}
+
+int muon_direction_standalone(int dtype, float* X_out, const float* G, float* mom, float* v, int k, int in, int out,
+                              float mu, float b2, float n_tokens, const float* coeffs, int steps, unsigned int* status,
+                              cudaStream_t s);
 
 extern "C" {
 
@@ -264,25 +324,38 @@ int32_t femto_attention_fwd(int32_t dtype, void* O, float* l, float* m, float* l
   AttnArgs a;
   FEMTO_TRY(fill_attn(a, Q, K, V, O, B, T, H, Hkv, hd, window_left, doc_start));
   a.l = l; a.m = m; a.lse = lse;
+  FEMTO_TRY(standalone_status(&a.status));
   return dtype == FEMTO_BF16 ? attention_fwd<bf16>(a, (cudaStream_t)stream) : attention_fwd<float>(a, (cudaStream_t)stream);
 }
 
 int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const void* dO, const void* Q, const void* K,
-                            const void* V, const void* O, const float* lse, int32_t B, int32_t T, int32_t H,
-                            int32_t Hkv, int32_t hd, int32_t window_left, const int32_t* doc_start, void* stream) {
+                            const void* V, const void* O, const float* lse, const float* l, const float* m, int32_t B,
+                            int32_t T, int32_t H, int32_t Hkv, int32_t hd, int32_t window_left, const int32_t* doc_start,
+                            int32_t accumulate, void* stream) {
   FEMTO_TRY(require_device());
-  if (!dQ || !dK || !dV || !dO || !lse) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (!dQ || !dK || !dV || !dO) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (!lse && (!l || !m)) return femto_fail(FEMTO_ERR_ARG, "pass lse, or both l and m");
   AttnArgs a;
   FEMTO_TRY(fill_attn(a, Q, K, V, const_cast<void*>(O), B, T, H, Hkv, hd, window_left, doc_start));
-  a.lse = const_cast<float*>(lse); a.dO = dO; a.dQ = dQ; a.dK = dK; a.dV = dV;
+  a.dO = dO; a.dQ = dQ; a.dK = dK; a.dV = dV; a.accumulate = accumulate != 0;
   a.do_stride = a.q_stride; a.dq_stride = a.q_stride; a.dkv_stride = a.kv_stride;
-  size_t need = std::max(sizeof(float) * (size_t)B * H * T * 2, attention_bwd_tc_ws_bytes(B, T, H, hd));
+  const size_t rows = (size_t)B * H * T;
+  const size_t need = (std::max(sizeof(float) * rows * 2, attention_bwd_tc_ws_bytes(B, T, H, hd)) + 255) & ~(size_t)255;
   char* ws = nullptr;
-  FEMTO_TRY(standalone_scratch(need, &ws));
+  FEMTO_TRY(standalone_scratch(need + sizeof(float) * rows, &ws));
   a.ws = ws; a.ws_bytes = need;
-  int r = dtype == FEMTO_BF16 ? attention_bwd<bf16>(a, (cudaStream_t)stream) : attention_bwd<float>(a, (cudaStream_t)stream);
-  cudaStreamSynchronize((cudaStream_t)stream);
-  return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (lse) {
+    a.lse = const_cast<float*>(lse);
+  } else {
+    float* tmp = reinterpret_cast<float*>(ws + need);
+    k_lse_from_lm<<<cdiv((long long)rows, 256), 256, 0, s>>>(l, m, tmp, (long long)rows);
+    KERNEL_CHECK();
+    a.lse = tmp;
+  }
+  FEMTO_TRY(standalone_status(&a.status));
+  int r = dtype == FEMTO_BF16 ? attention_bwd<bf16>(a, s) : attention_bwd<float>(a, s);
+  return standalone_finish(r, a.status, s);
 }
 
 int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void* B, int32_t b_kmajor, int64_t ldb,
@@ -295,14 +368,14 @@ int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void
   g.A = A; g.B = B; g.C = C; g.lda = lda; g.ldb = ldb; g.ldc = ldc; g.a_kmajor = a_kmajor != 0; g.b_kmajor = b_kmajor != 0;
   g.M = M; g.N = N; g.K = K; g.batch = batch < 1 ? 1 : batch; g.strideA = strideA; g.strideB = strideB; g.strideC = strideC;
   g.epi = out_f32 ? EPI_F32 : EPI_STORE; g.beta = accumulate ? 1.f : 0.f;
+  FEMTO_TRY(standalone_status(&g.status));
   if (!out_f32) return gemm<bf16>(g, (cudaStream_t)stream);  // asynchronous, no scratch
   char* ws = nullptr;  // split-K partials of the fp32 form
   const size_t wsb = (size_t)160 << 20;
   FEMTO_TRY(standalone_scratch(wsb, &ws));
   g.ws = ws; g.ws_bytes = wsb;
   int r = gemm<bf16>(g, (cudaStream_t)stream);
-  cudaStreamSynchronize((cudaStream_t)stream);
-  return r;
+  return standalone_finish(r, g.status, (cudaStream_t)stream);
 }
 
 int32_t femto_embedding_gradient(int32_t dtype, float* table, const void* dy, const int32_t* tokens0, int32_t N,
@@ -351,17 +424,84 @@ int32_t femto_newton_schulz(int32_t dtype, void* X, int32_t k, int32_t rows, int
   void* B2 = (char*)A + al(es * r * r * k);
   void* ws = (char*)B2 + al(es * r * r * k);
   cudaStream_t s = (cudaStream_t)stream;
+  unsigned int* status = nullptr;
+  FEMTO_TRY(standalone_status(&status));
   // row-major [rows][cols] == stored [in=rows][out=cols]
   int rc = dtype == FEMTO_BF16
-               ? newton_schulz_t<bf16>((bf16*)X, (bf16*)S2, (bf16*)A, (bf16*)B2, k, rows, cols, coeffs, steps, ws, wsb, nullptr, s)
-               : newton_schulz_t<float>((float*)X, (float*)S2, (float*)A, (float*)B2, k, rows, cols, coeffs, steps, ws, wsb, nullptr, s);
-  cudaStreamSynchronize(s);
-  return rc;
+               ? newton_schulz_t<bf16>((bf16*)X, (bf16*)S2, (bf16*)A, (bf16*)B2, k, rows, cols, coeffs, steps, ws, wsb, status, s)
+               : newton_schulz_t<float>((float*)X, (float*)S2, (float*)A, (float*)B2, k, rows, cols, coeffs, steps, ws, wsb, status, s);
+  return standalone_finish(rc, status, s);
+}
+
+int32_t femto_rmsnorm_fwd(int32_t dtype, const void* x, void* y, float* r, int32_t N, int32_t D, float eps, void* stream) {
+  FEMTO_TRY(require_device());
+  if (!x || !y || !r || N <= 0 || D <= 0) return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if (dtype != FEMTO_F32 && dtype != FEMTO_BF16) return femto_fail(FEMTO_ERR_ARG, "dtype must be FEMTO_F32 or FEMTO_BF16");
+  if (!aligned16(x) || !aligned16(y)) return femto_fail(FEMTO_ERR_ALIGN, "x and y must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  return dtype == FEMTO_BF16 ? Stream<bf16>::norm((const bf16*)x, (bf16*)y, r, N, D, eps, s)
+                             : Stream<float>::norm((const float*)x, (float*)y, r, N, D, eps, s);
+}
+
+int32_t femto_rmsnorm_bwd(int32_t dtype, const void* dy, const void* y, const float* r, void* dx, int32_t N, int32_t D,
+                          void* stream) {
+  FEMTO_TRY(require_device());
+  if (!dy || !y || !r || !dx || N <= 0 || D <= 0) return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if (dtype != FEMTO_F32 && dtype != FEMTO_BF16) return femto_fail(FEMTO_ERR_ARG, "dtype must be FEMTO_F32 or FEMTO_BF16");
+  if (!aligned16(dy) || !aligned16(y) || !aligned16(dx)) return femto_fail(FEMTO_ERR_ALIGN, "dy, y and dx must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  return dtype == FEMTO_BF16 ? Stream<bf16>::norm_bwd_resid((const bf16*)dy, (const bf16*)y, r, nullptr, (bf16*)dx, N, D, s)
+                             : Stream<float>::norm_bwd_resid((const float*)dy, (const float*)y, r, nullptr, (float*)dx, N, D, s);
+}
+
+int32_t femto_embed_gather(int32_t dtype, void* out, const void* table, const int32_t* tokens0, int32_t N, int32_t D,
+                           int32_t rows, void* stream) {
+  FEMTO_TRY(require_device());
+  if (!out || !table || !tokens0 || N <= 0 || D <= 0 || rows <= 0) return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if (dtype != FEMTO_F32 && dtype != FEMTO_BF16) return femto_fail(FEMTO_ERR_ARG, "dtype must be FEMTO_F32 or FEMTO_BF16");
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned int* status = nullptr;
+  FEMTO_TRY(standalone_status(&status));
+  const int grid = cdiv(N, 8);
+  if (dtype == FEMTO_BF16) {
+    if (D % 8 == 0 && aligned16(out) && aligned16(table)) k_embed_gather<bf16, 8><<<grid, 256, 0, s>>>((const bf16*)table, tokens0, (bf16*)out, N, D, rows, status);
+    else k_embed_gather<bf16, 1><<<grid, 256, 0, s>>>((const bf16*)table, tokens0, (bf16*)out, N, D, rows, status);
+  } else {
+    if (D % 4 == 0 && aligned16(out) && aligned16(table)) k_embed_gather<float, 4><<<grid, 256, 0, s>>>((const float*)table, tokens0, (float*)out, N, D, rows, status);
+    else k_embed_gather<float, 1><<<grid, 256, 0, s>>>((const float*)table, tokens0, (float*)out, N, D, rows, status);
+  }
+  KERNEL_CHECK();
+  return 0;
+}
+
+int32_t femto_muon_direction(int32_t dtype, float* X_out, const float* G, float* momentum, float* second_moment,
+                             int32_t k, int32_t rows, int32_t cols, float mu, float beta2, float n_tokens,
+                             const float* h_coeffs, int32_t steps, void* stream) {
+  FEMTO_TRY(require_device());
+  if (!X_out || !G || !momentum || !second_moment || !h_coeffs || k <= 0 || rows <= 0 || cols <= 0 || steps < 0 || steps > 5)
+    return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  if (!(n_tokens > 0.f)) return femto_fail(FEMTO_ERR_ARG, "n_tokens must be positive");
+  if (dtype != FEMTO_F32 && dtype != FEMTO_BF16) return femto_fail(FEMTO_ERR_ARG, "dtype must be FEMTO_F32 or FEMTO_BF16");
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned int* status = nullptr;
+  FEMTO_TRY(standalone_status(&status));
+  int rc = muon_direction_standalone(dtype, X_out, G, momentum, second_moment, k, rows, cols, mu, beta2, n_tokens, h_coeffs,
+                                     steps, status, s);
+  return standalone_finish(rc, status, s);
 }
 
 int32_t femto_status_word(femto_handle* h, int32_t* out) {
-  if (!h || !out) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (!out) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   unsigned int v = 0;
+  if (!h) {
+    // the stand-alone kernel-level entry points of the current device (synchronises the device)
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceSynchronize());
+    if (dev >= 0 && dev < 64 && g_sa_status[dev]) CUDA_TRY(cudaMemcpy(&v, g_sa_status[dev], sizeof(v), cudaMemcpyDeviceToHost));
+    *out = (int32_t)(v | static_entry_status_word());
+    return 0;
+  }
   CUDA_TRY(cudaMemcpy(&v, h->status, sizeof(v), cudaMemcpyDeviceToHost));
   *out = (int32_t)v;
   return 0;

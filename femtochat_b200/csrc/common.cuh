@@ -94,6 +94,21 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Per-device one-time set-up (function attributes, device properties): a process may drive several GPUs, and
+// cudaFuncSetAttribute / device attributes belong to the device that is current when they are called.
+struct PerDevice {
+  static constexpr int MAX = 64;
+  bool done[MAX] = {};
+  int value[MAX] = {};
+  // index of the current device, or -1 when it cannot be tracked (then the caller repeats the set-up every time)
+  static int current() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX) return -1;
+    return dev;
+  }
+};
+int device_sm_count();   // multiprocessors of the current device (cached per device)
+
 static inline int cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -150,6 +165,7 @@ struct AttnArgs {
   long long q_stride = 0, kv_stride = 0, o_stride = 0;
   const void* dO = nullptr; void* dQ = nullptr; void* dK = nullptr; void* dV = nullptr;
   long long do_stride = 0, dq_stride = 0, dkv_stride = 0;
+  bool accumulate = false;         // reverse pass: add to dQ / dK / dV instead of overwriting them
   int B = 0, T = 0, H = 0, Hkv = 0, hd = 0, window_left = 0;
   const int* doc_start = nullptr;  // [B][T] or null
   void* ws = nullptr; size_t ws_bytes = 0;
@@ -183,6 +199,8 @@ int reduce_partials(const float* partial, int nrow, int ncol, float* out, const 
 // process exits.  cudaMalloc / cudaFree on every call cost more than the kernels.  Those entry points synchronise
 // before returning, so consecutive calls may share it; calls from several host threads at once may not.
 int standalone_scratch(size_t bytes, char** out);
+// Their status word (bounded waits that ran out, bad token ids): one per device, allocated on first use.
+int standalone_status(unsigned int** out);
 
 // ---- lm_head tail ------------------------------------------------------------------------------
 // loss rows and (optionally) dX, dW of sum_valid(logsumexp(z) - z[target]), z = 15 tanh(xW/15),

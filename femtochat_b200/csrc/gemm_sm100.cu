@@ -590,16 +590,18 @@ bool gemm_tc_supported(const GemmArgs& g) {
   return true;
 }
 
-static int num_sms() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
+int device_sm_count() {
+  static PerDevice pd;
+  const int dev = PerDevice::current();
+  if (dev >= 0 && pd.done[dev]) return pd.value[dev];
+  int n = 0, cur = 0;
+  cudaGetDevice(&cur);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, cur);
+  if (n <= 0) n = 148;
+  if (dev >= 0) { pd.value[dev] = n; pd.done[dev] = true; }
   return n;
 }
+static int num_sms() { return device_sm_count(); }
 
 // Optional per-launch timing of the GEMM kernel (measurement aid, off by default).
 namespace {
@@ -676,13 +678,14 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
     p.tma_store = 1;
   }
   const int grid = std::min(p.total_units, sms);
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDevice attr;
+  const int dev = PerDevice::current();
+  if (dev < 0 || !attr.done[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr_done = true;
+    if (dev >= 0) attr.done[dev] = true;
   }
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (g_prof.on) {

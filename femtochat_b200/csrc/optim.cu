@@ -361,6 +361,79 @@ template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& 
   return 0;
 }
 
+// X_out[k][in][out] = fac * Polar-Express direction: the stand-alone form of muon_direction! (src/optim.jl:198-236)
+// on a contiguous stack of k fp32 gradients G[k][in][out] (the stored orientation of a Julia (out, in) matrix).
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256) k_direction_out(const T* __restrict__ X, const float* __restrict__ fac,
+                                                       float* __restrict__ out_, long long per, int out, int by_col, int dim) {
+  const int k = blockIdx.y;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+    const int j = by_col ? (int)(i % out) : (int)(i / out);
+    out_[k * per + i] = to_f<T>(X[k * per + i]) * fac[(long long)k * dim + j];
+  }
+}
+__global__ void k_stack_offsets(long long* offs, int k, long long per) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < k) offs[i] = (long long)i * per;
+}
+}  // namespace
+
+template <typename T>
+static int muon_direction_t(float* X_out, const float* G, float* mom, float* v, int k, int in, int out, float mu, float b2,
+                            float nt, const float* coeffs, int steps, unsigned int* status, char* buf, cudaStream_t s) {
+  const long long per = (long long)in * out;
+  const size_t r = std::min(in, out);
+  auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+  char* p = buf;
+  float* X = (float*)p; p += al(4 * per * k);
+  T* Xa = (T*)p; p += al(sizeof(T) * per * k);
+  T* Xb = (T*)p; p += al(sizeof(T) * per * k);
+  T* A = (T*)p; p += al(sizeof(T) * r * r * k);
+  T* B2 = (T*)p; p += al(sizeof(T) * r * r * k);
+  float* vec = (float*)p; p += al(4 * (size_t)k * std::max(in, out));
+  float* fac = (float*)p; p += al(4 * (size_t)k * std::max(in, out));
+  long long* offs = (long long*)p; p += al(8 * (size_t)k);
+  void* ws = p;
+  const size_t wsb = (size_t)160 << 20;
+  k_stack_offsets<<<cdiv(k, 256), 256, 0, s>>>(offs, k, per);
+  KERNEL_CHECK();
+  dim3 eg(egrid(per), k);
+  k_muon_momentum<<<eg, 256, 0, s>>>(G, offs, mom, X, per, mu, 1.f / nt);
+  KERNEL_CHECK();
+  k_sumsq_cols<float><<<dim3(cdiv(out, 256), k), 256, 0, s>>>(X, in, out, vec);
+  KERNEL_CHECK();
+  k_muoneq_factors<<<k, 256, 0, s>>>(vec, out, fac);
+  KERNEL_CHECK();
+  k_scale_cols_cast<T><<<eg, 256, 0, s>>>(X, fac, Xa, per, out);
+  KERNEL_CHECK();
+  FEMTO_TRY(newton_schulz_t<T>(Xa, Xb, A, B2, k, in, out, coeffs, steps, ws, wsb, status, s));
+  const bool by_col = out >= in;
+  const int dim = by_col ? out : in, dsize = by_col ? in : out;
+  if (by_col) k_sumsq_cols<T><<<dim3(cdiv(out, 256), k), 256, 0, s>>>(Xa, in, out, vec);
+  else k_sumsq_rows<T><<<dim3(cdiv(in, 8), k), 256, 0, s>>>(Xa, in, out, vec);
+  KERNEL_CHECK();
+  k_normuon_factors<<<k, 256, 0, s>>>(vec, dim, dsize, std::min(in, out), b2, v, fac);
+  KERNEL_CHECK();
+  k_direction_out<T><<<eg, 256, 0, s>>>(Xa, fac, X_out, per, out, by_col ? 1 : 0, dim);
+  KERNEL_CHECK();
+  return 0;
+}
+
+int muon_direction_standalone(int dtype, float* X_out, const float* G, float* mom, float* v, int k, int in, int out,
+                              float mu, float b2, float n_tokens, const float* coeffs, int steps, unsigned int* status,
+                              cudaStream_t s) {
+  const size_t es = dtype == FEMTO_BF16 ? 2 : 4;
+  const size_t per = (size_t)in * out, r = std::min(in, out);
+  auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+  const size_t total = al(4 * per * k) + 2 * al(es * per * k) + 2 * al(es * r * r * k) + 2 * al(4 * (size_t)k * std::max(in, out)) +
+                       al(8 * (size_t)k) + ((size_t)160 << 20) + 1024;
+  char* buf = nullptr;
+  FEMTO_TRY(standalone_scratch(total, &buf));
+  return dtype == FEMTO_BF16 ? muon_direction_t<bf16>(X_out, G, mom, v, k, in, out, mu, b2, n_tokens, coeffs, steps, status, buf, s)
+                             : muon_direction_t<float>(X_out, G, mom, v, k, in, out, mu, b2, n_tokens, coeffs, steps, status, buf, s);
+}
+
 int optimizer_state_sizes(femto_handle* h, long long* out4) {
   long long adam = 0, mm = 0, mv = 0;
   adam += (long long)h->Vp * h->d * 2;

@@ -88,9 +88,15 @@ extern "C" int32_t femto_xent_fused(int32_t dtype, const void* x, const void* W,
   a.loss_rows = (float*)p; p += al(4 * (size_t)N);
   a.dlogit = p; p += al(es * (size_t)chunk * ldw);
   a.ws = p; a.ws_bytes = wsb;
+  FEMTO_TRY(standalone_status(&a.status));
   int r = dtype == FEMTO_BF16 ? xent_tail<bf16>(a, s) : xent_tail<float>(a, s);
   if (!r) r = sum_rows_to_scalar(a.loss_rows, N, loss_out, targets0, n_valid_out, 0.f, s);
   cudaStreamSynchronize(s);
+  if (!r) {
+    unsigned int w = 0;
+    CUDA_TRY(cudaMemcpy(&w, a.status, sizeof(w), cudaMemcpyDeviceToHost));
+    if (w) { cudaMemset(a.status, 0, sizeof(w)); r = femto_fail(FEMTO_ERR_DEVICE_STATUS + (int)w, "device status word %u", w); }
+  }
   return r;
 }
 

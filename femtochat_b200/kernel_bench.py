@@ -1,4 +1,4 @@
-"""Isolated kernel sweep (BASELINE.json configs[1]): attention forward/reverse, fused lm_head tail,
+"""Isolated kernel sweep: attention forward/reverse, fused lm_head tail,
 Newton-Schulz chains and the GEMM forms of the step, timed with CUDA events on seeded Gaussian inputs.
 
     python -m femtochat_b200.kernel_bench [--kernel all|attn|xent|ns|gemm|stream] [--small] [--iters N]

@@ -192,11 +192,15 @@ int32_t femto_optimizer_set_t(femto_optimizer* o, const int32_t* h_t, int32_t co
 int32_t femto_attention_fwd(int32_t dtype, void* O, float* l, float* m, float* lse, const void* Q,
                             const void* K, const void* V, int32_t B, int32_t T, int32_t H, int32_t Hkv,
                             int32_t hd, int32_t window_left, const int32_t* doc_start, void* stream);
-/* Δattention!(A,dQ,dK,dV,dO,Q,K,V,O,l,m,window; accumulate=false) (ext/FemtoChatCUDAExt.jl:1771). */
+/* Δattention!(A,dQ,dK,dV,dO,Q,K,V,O,l,m,window; accumulate=true) (ext/FemtoChatCUDAExt.jl:1771-1776).  The saved
+ * row statistics are given either as lse = m + log l, or as the reference's pair (l, m) with lse NULL.
+ * accumulate != 0 adds to dQ / dK / dV (the reference's default), 0 overwrites them.  Synchronises before returning
+ * (its scratch is a grow-only buffer that the library keeps per device); a bounded wait that ran out inside a kernel
+ * comes back as FEMTO_ERR_DEVICE_STATUS + the status word. */
 int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const void* dO, const void* Q,
-                            const void* K, const void* V, const void* O, const float* lse, int32_t B,
-                            int32_t T, int32_t H, int32_t Hkv, int32_t hd, int32_t window_left,
-                            const int32_t* doc_start, void* stream);
+                            const void* K, const void* V, const void* O, const float* lse, const float* l,
+                            const float* m, int32_t B, int32_t T, int32_t H, int32_t Hkv, int32_t hd,
+                            int32_t window_left, const int32_t* doc_start, int32_t accumulate, void* stream);
 /* Same computation as femto_attention_bwd for callers that cannot allocate device memory (a host
  * runtime that owns the whole device pool, or a phase in which cudaMalloc is forbidden or would
  * stall the device).  No counterpart in the reference.  The scratch (two floats per (batch, head,
@@ -204,7 +208,10 @@ int32_t femto_attention_bwd(int32_t dtype, void* dQ, void* dK, void* dV, const v
  * B*H*T <= 1 048 576 and fails with FEMTO_ERR_SHAPE beyond that; it never calls cudaMalloc/cudaFree.
  * The first call on a device looks up the array's device address (make that call before any stream
  * capture).  All calls on a device share the array: calls that overlap on the GPU (different
- * streams) race; calls on one stream are safe.  Asynchronous on `stream`. */
+ * streams) race; calls on one stream are safe.  Asynchronous on `stream`; always overwrites dQ / dK / dV and takes
+ * lse only.  Its device status word (also part of the library image) is included in femto_status_word(NULL, ..).
+ * The cached device addresses are looked up without locking (two first calls from different host threads both do
+ * the lookup) and are not refreshed after cudaDeviceReset. */
 int32_t femto_attention_bwd_static(int32_t dtype, void* dQ, void* dK, void* dV, const void* dO, const void* Q,
                                    const void* K, const void* V, const void* O, const float* lse, int32_t B,
                                    int32_t T, int32_t H, int32_t Hkv, int32_t hd, int32_t window_left,
@@ -249,8 +256,32 @@ int32_t femto_adamw(float* theta, const float* delta, float* m, float* v, int64_
                     float beta1, float beta2, float eps, float lambda, int32_t t, float n_tokens,
                     void* stream);
 
+/* norm (src/gpt.jl:16-20): y = x / r, r = sqrt(mean(x^2) + eps) over each row of x [N][D]; r [N] is kept for the
+ * reverse.  eps is the caller's eps(eltype): 2^-7 in a bf16 model, 2^-23 in fp32.  Asynchronous. */
+int32_t femto_rmsnorm_fwd(int32_t dtype, const void* x, void* y, float* r, int32_t N, int32_t D, float eps,
+                          void* stream);
+/* Reverse of norm (ext/FemtoChatMooncakeExt.jl:248-255) from the saved output: dx = (dy - y mean(dy y)) / r,
+ * which equals dy / r - x sum(dy x) / (D r^3).  Asynchronous. */
+int32_t femto_rmsnorm_bwd(int32_t dtype, const void* dy, const void* y, const float* r, void* dx, int32_t N,
+                          int32_t D, void* stream);
+/* The Embedding call E[:, tokens] (src/gpt.jl:34; GPU kernel ext/FemtoChatCUDAExt.jl:63-75): out[n] = table[tokens0[n]],
+ * table [rows][D] and out [N][D] of `dtype`, tokens 0-based.  An id outside 0..rows-1 is clamped and raises bit 1 of
+ * the status word that femto_status_word(NULL, ..) reads.  Asynchronous. */
+int32_t femto_embed_gather(int32_t dtype, void* out, const void* table, const int32_t* tokens0, int32_t N, int32_t D,
+                           int32_t rows, void* stream);
+/* muon_direction! (src/optim.jl:198-236) on a stack of k same-shape matrices: Nesterov momentum, MuonEq row
+ * equilibration, Polar Express in `dtype`, Muon+ renormalisation and the NorMuon second-moment scaling.
+ * G, momentum and X_out are fp32 [k][rows][cols] where a Julia (m, n) matrix is stored as rows = n, cols = m;
+ * second_moment is fp32 [k][cols] when cols >= rows, else [k][rows]
+ * (src/optim.jl:180).  momentum and second_moment are updated in place.  Synchronises before returning. */
+int32_t femto_muon_direction(int32_t dtype, float* X_out, const float* G, float* momentum, float* second_moment,
+                             int32_t k, int32_t rows, int32_t cols, float mu, float beta2, float n_tokens,
+                             const float* h_coeffs, int32_t steps, void* stream);
+
 /* ---- status --------------------------------------------------------------------------------- */
-/* Device status word (0 = ok): bounded waits that ran out, out-of-range token ids, ... */
+/* Device status word (0 = ok): bounded waits that ran out (bit 2), out-of-range token ids (bit 1), ...
+ * h == NULL reads the word of the stand-alone kernel-level entry points on the current device (after a
+ * cudaDeviceSynchronize). */
 int32_t femto_status_word(femto_handle* h, int32_t* h_out);
 int32_t femto_sync(femto_handle* h, void* stream);
 /* Number of kernels launched by this handle since creation (host counter). */

@@ -94,8 +94,8 @@ def test_attention_forward_and_reverse(dtype, B, T, H, Hkv, hd, left, docs):
                                      _lib.ptr(dev[1]), _lib.ptr(dev[2]), B, T, H, Hkv, hd, left, _lib.ptr(dsd), None))
     dQ, dK, dV = torch.zeros_like(dev[0]), torch.zeros_like(dev[1]), torch.zeros_like(dev[2])
     _lib.check(L.femto_attention_bwd(dtype, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dev[3]), _lib.ptr(dev[0]),
-                                     _lib.ptr(dev[1]), _lib.ptr(dev[2]), _lib.ptr(O), _lib.ptr(lse), B, T, H, Hkv, hd, left,
-                                     _lib.ptr(dsd), None))
+                                     _lib.ptr(dev[1]), _lib.ptr(dev[2]), _lib.ptr(O), _lib.ptr(lse), None, None, B, T, H, Hkv, hd,
+                                     left, _lib.ptr(dsd), 0, None))
     torch.cuda.synchronize()
     tol = 2e-2 if dtype == _lib.BF16 else 2e-5
     assert (O.double().cpu() - O_ref).abs().max() <= tol
@@ -105,6 +105,83 @@ def test_attention_forward_and_reverse(dtype, B, T, H, Hkv, hd, left, docs):
     for got, ref in ((dQ, dq_ref), (dK, dk_ref), (dV, dv_ref)):
         rel = (got.double().cpu() - ref).norm() / ref.norm()
         assert rel <= (1e-2 if dtype == _lib.BF16 else 1e-5), rel
+
+
+def test_attention_at_benchmark_shape_geometric_documents():
+    """The benchmark's attention shape: T=2048, 10 query / 5 kv heads, head_dim 128, short window 1024, documents of
+    geometric(512) length (B=1 so that the fp64 naive reference stays small)."""
+    import numpy as np
+    B, T, H, Hkv, hd, left = 1, 2048, 10, 5, 128, 1024
+    Q, K, V, dO, _ = _attn_inputs(_lib.BF16, B, T, H, Hkv, hd, seed=1, docs=False)
+    rng = np.random.default_rng(2)
+    starts, t = [], 0
+    while t < T:
+        n = int(min(max(rng.geometric(1.0 / 512), 2), T - t))
+        starts += [t] * n
+        t += n
+    ds = torch.tensor(starts, dtype=torch.int32)[None, :].contiguous()
+    Qd, Kd, Vd, dOd = (x.double() for x in (Q, K, V, dO))
+    O_ref = fo.naive_attention(Qd, Kd, Vd, (left, 0), ds.long())
+    _, l_ref, m_ref = fo.flash_attention_forward(Qd, Kd, Vd, (left, 0), ds.long())
+    dq_ref, dk_ref, dv_ref = fo.flash_attention_backward(dOd, Qd, Kd, Vd, O_ref, l_ref, m_ref, (left, 0), ds.long())
+    dev = [x.cuda() for x in (Q, K, V, dO)]
+    dsd = ds.cuda()
+    O = torch.zeros_like(dev[0])
+    lse = torch.zeros(B, H, T, device="cuda")
+    L = _lib.lib()
+    _lib.check(L.femto_attention_fwd(_lib.BF16, _lib.ptr(O), None, None, _lib.ptr(lse), _lib.ptr(dev[0]), _lib.ptr(dev[1]),
+                                     _lib.ptr(dev[2]), B, T, H, Hkv, hd, left, _lib.ptr(dsd), None))
+    dQ, dK, dV = torch.zeros_like(dev[0]), torch.zeros_like(dev[1]), torch.zeros_like(dev[2])
+    _lib.check(L.femto_attention_bwd(_lib.BF16, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dev[3]), _lib.ptr(dev[0]),
+                                     _lib.ptr(dev[1]), _lib.ptr(dev[2]), _lib.ptr(O), _lib.ptr(lse), None, None, B, T, H, Hkv,
+                                     hd, left, _lib.ptr(dsd), 0, None))
+    torch.cuda.synchronize()
+    assert (O.double().cpu() - O_ref).abs().max() <= 2e-2
+    assert (lse.double().cpu() - (m_ref + torch.log(l_ref))).abs().max() <= 1e-3
+    for got, ref in ((dQ, dq_ref), (dK, dk_ref), (dV, dv_ref)):
+        rel = (got.double().cpu() - ref).norm() / ref.norm()
+        assert rel <= 1e-2, rel
+
+
+@pytest.mark.parametrize("dtype,T,hd", [(_lib.BF16, 256, 128), (_lib.F32, 40, 16)])
+def test_attention_reverse_accumulates_and_takes_l_m(dtype, T, hd):
+    """The reference's call form (ext/FemtoChatCUDAExt.jl:1771-1776): the saved statistics are the row sum l and
+    the row max m, and accumulate=true (its default) adds to dQ / dK / dV."""
+    B, H, Hkv, left = 2, 4, 2, T // 2
+    Q, K, V, dO, ds = _attn_inputs(dtype, B, T, H, Hkv, hd, seed=5, docs=True)
+    dev = [x.cuda() for x in (Q, K, V, dO)]
+    dsd = ds.cuda()
+    O = torch.zeros_like(dev[0])
+    lse, l, m = (torch.zeros(B, H, T, device="cuda") for _ in range(3))
+    L = _lib.lib()
+    _lib.check(L.femto_attention_fwd(dtype, _lib.ptr(O), _lib.ptr(l), _lib.ptr(m), _lib.ptr(lse), _lib.ptr(dev[0]),
+                                     _lib.ptr(dev[1]), _lib.ptr(dev[2]), B, T, H, Hkv, hd, left, _lib.ptr(dsd), None))
+
+    def bwd(dQ, dK, dV, use_lm, acc):
+        _lib.check(L.femto_attention_bwd(dtype, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dev[3]), _lib.ptr(dev[0]),
+                                         _lib.ptr(dev[1]), _lib.ptr(dev[2]), _lib.ptr(O), None if use_lm else _lib.ptr(lse),
+                                         _lib.ptr(l) if use_lm else None, _lib.ptr(m) if use_lm else None, B, T, H, Hkv,
+                                         hd, left, _lib.ptr(dsd), acc, None))
+        torch.cuda.synchronize()
+
+    base = [torch.zeros_like(dev[0]), torch.zeros_like(dev[1]), torch.zeros_like(dev[2])]
+    bwd(*base, False, 0)
+    via_lm = [torch.full_like(x, 7.0) for x in base]          # accumulate=0 overwrites whatever was there
+    bwd(*via_lm, True, 0)
+    tol = 2e-2 if dtype == _lib.BF16 else 1e-5
+    for a, b in zip(base, via_lm):
+        assert (a.float() - b.float()).abs().max() <= tol * max(1.0, float(a.float().abs().max()))
+    g = torch.Generator().manual_seed(8)
+    init = [torch.randn(x.shape, generator=g).to(x.dtype).cuda() for x in base]
+    acc = [x.clone() for x in init]
+    bwd(*acc, False, 1)
+    for a, i0, b in zip(acc, init, base):
+        want = i0.float() + b.float()
+        assert (a.float() - want).abs().max() <= (3e-2 if dtype == _lib.BF16 else 1e-5) * max(1.0, float(want.abs().max()))
+    # neither form of the statistics given -> argument error, nothing launched
+    assert L.femto_attention_bwd(dtype, _lib.ptr(acc[0]), _lib.ptr(acc[1]), _lib.ptr(acc[2]), _lib.ptr(dev[3]),
+                                 _lib.ptr(dev[0]), _lib.ptr(dev[1]), _lib.ptr(dev[2]), _lib.ptr(O), None, None, None, B, T, H,
+                                 Hkv, hd, left, _lib.ptr(dsd), 0, None) == -1
 
 
 # ---- embedding gradient ---------------------------------------------------------------------------------
@@ -138,7 +215,11 @@ def test_embedding_gradient_segmented_scatter(dtype):
 
 # ---- lm_head tail -----------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype,N,D,V,ldw", [(_lib.F32, 70, 32, 50, 64), (_lib.BF16, 512, 256, 1000, 1024),
-                                              (_lib.BF16, 300, 64, 100, 128)])
+                                              (_lib.BF16, 300, 64, 100, 128),
+                                              # more tokens than one chunk of 8192: later chunks offset every row
+                                              # buffer, add to dW, and the last one is short
+                                              (_lib.BF16, 8192 + 300, 128, 1000, 1024), (_lib.F32, 8192 + 300, 32, 50, 64),
+                                              (_lib.BF16, 20000, 256, 1000, 1024)])
 def test_xent_fused_tail(dtype, N, D, V, ldw):
     g = torch.Generator().manual_seed(9)
     td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
@@ -273,3 +354,125 @@ def test_cross_entropy_on_materialised_logits(reduction):
     got = delta.double().cpu()
     assert torch.allclose(got[:, :V], delta0[:, :V].double() + d_ref, rtol=1e-5, atol=1e-6)
     assert torch.equal(got[:, V:], delta0[:, V:].double())   # padded columns untouched
+
+
+# ---- streaming kernels behind their own entry points --------------------------------------------------------------
+@pytest.mark.parametrize("dtype,N,D", [(_lib.F32, 37, 40), (_lib.F32, 9, 33), (_lib.BF16, 300, 1280), (_lib.BF16, 65, 128)])
+def test_rmsnorm_forward_and_reverse(dtype, N, D):
+    """norm (src/gpt.jl:16-20) and its reverse (ext/FemtoChatMooncakeExt.jl:248-255) with eps = eps(eltype)."""
+    td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
+    eps = fo.EPS_BF16 if dtype == _lib.BF16 else fo.EPS_F32
+    g = torch.Generator().manual_seed(N + D)
+    x = (torch.randn(N, D, generator=g) * 2).to(td)
+    dy = torch.randn(N, D, generator=g).to(td)
+    y_ref = fo.norm(x.double(), eps)
+    dx_ref = fo.norm_backward(dy.double(), x.double(), eps)
+    xd, dyd = x.cuda(), dy.cuda()
+    y, dx = torch.zeros_like(xd), torch.zeros_like(xd)
+    r = torch.zeros(N, device="cuda")
+    L = _lib.lib()
+    _lib.check(L.femto_rmsnorm_fwd(dtype, _lib.ptr(xd), _lib.ptr(y), _lib.ptr(r), N, D, eps, None))
+    _lib.check(L.femto_rmsnorm_bwd(dtype, _lib.ptr(dyd), _lib.ptr(y), _lib.ptr(r), _lib.ptr(dx), N, D, None))
+    torch.cuda.synchronize()
+    tol = 2e-2 if dtype == _lib.BF16 else 1e-5
+    assert (y.double().cpu() - y_ref).abs().max() <= tol
+    assert (r.double().cpu() - torch.sqrt(x.double().pow(2).mean(-1) + eps)).abs().max() <= 1e-5 * float(r.max())
+    assert (dx.double().cpu() - dx_ref).abs().max() <= tol * max(1.0, float(dx_ref.abs().max()))
+
+
+@pytest.mark.parametrize("dtype,D", [(_lib.F32, 36), (_lib.BF16, 640), (_lib.BF16, 30)])
+def test_embed_gather_is_bit_exact(dtype, D):
+    """E[:, tokens] (src/gpt.jl:34): a pure row copy, so bit-exact; a bad id is clamped and flagged, not a fault."""
+    td = torch.bfloat16 if dtype == _lib.BF16 else torch.float32
+    rows, N = 500, 1000
+    g = torch.Generator().manual_seed(D)
+    table = torch.randn(rows, D, generator=g).to(td)
+    tok = torch.randint(0, rows, (N,), generator=g, dtype=torch.int32)
+    L = _lib.lib()
+    tb, tk = table.cuda(), tok.cuda()
+    out = torch.zeros(N, D, device="cuda", dtype=td)
+    _lib.check(L.femto_embed_gather(dtype, _lib.ptr(out), _lib.ptr(tb), _lib.ptr(tk), N, D, rows, None))
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), table[tok.long()])
+    w = C.c_int32(-1)
+    _lib.check(L.femto_status_word(None, C.byref(w)))
+    assert w.value == 0
+    bad = tok.clone()
+    bad[3] = rows + 7
+    bd = bad.cuda()
+    _lib.check(L.femto_embed_gather(dtype, _lib.ptr(out), _lib.ptr(tb), _lib.ptr(bd), N, D, rows, None))
+    _lib.check(L.femto_status_word(None, C.byref(w)))
+    assert w.value & 1
+
+
+@pytest.mark.parametrize("dtype,k,m,n", [(_lib.F32, 3, 48, 24), (_lib.F32, 2, 24, 48), (_lib.F32, 2, 5, 12),
+                                          (_lib.BF16, 2, 512, 256), (_lib.BF16, 2, 256, 512), (_lib.BF16, 2, 256, 256)])
+def test_muon_direction_matches_oracle_two_steps(dtype, k, m, n):
+    """muon_direction! (src/optim.jl:198-236) on a stack of k Julia (m, n) matrices, two consecutive calls so that
+    the momentum and the NorMuon second moment carried between steps are compared as well."""
+    g = torch.Generator().manual_seed(m * 3 + n)
+    specs = [fo.Spec(i * m * n, (m, n)) for i in range(k)]
+    st = fo.MuonState(specs, 0.02, 0.95, 0.9, 0.0)
+    ora = fo.MuonAdamW.__new__(fo.MuonAdamW)
+    ora.coeffs, ora.compute_dtype = fo.POLAR_EXPRESS_COEFFS, (torch.bfloat16 if dtype == _lib.BF16 else None)
+    coeffs = (C.c_float * 15)(*[c for abc in fo.POLAR_EXPRESS_COEFFS for c in abc])
+    mom = torch.zeros(k, n, m, device="cuda")
+    v = torch.zeros(k, max(m, n), device="cuda")
+    out = torch.zeros(k, n, m, device="cuda")
+    L = _lib.lib()
+    for step in range(2):
+        G = torch.randn(k, m, n, generator=g) * 3                      # Julia orientation
+        X_ref = ora.muon_direction(st, G.clone(), 0.9, 64.0)
+        Gs = G.transpose(1, 2).contiguous().cuda()                     # stored orientation [k][n][m]
+        _lib.check(L.femto_muon_direction(dtype, _lib.ptr(out), _lib.ptr(Gs), _lib.ptr(mom), _lib.ptr(v), k, n, m, 0.9, 0.9,
+                                          64.0, coeffs, 5, None))
+        got = out.cpu().transpose(1, 2)
+        if dtype == _lib.F32:
+            assert (got - X_ref).abs().max() <= 2e-4 * max(1.0, float(X_ref.abs().max())), step
+        else:
+            assert cosine(got, X_ref) >= 0.995, step
+            assert abs(float(got.norm() / X_ref.norm()) - 1.0) <= 2e-2
+        assert (mom.cpu().transpose(1, 2) - st.m).abs().max() <= 1e-6 * max(1.0, float(st.m.abs().max()))
+        assert (v.cpu().reshape(st.v.shape) - st.v).abs().max() <= (2e-2 if dtype == _lib.BF16 else 1e-5) * float(st.v.abs().max())
+
+
+def test_muon_adamw_three_steps_bf16_against_oracle():
+    """The whole MuonAdamW step with the Polar-Express chain in bf16 (the training configuration) against the oracle
+    run with compute_dtype=bfloat16, on 256- and 512-wide matrices that take the tensor-core GEMM.  bf16 Newton-Schulz
+    amplifies rounding differences, so the comparison is on the update Theta_t - Theta_0: cosine >= 0.99 per step
+    over the Muon matrices, and 1e-5 absolute on everything AdamW owns (fp32 on both sides)."""
+    kw = dict(sequence_len=32, max_document_tokens=64, vocab_size=512, n_layer=2, n_head=2, n_kv_head=1, n_embed=256,
+              window_pattern="SL")
+    cfg, ocfg = fb.GPTConfig(**kw), fo.GPTConfig(**kw)
+    lay, olay = fb.parameter_layout(cfg), fo.parameter_layout(ocfg)
+    th0 = torch.zeros(lay.nparams)
+    fo.initialize(th0, ocfg, olay, 17, all_nonzero=True)
+    g = torch.Generator().manual_seed(21)
+    deltas = [torch.randn(lay.nparams, generator=g) * 0.5 for _ in range(3)]
+    oopt = fo.MuonAdamW(olay, weight_decay=0.1, compute_dtype=torch.bfloat16)
+    th_ref = th0.clone()
+    params = fb.Params(th0.clone().cuda())
+    st = fb.GradientState(cfg, max_batch=1, compute_type="bfloat16")
+    st.refresh_weights(params.theta)
+    opt = fb.MuonAdamW(params, lay, st, weight_decay=0.1, compute_type="bfloat16")
+    muon_mask = torch.zeros(lay.nparams, dtype=torch.bool)
+    for grp in opt.muon:
+        for sp in grp.specs:
+            muon_mask[sp.offset:sp.offset + sp.size] = True
+    prev_ref, prev = th0.clone(), th0.clone()
+    for i, d in enumerate(deltas):
+        kwargs = dict(eta=0.5 + 0.25 * i, mu=0.9, lam=0.05, Nt=64.0)
+        oopt.step(th_ref, d, **kwargs)
+        params.delta.copy_(d.cuda())
+        opt.step(**kwargs)
+        got = params.theta.cpu()
+        assert (got[~muon_mask] - th_ref[~muon_mask]).abs().max() <= 1e-5
+        for grp in opt.muon:
+            for sp in grp.specs:
+                sl = slice(sp.offset, sp.offset + sp.size)
+                c = cosine(got[sl] - prev[sl], th_ref[sl] - prev_ref[sl])
+                assert c >= (0.99 if min(sp.shape) >= 128 else 0.95), (i, sp.shape, c)
+        prev_ref, prev = th_ref.clone(), got.clone()
+        params.theta.copy_(th_ref.cuda())      # keep both sides on the same trajectory
+        st.refresh_weights(params.theta)
+    assert st.status_word() == 0

@@ -100,3 +100,143 @@ def test_packed_batches_follow_loader_format():
     b = fb.PackedBatches(V, T, B, seed=5).next()[0]
     c = fb.PackedBatches(V, T, B, seed=5, rank=1).next()[0]
     assert (a == b).all() and (a != c).any()
+
+
+def _header_prototypes():
+    """name -> (return kind, [argument kinds]) of every function declared in include/femto.h; a kind is
+    'ptr', 'i32', 'i64', 'f32' or 'f64'."""
+    hdr = open(os.path.join(ROOT, "include", "femto.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+
+    def kind(decl):
+        decl = decl.strip()
+        if "*" in decl:
+            return "ptr"
+        for pat, k in (("int32_t", "i32"), ("int64_t", "i64"), ("float", "f32"), ("double", "f64")):
+            if re.search(rf"\b{pat}\b", decl):
+                return k
+        raise AssertionError(f"unknown C type in {decl!r}")
+
+    out = {}
+    for m in re.finditer(r"([A-Za-z_][A-Za-z0-9_ ]*?[\s\*]+)(femto_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", hdr):
+        ret, name, args = m.group(1), m.group(2), m.group(3).strip()
+        out[name] = (kind(ret), [] if args in ("", "void") else [kind(a) for a in args.split(",")])
+    return out
+
+
+def test_ctypes_table_matches_the_header():
+    """Every signature in femtochat_b200/_lib.py has the header's argument count and kinds."""
+    protos = _header_prototypes()
+    kinds = {ctypes.c_int32: "i32", ctypes.c_int64: "i64", ctypes.c_float: "f32", ctypes.c_double: "f64"}
+
+    def kind(t):
+        return kinds.get(t, "ptr")
+
+    for name, (res, args) in _lib.SIGNATURES.items():
+        assert name in protos, name
+        assert [kind(a) for a in args] == protos[name][1], name
+        assert kind(res) == protos[name][0], name
+
+
+def test_julia_shim_ccalls_match_the_header():
+    """julia/FemtoChatCUDAExt.jl cannot be executed here (no Julia toolchain), so each of its ccall signatures is
+    parsed and compared with include/femto.h: same entry point name, same number of arguments, and each Julia
+    argument type the right width (Int32 / Int64 / Float32 / pointer-like)."""
+    src = open(os.path.join(ROOT, "julia", "FemtoChatCUDAExt.jl")).read()
+    protos = _header_prototypes()
+
+    def jl_kind(t):
+        t = t.strip()
+        if t.startswith(("Ptr{", "CuPtr{", "Ref{")) or t == "Cstring":
+            return "ptr"
+        return {"Int32": "i32", "Int64": "i64", "Float32": "f32", "Float64": "f64"}[t]
+
+    def split_top(s):
+        parts, depth, cur = [], 0, ""
+        for ch in s:
+            if ch in "({[":
+                depth += 1
+            elif ch in ")}]":
+                depth -= 1
+            if ch == "," and depth == 0:
+                parts.append(cur)
+                cur = ""
+            else:
+                cur += ch
+        if cur.strip():
+            parts.append(cur)
+        return [p.strip() for p in parts]
+
+    seen = set()
+    for m in re.finditer(r"ccall\(\(:(femto_[a-z0-9_]+), libfemto\),\s*([A-Za-z0-9]+),\s*\(", src):
+        name, ret = m.group(1), m.group(2)
+        i, depth = m.end(), 1                        # scan the argument-type tuple to its closing parenthesis
+        while depth:
+            depth += {"(": 1, ")": -1}.get(src[i], 0)
+            i += 1
+        types = [t for t in split_top(src[m.end():i - 1]) if t]
+        assert name in protos, f"{name} is not declared in include/femto.h"
+        want_ret, want_args = protos[name]
+        assert jl_kind(ret) == want_ret, name
+        assert [jl_kind(t) for t in types] == want_args, (name, types, want_args)
+        # the call passes as many values as the tuple has types
+        j, depth = i, 0
+        while True:
+            depth += {"(": 1, ")": -1}.get(src[j], 0)
+            if depth < 0:
+                break
+            j += 1
+        values = [v for v in split_top(src[i:j]) if v]
+        assert len(values) == len(types), (name, len(values), len(types))
+        seen.add(name)
+    # every seam that INTEGRATION.md maps is bound
+    for name in ("femto_create", "femto_destroy", "femto_refresh_weights", "femto_loss_and_gradient", "femto_forward_loss",
+                 "femto_forward_logits", "femto_forward_token_losses", "femto_optimizer_state_sizes",
+                 "femto_optimizer_create", "femto_optimizer_step", "femto_optimizer_set_t", "femto_optimizer_destroy",
+                 "femto_attention_fwd", "femto_attention_bwd", "femto_embedding_gradient", "femto_embed_gather",
+                 "femto_rmsnorm_fwd", "femto_rmsnorm_bwd", "femto_gemm_bf16", "femto_newton_schulz",
+                 "femto_muon_direction", "femto_adamw", "femto_cross_entropy", "femto_cross_entropy_gradient",
+                 "femto_status_word", "femto_last_error"):
+        assert name in seen, f"{name} is not bound in the Julia shim"
+    # the methods the reference's extension defines are defined here too
+    for method in ("function gradient_state(", "function loss_and_gradient!(", "function MuonAdamW(", "function attention!(",
+                   "function Δattention!(", "function embedding_gradient!(", "function batched_mul!(", "function gather!(",
+                   "function scatter!("):
+        assert method in src, method
+    assert "accumulate::Bool=true" in src          # the reference's default for Δattention!
+    assert "reduction=:mean" in src                # the reference drivers differentiate the mean loss
+
+
+@pytest.mark.parametrize("world", [2, 3, 8, 32])
+def test_shard_plan_tiles_the_parameter_vector(world):
+    """Owner-sharded update: the single-owner ranges are disjoint, lie inside [0, nparams), give every Muon matrix
+    exactly one owner and every divisible large table `world` equal slices; the rest is replicated.  Also with more
+    ranks than layers (some ranks then own no block)."""
+    kw = dict(sequence_len=64, max_document_tokens=64, vocab_size=32768, n_layer=5, n_head=2, n_kv_head=1, n_embed=128,
+              window_pattern="SL")
+    lay = fb.parameter_layout(fb.GPTConfig(**kw))
+    plan = fb.shard_plan(lay, world)
+    at = 0
+    owned = 0
+    for off, n, owner in plan:
+        assert off >= at and n > 0 and 0 <= owner < world       # sorted and disjoint
+        at = off + n
+        owned += n
+    assert at <= lay.nparams
+    mats = sum(b[k].size for b in lay.blocks for k in ("wq", "wk", "wv", "wo", "fc", "proj", "ve_gate") if b[k] is not None)
+    tables = [lay.lm_head, lay.embedding] + [b["ve_table"] for b in lay.blocks if b["ve_table"] is not None]
+    big = sum(t.size for t in tables if t.size >= fb.optim.SHARD_MIN_TABLE and t.size % (4 * world) == 0)
+    assert owned == mats + big
+    # every Muon matrix lies inside exactly one range of one owner
+    for b in lay.blocks:
+        for k in ("wq", "wk", "wv", "wo", "fc", "proj", "ve_gate"):
+            sp = b[k]
+            if sp is None:
+                continue
+            inside = [(o, n, r) for o, n, r in plan if o <= sp.offset and sp.offset + sp.size <= o + n]
+            assert len(inside) == 1, k
+    # table slices: rank r owns slice r
+    for t in tables:
+        if t.size >= fb.optim.SHARD_MIN_TABLE and t.size % (4 * world) == 0:
+            for r in range(world):
+                assert (t.offset + r * (t.size // world), t.size // world, r) in plan

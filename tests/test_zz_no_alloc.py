@@ -30,8 +30,15 @@ def _bwd(fn, dtype, Q, K, V, dO, O, lse, left):
     B, T, H, hd = Q.shape
     Hkv = K.shape[2]
     dQ, dK, dV = torch.full_like(Q, 7.0), torch.full_like(K, 7.0), torch.full_like(V, 7.0)
-    _lib.check(fn(dtype, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dO), _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V),
-                  _lib.ptr(O), _lib.ptr(lse), B, T, H, Hkv, hd, left, None, None))
+    L = _lib.lib()
+    if fn == "static":
+        _lib.check(L.femto_attention_bwd_static(dtype, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dO), _lib.ptr(Q),
+                                                _lib.ptr(K), _lib.ptr(V), _lib.ptr(O), _lib.ptr(lse), B, T, H, Hkv, hd, left,
+                                                None, None))
+    else:    # the allocating entry point: lse form of the statistics, accumulate = 0
+        _lib.check(L.femto_attention_bwd(dtype, _lib.ptr(dQ), _lib.ptr(dK), _lib.ptr(dV), _lib.ptr(dO), _lib.ptr(Q), _lib.ptr(K),
+                                         _lib.ptr(V), _lib.ptr(O), _lib.ptr(lse), None, None, B, T, H, Hkv, hd, left, None, 0,
+                                         None))
     torch.cuda.synchronize()
     return dQ, dK, dV
 
@@ -43,8 +50,8 @@ def test_static_scratch_matches_allocating_entry_point_twice(dtype, shape):
     first = _case(dtype, B, T, H, Hkv, hd, left, seed=1)
     second = _case(dtype, B, T, H, Hkv, hd, left, seed=2)   # different data: stale scratch would show
     for data in (first, second):
-        ref = _bwd(L.femto_attention_bwd, dtype, *data, left)
-        got = _bwd(L.femto_attention_bwd_static, dtype, *data, left)
+        ref = _bwd("allocating", dtype, *data, left)
+        got = _bwd("static", dtype, *data, left)
         for r, g in zip(ref, got):
             assert torch.isfinite(g.float()).all()
             assert torch.equal(r, g)     # same kernels, same order of summation: bit-identical
