@@ -51,6 +51,7 @@ unsigned int static_entry_status_word() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES || !g_status_ptr[dev]) return 0;
   unsigned int w = 0;
   if (cudaMemcpy(&w, g_status_ptr[dev], sizeof(w), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+  if (w) cudaMemset(g_status_ptr[dev], 0, sizeof(w));   // read and clear
   return w;
 }
 

@@ -498,7 +498,10 @@ int32_t femto_status_word(femto_handle* h, int32_t* out) {
     int dev = -1;
     CUDA_TRY(cudaGetDevice(&dev));
     CUDA_TRY(cudaDeviceSynchronize());
-    if (dev >= 0 && dev < 64 && g_sa_status[dev]) CUDA_TRY(cudaMemcpy(&v, g_sa_status[dev], sizeof(v), cudaMemcpyDeviceToHost));
+    if (dev >= 0 && dev < 64 && g_sa_status[dev]) {
+      CUDA_TRY(cudaMemcpy(&v, g_sa_status[dev], sizeof(v), cudaMemcpyDeviceToHost));
+      if (v) CUDA_TRY(cudaMemset(g_sa_status[dev], 0, sizeof(v)));   // read and clear
+    }
     *out = (int32_t)(v | static_entry_status_word());
     return 0;
   }

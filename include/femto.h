@@ -280,8 +280,9 @@ int32_t femto_muon_direction(int32_t dtype, float* X_out, const float* G, float*
 
 /* ---- status --------------------------------------------------------------------------------- */
 /* Device status word (0 = ok): bounded waits that ran out (bit 2), out-of-range token ids (bit 1), ...
- * h == NULL reads the word of the stand-alone kernel-level entry points on the current device (after a
- * cudaDeviceSynchronize). */
+ * h == NULL reads AND CLEARS the word of the stand-alone kernel-level entry points on the current device (after a
+ * cudaDeviceSynchronize); a bit raised by an asynchronous entry point that nobody read is reported by the next
+ * synchronising one as FEMTO_ERR_DEVICE_STATUS + word. */
 int32_t femto_status_word(femto_handle* h, int32_t* h_out);
 int32_t femto_sync(femto_handle* h, void* stream);
 /* Number of kernels launched by this handle since creation (host counter). */

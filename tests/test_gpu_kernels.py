@@ -433,7 +433,7 @@ def test_muon_direction_matches_oracle_two_steps(dtype, k, m, n):
             assert cosine(got, X_ref) >= 0.995, step
             assert abs(float(got.norm() / X_ref.norm()) - 1.0) <= 2e-2
         assert (mom.cpu().transpose(1, 2) - st.m).abs().max() <= 1e-6 * max(1.0, float(st.m.abs().max()))
-        assert (v.cpu().reshape(st.v.shape) - st.v).abs().max() <= (2e-2 if dtype == _lib.BF16 else 1e-5) * float(st.v.abs().max())
+        assert (v.cpu().reshape(st.v.shape) - st.v).abs().max() <= (6e-2 if dtype == _lib.BF16 else 1e-5) * float(st.v.abs().max())
 
 
 def test_muon_adamw_three_steps_bf16_against_oracle():
