@@ -26,12 +26,13 @@ import femtochat_b200 as fb
 from femtochat_b200 import _lib
 
 CASES = {
-    # fp32 build: differences are summation order only
+    # fp32 build: the gradients differ by summation order only (tol_delta); Theta and the moments pass through five
+    # Newton-Schulz iterations, which amplify those last-bit differences (tol)
     "fp32": dict(cfg=dict(sequence_len=32, max_document_tokens=64, vocab_size=8192, n_layer=5, n_head=2, n_kv_head=1,
-                          n_embed=128, window_pattern="SL"), ctype="float32", tol=2e-5),
+                          n_embed=128, window_pattern="SL"), ctype="float32", tol_delta=1e-5, tol=2e-4),
     # bf16 build on the tensor-core kernels: each rank's partial gradient is rounded on its own
     "bf16": dict(cfg=dict(sequence_len=256, max_document_tokens=512, vocab_size=4096, n_layer=4, n_head=4, n_kv_head=2,
-                          n_embed=512, window_pattern="SL"), ctype="bfloat16", tol=2e-2),
+                          n_embed=512, window_pattern="SL"), ctype="bfloat16", tol_delta=1e-3, tol=2e-2),
 }
 
 
@@ -87,6 +88,7 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
 
     worst = dict(loss=0.0, delta=0.0, theta=0.0, moments=0.0)
     nt_exact = True
+    replicated = True
     loss_acc = torch.zeros(1, device="cuda")
     nv_acc = torch.zeros(1, dtype=torch.int32, device="cuda")
     for step in range(steps):
@@ -109,6 +111,12 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
         opt.step(**kw)
         opt.gather_state()
         torch.cuda.synchronize()
+        # Theta identical on every rank (bitwise) after the exchange, before anything else touches it
+        cs = torch.stack([params.theta.double().sum(), params.theta.double().abs().sum()])
+        hi, lo = cs.clone(), cs.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        replicated = replicated and bool((hi == lo).all().item())
 
         # the owners' parts of delta travel to rank 0 for the comparison
         owner_parts = []
@@ -140,15 +148,9 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
             params.theta.copy_(rp.theta)
         dist.broadcast(params.theta, 0)
         st.refresh_weights(params.theta)
-    # Theta identical on every rank (bitwise) after the exchange
-    cs = torch.stack([params.theta.double().sum(), params.theta.double().abs().sum()])
-    hi, lo = cs.clone(), cs.clone()
-    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-    replicated = bool((hi == lo).all().item())
     status = st.status_word()
     tol = spec["tol"]
-    ok = (nt_exact and replicated and status == 0 and worst["loss"] <= 1e-5 + tol * 1e-2 and worst["delta"] <= tol and
+    ok = (nt_exact and replicated and status == 0 and worst["loss"] <= 1e-5 + tol * 1e-2 and worst["delta"] <= spec["tol_delta"] and
           worst["theta"] <= tol and worst["moments"] <= tol)
     opt.close()
     st.close()
