@@ -4,4 +4,5 @@ from .gpt import GPT, GradientState, gradient_state, initialize_, loss_and_gradi
 from .optim import MuonAdamW, POLAR_EXPRESS_COEFFS, QUINTIC_COEFFS, shard_plan
 from .scaling import (estimate_flops, num_matmul_params, num_scaling_params, training_scaling, training_schedule,
                       PEAK_FLOPS_B200, PEAK_BANDWIDTH_B200)
-from .data import PackedBatches, bos_token_id
+from .data import PackedBatches, DevicePackedBatches, Feeder, bos_token_id
+from .checkpoints import optimizer_state, restore_optimizer_, save_checkpoint, load_checkpoint

@@ -30,6 +30,11 @@ class TensorDesc(C.Structure):
                 ("cols", C.c_int64)]
 
 
+class Segment(C.Structure):
+    _fields_ = [("src", C.c_int64), ("col", C.c_int32), ("row", C.c_int32), ("n", C.c_int32), ("pos0", C.c_int32),
+                ("next", C.c_int32), ("reserved", C.c_int32)]
+
+
 class OptimizerConfig(C.Structure):
     _fields_ = [
         ("unembedding_lr", C.c_float), ("embedding_lr", C.c_float), ("matrix_lr", C.c_float),
@@ -64,6 +69,12 @@ SIGNATURES = {
     "femto_forward_logits": (I32, [P, P, P, P, I32, P, P]),
     "femto_forward_token_losses": (I32, [P, P, P, P, P, I32, P, P, P]),
     "femto_loss_and_gradient_host": (I32, [P, P, P, P, P, P, I32, I32, I32, C.POINTER(F), C.POINTER(I32), P]),
+    "femto_pack_batch": (I32, [P, I64, P, I32, I32, I32, I32, I32, P, P, P, P, P]),
+    "femto_feeder_create": (I32, [I32, I32, I32, C.POINTER(P)]),
+    "femto_feeder_destroy": (I32, [P]),
+    "femto_feeder_submit": (I32, [P, P, P, P]),
+    "femto_feeder_next": (I32, [P, P, C.POINTER(P), C.POINTER(P), C.POINTER(P)]),
+    "femto_feeder_release": (I32, [P, P]),
     "femto_grad_sync": (I32, [P, P, P, P, P]),
     "femto_set_overlap": (I32, [P, I32]),
     "femto_optimizer_state_sizes": (I32, [P, C.POINTER(I64)]),

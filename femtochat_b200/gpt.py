@@ -121,14 +121,19 @@ def _dev_i32(x):
 
 
 def loss_and_gradient_(params: Params, state: GradientState, layout: Layout, tokens, targets, positions=None,
-                       reduction: str = "sum", accumulate: bool = False, sync: bool = True):
+                       reduction: str = "sum", accumulate: bool = False, sync: bool = True, batch: int = None):
     """`loss_and_gradient!` (ext/FemtoChatEnzymeExt.jl:38-44): fills params.δ (or adds to it, as
     the training script's later micro-steps do, scripts/train.jl:117-131) and returns the loss.
     With sync=False returns the device scalars (loss, n_valid) without waiting."""
-    tok, tgt, pos = _dev_i32(tokens), _dev_i32(targets), _dev_i32(positions)
-    B = tok.shape[0]
+    if isinstance(tokens, C.c_void_p):    # device pointers handed out by a Feeder: batch = the feeder's
+        if batch is None:
+            raise ValueError("pass batch= with raw device pointers")
+        ptok, ptgt, ppos, B = tokens, targets, positions, batch
+    else:
+        tok, tgt, pos = _dev_i32(tokens), _dev_i32(targets), _dev_i32(positions)
+        ptok, ptgt, ppos, B = _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), tok.shape[0]
     _lib.check(_lib.lib().femto_loss_and_gradient(
-        state.h, _lib.ptr(params.theta), _lib.ptr(params.delta), _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), B,
+        state.h, _lib.ptr(params.theta), _lib.ptr(params.delta), ptok, ptgt, ppos, B,
         _lib.REDUCTION[reduction], 1 if accumulate else 0, _lib.ptr(state._loss), _lib.ptr(state._nvalid),
         _lib.stream_ptr()))
     if not sync:

@@ -123,6 +123,39 @@ int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float*
                                      const int32_t* h_positions, int32_t B, int32_t reduction,
                                      int32_t accumulate, float* h_loss, int32_t* h_n_valid, void* stream);
 
+/* ---- batch producer (src/dataloader.jl:241-274; scripts/train.jl:144-145) ---------------------- */
+/* One run of a document inside a batch column: rows row..row+n-1 of column col take the tokens
+ * stream[src..src+n-1]; positions count up from pos0; the target of the last row is `next` (0-based id of the
+ * document's next token when it continues in the following batch, BOS when it ends here, -1 for none). */
+typedef struct femto_segment {
+  int64_t src;
+  int32_t col, row, n, pos0, next, reserved;
+} femto_segment;
+/* model_batch! (src/dataloader.jl:241-274) on the device: builds the three int32 [B][T] arrays of a packed batch
+ * from a token stream that already lies in device memory as 0-based 16-bit ids (documents back to back, each
+ * starting with BOS) and a list of segments (device array; the O(#documents) assignment of documents to columns
+ * stays on the host).  Rows no segment covers are padding: token BOS, target -1, position 0 (:243-245).  Ids are
+ * written with `index_base` added (1 = the reference's 1-based ids).  A segment that leaves the batch or the
+ * stream is skipped and raises bit 1 of *status (device word, may be NULL).  Asynchronous. */
+int32_t femto_pack_batch(const uint16_t* stream0, int64_t n_stream, const femto_segment* segments,
+                         int32_t n_segments, int32_t B, int32_t T, int32_t bos0, int32_t index_base,
+                         int32_t* tokens, int32_t* targets, int32_t* positions, uint32_t* status, void* stream);
+/* Pinned, multi-buffered feeder for hosts that build batches on the CPU (the reference's producer task and
+ * Channel(2), scripts/train.jl:88-100,144-145): femto_feeder_submit copies the three host arrays into a pinned
+ * slot and queues the host-to-device copy on the feeder's own stream; femto_feeder_next makes `compute_stream` wait
+ * for the oldest submitted batch and returns its device arrays (positions NULL if none were submitted);
+ * femto_feeder_release, called once the work that reads them has been queued, lets the slot be refilled (the next
+ * femto_feeder_next does it implicitly).  With depth >= 2 the copy of batch i+1 overlaps the step on batch i.
+ * No counterpart as a function in the reference, where the copy is a blocking to_rarray inside the loop. */
+typedef struct femto_feeder femto_feeder;
+int32_t femto_feeder_create(int32_t B, int32_t T, int32_t depth, femto_feeder** h_out);
+int32_t femto_feeder_destroy(femto_feeder* f);
+int32_t femto_feeder_submit(femto_feeder* f, const int32_t* h_tokens, const int32_t* h_targets,
+                            const int32_t* h_positions);
+int32_t femto_feeder_next(femto_feeder* f, void* compute_stream, const int32_t** d_tokens,
+                          const int32_t** d_targets, const int32_t** d_positions);
+int32_t femto_feeder_release(femto_feeder* f, void* compute_stream);
+
 /* ---- data parallel (new; the reference is single-GPU, scripts/train.jl:13) ------------------- */
 /* Sums delta, loss and n_valid over ranks (in place).  No-op when world == 1. */
 int32_t femto_grad_sync(femto_handle* h, float* delta, float* loss_inout, int32_t* n_valid_inout,

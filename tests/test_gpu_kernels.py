@@ -476,3 +476,71 @@ def test_muon_adamw_three_steps_bf16_against_oracle():
         params.theta.copy_(th_ref.cuda())      # keep both sides on the same trajectory
         st.refresh_weights(params.theta)
     assert st.status_word() == 0
+
+
+# ---- batch producer ---------------------------------------------------------------------------------------------------
+def test_device_batch_producer_is_bit_exact_against_the_host_packer():
+    """model_batch! (src/dataloader.jl:241-274) on the device: tokens, targets and positions of five consecutive
+    batches equal the host packer's arrays bit for bit (documents continuing across batches, a document's last token
+    predicting BOS, positions restarting on BOS); padding rows and a bad segment follow the documented rules."""
+    V, T, B = 4096, 256, 6
+    host = fb.PackedBatches(V, T, B, max_document_tokens=300, mean_doc_len=40, seed=9)
+    dev = fb.DevicePackedBatches(V, T, B, batches=5, max_document_tokens=300, mean_doc_len=40, seed=9)
+    for _ in range(5):
+        want = host.next()
+        got = dev.next()
+        torch.cuda.synchronize()
+        for w, g in zip(want, got):
+            assert torch.equal(torch.from_numpy(w), g.cpu())
+    assert int(dev.status.item()) == 0
+    # padding: a batch with a single short segment
+    import numpy as np
+    from femtochat_b200.data import SEGMENT_DTYPE
+    segs = np.array([(0, 1, 3, 5, 7, -1, 0), (10, 9, 0, 4, 0, 2, 0)], dtype=SEGMENT_DTYPE)   # the second one is outside the batch
+    sd = torch.from_numpy(segs.view(np.uint8).reshape(-1)).cuda()
+    tok, tgt, pos = (torch.empty(B, T, dtype=torch.int32, device="cuda") for _ in range(3))
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.lib().femto_pack_batch(_lib.ptr(dev.stream), dev.n_stream, _lib.ptr(sd), 2, B, T, dev.bos - 1, 1,
+                                           _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), _lib.ptr(st), None))
+    torch.cuda.synchronize()
+    s16 = torch.from_numpy(dev._stream_host.astype(np.int32))
+    assert int(st.item()) & 1                                   # the out-of-range segment was flagged and skipped
+    assert torch.equal(tok[1, 3:8].cpu(), s16[0:5] + 1) and torch.equal(pos[1, 3:8].cpu(), torch.arange(7, 12, dtype=torch.int32))
+    assert torch.equal(tgt[1, 3:7].cpu(), s16[1:5] + 1) and int(tgt[1, 7]) == -1
+    mask = torch.ones(B, T, dtype=torch.bool)
+    mask[1, 3:8] = False
+    assert (tok.cpu()[mask] == dev.bos).all() and (tgt.cpu()[mask] == -1).all() and (pos.cpu()[mask] == 0).all()
+
+
+def test_feeder_delivers_batches_in_order_and_a_step_runs_from_it():
+    """The pinned multi-buffered feeder: batches come out in submission order with the submitted contents, a full
+    feeder and an empty one are refused with FEMTO_ERR_STATE, and a training step fed from it gives the loss of the
+    same step fed directly."""
+    kw = dict(sequence_len=96, max_document_tokens=64, vocab_size=100, n_layer=3, n_head=4, n_kv_head=2, n_embed=64,
+              window_pattern="SL")
+    cfg = fb.GPTConfig(**kw)
+    lay = fb.parameter_layout(cfg)
+    B, T = 3, 96
+    pk = fb.PackedBatches(100, T, B, max_document_tokens=64, mean_doc_len=20, seed=4)
+    batches = [pk.next() for _ in range(5)]
+    fd = fb.Feeder(B, T, depth=2)
+    fd.submit(*batches[0])
+    fd.submit(*batches[1])
+    L = _lib.lib()
+    assert L.femto_feeder_submit(fd.f, fd._host_ptr(batches[2][0]), fd._host_ptr(batches[2][1]), None) == -4   # full
+    theta = torch.zeros(lay.nparams)
+    fo.initialize(theta, fo.GPTConfig(**kw), fo.parameter_layout(fo.GPTConfig(**kw)), 3, all_nonzero=True)
+    params = fb.Params(theta.cuda())
+    st = fb.GradientState(cfg, max_batch=B)
+    st.refresh_weights(params.theta)
+    for i in range(5):
+        a, b, c = fd.next()
+        got = fb.loss_and_gradient_(params, st, lay, a, b, c, batch=B)
+        fd.release()
+        if i + 2 < 5:
+            fd.submit(*batches[i + 2])
+        want = fb.loss_and_gradient_(params, st, lay, *(torch.from_numpy(x) for x in batches[i]))
+        assert got == want, i
+    a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    assert L.femto_feeder_next(fd.f, None, C.byref(a), C.byref(b), C.byref(c)) == -4                       # empty
+    fd.close()

@@ -281,3 +281,53 @@ def test_owner_sharded_update_matches_full_update(cfgkw, ctype, world, tol):
         assert err <= tol * max(1.0, float(want.abs().max())), (name, err)
     opts[0].shard(0, 1)                                # back to the full update
     assert opts[0].shard_ranges() == []
+
+
+def test_checkpoint_round_trip_resumes_bit_for_bit(tmp_path):
+    """src/checkpoints.jl:9-39: the per-group optimiser state (AdamW m, v, t; Muon momentum and NorMuon second moment)
+    and Theta go to a file, a FRESH optimiser restores them, and the next update equals the uninterrupted run's bit
+    for bit.  The saved groups have the reference's order and shapes."""
+    cfg = fb.GPTConfig(**SHARD)
+    lay = fb.parameter_layout(cfg)
+    theta0 = torch.empty(lay.nparams, dtype=torch.float32, device="cuda")
+    fb.initialize_(theta0, lay, seed=5, all_nonzero=True)
+    st = fb.GradientState(cfg, max_batch=1)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    deltas = [torch.randn(lay.nparams, generator=g, device="cuda") * 0.3 for _ in range(3)]
+    kw = dict(eta=0.7, mu=0.9, lam=0.05, Nt=64.0)
+
+    a = fb.Params(theta0.clone())
+    opt_a = fb.MuonAdamW(a, lay, st, weight_decay=0.1)
+    for d in deltas[:2]:
+        a.delta.copy_(d)
+        opt_a.step(**kw)
+    file = fb.save_checkpoint(str(tmp_path), 2, a, opt_a, dict(config=SHARD))
+    assert file.endswith("checkpoint_000002.pt") and not os.path.exists(file + ".part")
+    a.delta.copy_(deltas[2])
+    opt_a.step(**kw)
+
+    ck = fb.load_checkpoint(str(tmp_path), 2)
+    assert ck["step"] == 2 and ck["metadata"]["config"] == SHARD
+    saved = ck["optimizer"]
+    # the reference's group structure (src/optim.jl:333-425): lm_head, wte, per block [ve table], lam_b, lam_x0, then
+    # smear gate, lam_s, lam_y; Muon groups by shape in order of first appearance
+    n_ve = sum(1 for b in lay.blocks if b["ve_table"] is not None)
+    assert len(saved["adamw"]) == 2 + n_ve + 2 * cfg.n_layer + 3
+    assert saved["adamw"][0]["m"].numel() == lay.lm_head.size and saved["adamw"][1]["m"].numel() == lay.embedding.size
+    assert all(s["t"] == 2 for s in saved["adamw"])
+    d, kv = cfg.n_embed, cfg.n_embed // cfg.n_head * cfg.n_kv_head
+    shapes = [tuple(s["m"].shape) for s in saved["muon"]]         # row-major [k][cols][rows] of a Julia (rows, cols, k)
+    assert shapes[0] == (2 * cfg.n_layer, d, d) and shapes[1] == (2 * cfg.n_layer, d, kv)
+    assert shapes[2] == (cfg.n_layer, d, 4 * d) and shapes[3] == (cfg.n_layer, 4 * d, d)
+    assert tuple(saved["muon"][2]["v"].shape) == (cfg.n_layer, 4 * d)      # fc is (4d, d): rows >= cols -> (rows,1,k)
+
+    b = fb.Params(ck["parameters"].cuda())
+    opt_b = fb.MuonAdamW(b, lay, st, weight_decay=0.1)             # fresh moments, t = 0
+    fb.restore_optimizer_(opt_b, saved)
+    assert opt_b.get_t() == opt_a.get_t()[:0] + [2] * len(opt_b.adamw)
+    b.delta.copy_(deltas[2])
+    opt_b.step(**kw)
+    assert torch.equal(a.theta, b.theta)
+    for x, y in ((opt_a.adam_m, opt_b.adam_m), (opt_a.adam_v, opt_b.adam_v), (opt_a.muon_m, opt_b.muon_m),
+                 (opt_a.muon_v, opt_b.muon_v)):
+        assert torch.equal(x, y)
