@@ -6,3 +6,4 @@ from .scaling import (estimate_flops, num_matmul_params, num_scaling_params, tra
                       PEAK_FLOPS_B200, PEAK_BANDWIDTH_B200)
 from .data import PackedBatches, DevicePackedBatches, Feeder, bos_token_id
 from .checkpoints import optimizer_state, restore_optimizer_, save_checkpoint, load_checkpoint
+from .generation import KVCache, prefill, decode_step, generate, sample_token

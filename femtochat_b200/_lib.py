@@ -69,6 +69,11 @@ SIGNATURES = {
     "femto_forward_logits": (I32, [P, P, P, P, I32, P, P]),
     "femto_forward_token_losses": (I32, [P, P, P, P, P, I32, P, P, P]),
     "femto_loss_and_gradient_host": (I32, [P, P, P, P, P, P, I32, I32, I32, C.POINTER(F), C.POINTER(I32), P]),
+    "femto_kv_cache_create": (I32, [P, I32, I32, C.POINTER(P)]),
+    "femto_kv_cache_destroy": (I32, [P]),
+    "femto_kv_cache_length": (I32, [P]),
+    "femto_prefill": (I32, [P, P, P, P, P, I32, I32, P, P]),
+    "femto_decode_step": (I32, [P, P, P, P, P, I32, P, P]),
     "femto_pack_batch": (I32, [P, I64, P, I32, I32, I32, I32, I32, P, P, P, P, P]),
     "femto_feeder_create": (I32, [I32, I32, I32, C.POINTER(P)]),
     "femto_feeder_destroy": (I32, [P]),

@@ -276,10 +276,11 @@ __global__ void __launch_bounds__(1024) k_inv_nvalid(const int* tgt0, int n, flo
 template <typename T>
 static int step_t(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                   const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-                  int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out) {
+                  int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out, const StepExtra* ex) {
   typedef Stream<T> S;
-  const int N = B * h->T, d = h->d, dq = h->dq, kv = h->kv, H = h->H, Hkv = h->Hkv, hd = h->hd, Vp = h->Vp, V = h->V;
-  const int Tl = h->T, L = h->L;
+  const int Tl = (ex && ex->T > 0) ? ex->T : h->T;
+  const int N = B * Tl, d = h->d, dq = h->dq, kv = h->kv, H = h->H, Hkv = h->Hkv, hd = h->hd, Vp = h->Vp, V = h->V;
+  const int L = h->L;
   const float eps = h->eps;
   const bool mean = reduction == FEMTO_REDUCTION_MEAN;
   auto GA = [&]() { GemmArgs g; g.ws = h->gemm_ws; g.ws_bytes = h->gemm_ws_bytes; g.status = h->status; return g; };
@@ -340,6 +341,12 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   const T* xlast = (const T*)h->lb[L - 1].xout;
   const T* xb = (const T*)h->lb[h->backout].xout;
   FEMTO_TRY(S::backout_norm(xlast, xb, theta + h->off_lam_y, nullptr, (T*)h->xnf, h->rf, N, d, eps, s));
+
+  // ---- a prompt: its keys / values go to the cache, and only the last position of each column needs logits ----
+  if (ex && ex->cache) {
+    FEMTO_TRY(kv_cache_store_prompt<T>(ex->cache, B, Tl, s));
+    return kv_cache_last_logits<T>(ex->cache, (const T*)h->xnf, B, Tl, ex->last_logits, s);
+  }
 
   // ---- the model call without targets returns the soft-capped logits of the first V rows (src/gpt.jl:165-170) ----
   if (logits_out) {
@@ -445,9 +452,12 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
 
 int model_step(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-               int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out) {
-  if (!h || !theta || !tokens || (!logits_out && (!targets || (!loss_out && !token_losses_out))))
+               int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out, const StepExtra* ex) {
+  const bool prompt = ex && ex->cache && ex->last_logits;
+  if (!h || !theta || !tokens || (!logits_out && !prompt && (!targets || (!loss_out && !token_losses_out))))
     return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (ex && ex->T > 0 && (long long)B * ex->T > h->maxN) return femto_fail(FEMTO_ERR_SHAPE, "B x T = %d x %d exceeds the workspace", B, ex->T);
+  if (ex && ex->T > 0 && ex->T != h->T && backward) return femto_fail(FEMTO_ERR_UNSUPPORTED, "the reverse pass runs at sequence_len only");
   if (backward && !delta) return femto_fail(FEMTO_ERR_ARG, "delta is NULL");
   if (B <= 0 || B > h->maxB) return femto_fail(FEMTO_ERR_SHAPE, "B=%d outside 1..max_batch=%d", B, h->maxB);
   if (reduction != FEMTO_REDUCTION_SUM && reduction != FEMTO_REDUCTION_MEAN)
@@ -455,7 +465,7 @@ int model_step(femto_handle* h, const float* theta, float* delta, const int* tok
   if (!h->weights_valid) return femto_fail(FEMTO_ERR_STATE, "call femto_refresh_weights before the first step");
   if (!aligned16(theta) || (delta && !aligned16(delta))) return femto_fail(FEMTO_ERR_ALIGN, "Theta/delta must be 16-byte aligned");
   return h->bf ? step_t<bf16>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate, loss_out,
-                              nvalid_out, s, logits_out, token_losses_out)
+                              nvalid_out, s, logits_out, token_losses_out, ex)
                : step_t<float>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate,
-                               loss_out, nvalid_out, s, logits_out, token_losses_out);
+                               loss_out, nvalid_out, s, logits_out, token_losses_out, ex);
 }

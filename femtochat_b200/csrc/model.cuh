@@ -63,13 +63,25 @@ struct femto_handle {
   std::string err;
 };
 
+// Options of a forward pass that is not a training step: a sequence length other than the configured one (a
+// prompt) and a key/value cache that takes the prompt's keys and values (decode.cu).
+struct femto_kv_cache;
+struct StepExtra {
+  int T = 0;                        // rows per column of this call (0 = sequence_len)
+  femto_kv_cache* cache = nullptr;  // filled from the prompt when set
+  float* last_logits = nullptr;     // fp32 [B][vocab_size]: soft-capped logits of each column's last position
+};
+template <typename T> int kv_cache_store_prompt(femto_kv_cache* c, int B, int Tp, cudaStream_t s);
+template <typename T> int kv_cache_last_logits(femto_kv_cache* c, const T* xnf, int B, int Tp, float* logits_out, cudaStream_t s);
+
 int model_fill(femto_handle* h, const femto_config* cfg);  // derived sizes + layout, no device work
 int model_alloc(femto_handle* h);
 void model_free(femto_handle* h);
 int model_refresh(femto_handle* h, const float* theta, cudaStream_t s);
 int model_step(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-               int* nvalid_out, cudaStream_t s, float* logits_out = nullptr, float* token_losses_out = nullptr);
+               int* nvalid_out, cudaStream_t s, float* logits_out = nullptr, float* token_losses_out = nullptr,
+               const StepExtra* ex = nullptr);
 int layout_describe(const femto_config* cfg, std::vector<femto_tensor_desc>& out, long long* nparams, int* Vp);
 int layout_windows(const femto_config* cfg, std::vector<int>& left, std::vector<int>& has_ve);
 

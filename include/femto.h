@@ -123,6 +123,24 @@ int32_t femto_loss_and_gradient_host(femto_handle* h, const float* theta, float*
                                      const int32_t* h_positions, int32_t B, int32_t reduction,
                                      int32_t accumulate, float* h_loss, int32_t* h_n_valid, void* stream);
 
+/* ---- generation with a key/value cache (src/generation.jl:26-56) ----------------------------- */
+/* The reference's `generate` runs the whole context through the model for every new token (the cache is a TODO
+ * at src/gpt.jl:81).  Here femto_prefill runs the prompt once and keeps every block's keys and values;
+ * femto_decode_step then costs one row per column.  Logits are what `model(input; positions)[:, end, b]`
+ * returns: fp32 [B][vocab_size], soft-capped.  Sampling (temperature, top-k, src/generation.jl:7-24) stays on
+ * the host.  Valid while prompt + generated tokens <= max_len; the reference's sliding of the context window
+ * beyond sequence_len is a fresh femto_prefill of the slid context. */
+typedef struct femto_kv_cache femto_kv_cache;
+int32_t femto_kv_cache_create(femto_handle* h, int32_t max_batch, int32_t max_len, femto_kv_cache** h_out);
+int32_t femto_kv_cache_destroy(femto_kv_cache* c);
+int32_t femto_kv_cache_length(femto_kv_cache* c); /* tokens cached per column */
+/* tokens / positions: int32 [B][Tp] device arrays (positions NULL = 0..Tp-1); resets the cache to this prompt. */
+int32_t femto_prefill(femto_handle* h, femto_kv_cache* c, const float* theta, const int32_t* tokens,
+                      const int32_t* positions, int32_t B, int32_t Tp, float* logits_out, void* stream);
+/* tokens: int32 [B], one new token per column; positions: int32 [B] or NULL (= each column's last position + 1). */
+int32_t femto_decode_step(femto_handle* h, femto_kv_cache* c, const float* theta, const int32_t* tokens,
+                          const int32_t* positions, int32_t B, float* logits_out, void* stream);
+
 /* ---- batch producer (src/dataloader.jl:241-274; scripts/train.jl:144-145) ---------------------- */
 /* One run of a document inside a batch column: rows row..row+n-1 of column col take the tokens
  * stream[src..src+n-1]; positions count up from pos0; the target of the last row is `next` (0-based id of the

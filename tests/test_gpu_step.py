@@ -331,3 +331,77 @@ def test_checkpoint_round_trip_resumes_bit_for_bit(tmp_path):
     for x, y in ((opt_a.adam_m, opt_b.adam_m), (opt_a.adam_v, opt_b.adam_v), (opt_a.muon_m, opt_b.muon_m),
                  (opt_a.muon_v, opt_b.muon_v)):
         assert torch.equal(x, y)
+
+
+GEN = dict(sequence_len=64, max_document_tokens=128, vocab_size=100, n_layer=3, n_head=4, n_kv_head=2, n_embed=64,
+           window_pattern="SL")
+GEN_TC = dict(sequence_len=256, max_document_tokens=512, vocab_size=1000, n_layer=4, n_head=4, n_kv_head=2, n_embed=512,
+              window_pattern="SL")
+
+
+@pytest.mark.parametrize("cfgkw,ctype,doc_mask,tol", [(GEN, "float32", False, 1e-4), (GEN, "float32", True, 1e-4),
+                                                      (GEN_TC, "bfloat16", True, 3e-2)])
+def test_kv_cache_decode_matches_full_context_recompute(cfgkw, ctype, doc_mask, tol):
+    """src/generation.jl:40-52 recomputes the whole context for every token; with the key/value cache the prompt runs
+    once and each new token is one row.  The logits of every decoded position must equal the oracle's logits of the
+    full forward pass at that position (soft-capped, first vocab_size rows), for two columns with different
+    tokens, a short window, positions that restart inside the prompt (a second document) and the document mask."""
+    cfg, ocfg = fb.GPTConfig(**cfgkw), fo.GPTConfig(**cfgkw)
+    lay, olay = fb.parameter_layout(cfg), fo.parameter_layout(ocfg)
+    th = torch.zeros(lay.nparams)
+    fo.initialize(th, ocfg, olay, 13, all_nonzero=True)
+    T, V, B = cfgkw["sequence_len"], cfgkw["vocab_size"], 2
+    g = torch.Generator().manual_seed(6)
+    tok = torch.randint(1, V + 1, (B, T), generator=g, dtype=torch.int32)
+    pos = torch.arange(T, dtype=torch.int32)[None, :].repeat(B, 1)
+    pos[1, 9:] -= 9                                         # column 1: a new document starts at t = 9
+    sw = T // 4
+    eps = fo.EPS_BF16 if ctype == "bfloat16" else fo.EPS_F32
+    cache_o = {}
+    fo.Model(ocfg, fo.StepOptions(eps=eps, short_window=sw, doc_mask=doc_mask)).forward(
+        th.double() if ctype == "float32" else th, tok, tok, pos, cache=cache_o)
+    z_ref = cache_o["z"].float().reshape(B, T, V)           # logits of every position of the full sequence
+    tol = tol * float(z_ref.abs().max()) + 1e-6             # relative to the largest logit
+    model = fb.GPT(fb.Params(th.cuda()), cfg, lay, compute_type=ctype, short_window=sw, doc_mask=doc_mask)
+    st = model.state(B)
+    kc = fb.KVCache(st, B, T)
+    Tp = 20 if T == 64 else 131                             # the prompt; not a multiple of any tile size
+    z = fb.prefill(model, kc, tok[:, :Tp], pos[:, :Tp]).cpu()
+    assert len(kc) == Tp
+    assert (z - z_ref[:, Tp - 1]).abs().max() <= tol
+    for t in range(Tp, min(T, Tp + 40)):
+        z = fb.decode_step(model, kc, tok[:, t], pos[:, t]).cpu()
+        assert (z - z_ref[:, t]).abs().max() <= tol, t
+    assert len(kc) == min(T, Tp + 40)
+    assert st.status_word() == 0
+    # positions=None continues each column's document
+    kc2 = fb.KVCache(st, B, T)
+    fb.prefill(model, kc2, tok[:, :Tp], pos[:, :Tp])
+    z2 = fb.decode_step(model, kc2, tok[:, Tp]).cpu()
+    kc3 = fb.KVCache(st, B, T)
+    fb.prefill(model, kc3, tok[:, :Tp], pos[:, :Tp])
+    assert torch.equal(z2, fb.decode_step(model, kc3, tok[:, Tp], pos[:, Tp]).cpu())
+    for c in (kc, kc2, kc3):
+        c.close()
+
+
+def test_generate_with_cache_equals_generate_by_recompute():
+    """`generate` (src/generation.jl:26-56): greedy decoding (temperature 0) through the cache gives the tokens of
+    the reference's recompute-everything loop; with sampling the same generator state gives the same tokens."""
+    cfg = fb.GPTConfig(**GEN)
+    lay = fb.parameter_layout(cfg)
+    th = torch.zeros(lay.nparams)
+    fo.initialize(th, fo.GPTConfig(**GEN), fo.parameter_layout(fo.GPTConfig(**GEN)), 2, all_nonzero=True)
+    model = fb.GPT(fb.Params(th.cuda()), cfg, lay)
+    prompt = [5, 17, 3, 42]
+    a = fb.generate(model, prompt, max_new_tokens=12, temperature=0.0)
+    b = fb.generate(model, prompt, max_new_tokens=12, temperature=0.0, use_cache=False)
+    assert a == b and len(a) == 16 and a[:4] == prompt and all(1 <= t <= 100 for t in a)
+    ga, gb = torch.Generator().manual_seed(1), torch.Generator().manual_seed(1)
+    c = fb.generate(model, prompt, max_new_tokens=12, temperature=0.8, top_k=10, generator=ga)
+    d = fb.generate(model, prompt, max_new_tokens=12, temperature=0.8, top_k=10, generator=gb, use_cache=False)
+    assert c == d
+    # the context window slides once the sequence is longer than sequence_len (src/generation.jl:41-43)
+    e = fb.generate(model, list(range(1, 61)), max_new_tokens=8, temperature=0.0)
+    f = fb.generate(model, list(range(1, 61)), max_new_tokens=8, temperature=0.0, use_cache=False)
+    assert e == f and len(e) == 68
