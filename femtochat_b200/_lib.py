@@ -97,6 +97,7 @@ SIGNATURES = {
     "femto_attention_bwd": (I32, [I32, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, I32, P, I32, P]),
     "femto_attention_bwd_static": (I32, [I32, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, I32, P, P]),
     "femto_gemm_bf16": (I32, [P, I32, I64, P, I32, I64, P, I64, I32, I32, I32, I32, I64, I64, I64, I32, I32, P]),
+    "femto_gemm_pair_mode": (I32, [I32]),
     "femto_embedding_gradient": (I32, [I32, P, P, P, I32, I32, I32, P]),
     "femto_xent_fused": (I32, [I32, P, P, I64, P, I32, I32, I32, F, P, P, P, P, P]),
     "femto_newton_schulz": (I32, [I32, P, I32, I32, I32, C.POINTER(F), I32, P]),

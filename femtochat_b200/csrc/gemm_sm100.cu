@@ -20,18 +20,34 @@ using namespace sm100;
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int STORE_STAGE_BYTES = 8 * 4096;  // 8 epilogue warps x [32 rows][64 bf16]
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int TMEM_COLS = 512;
+constexpr int MAX_STAGES = 6;
+
+// One CTA per 128 x 256 tile (PAIR = false), or a pair of CTAs of one cluster per 256 x 256 tile (PAIR = true):
+// tcgen05.mma.cta_group::2 multiplies 256 rows at once, each CTA holding 128 rows of A and HALF of B's columns in
+// its own shared memory and its own 128 x 256 accumulator in its own TMEM.  A pair moves 2 x (16 + 16) KB of
+// operands per k-block where two single CTAs move 2 x (16 + 32) KB: a third less shared-memory and L2 traffic per
+// flop, and the smaller stages leave room for a six-deep ring.
+template <bool PAIR> struct Geo {
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;          // rows of an output tile (unit of scheduling)
+  static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN;        // columns of B this CTA loads
+  static constexpr int B_BYTES = BN_LOCAL * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SLOTS = PAIR ? 2 : 1;                 // 128-row halves per unit (split-K partial slots)
+};
 
 struct TcParams {
   GemmArgs g;
   int tiles_m, tiles_n, kblocks, splits, kb_per_split, total_units;
   float* partial;  // [unit][8 chunks][128 rows][32 cols] when splits > 1
   int tma_store;   // bf16 results leave through shared memory and TMA tiled stores
+  int pair;        // units are 256-row tiles computed by CTA pairs
   int a_slabs, b_slabs;  // an M/N-contiguous operand arrives with one 4-d copy per k-block instead of one per 64-wide slab
 };
 
@@ -100,8 +116,8 @@ __device__ __forceinline__ void stage_store_bf16(const float (&v)[32], uint8_t* 
 }
 
 // Tiles of a symmetric result that no element of the upper triangle touches (every role skips the same units).
-__device__ __forceinline__ bool below_diagonal(const GemmArgs& g, int mt, int nt) {
-  return g.upper_only && (nt + 1) * BN <= mt * BM;
+__device__ __forceinline__ bool below_diagonal(const GemmArgs& g, int mt, int nt, int tile_m) {
+  return g.upper_only && (nt + 1) * BN <= mt * tile_m;
 }
 
 // One 32-column chunk of one output row with a bf16 result: C = f(acc, aux).
@@ -162,11 +178,14 @@ __device__ __forceinline__ void bf16_chunk(const GemmArgs& g, float (&v)[32], in
   }
 }
 
-template <bool A_K, bool B_K>
+template <bool A_K, bool B_K, bool PAIR>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const TcParams p) {
+  typedef Geo<PAIR> G;
+  constexpr int STAGES = G::STAGES, STAGE_BYTES = G::STAGE_BYTES, TILE_M = G::TILE_M;
   extern __shared__ uint8_t smem_raw[];
+  // the same offsets in both CTAs of a pair: the shared-memory window of every CTA starts on the same alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* store_stage = smem + STAGES * STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + STORE_STAGE_BYTES);
@@ -179,18 +198,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const GemmArgs& g = p.g;
+  // In a pair the even CTA (rank 0) is the leader: its thread issues the MMAs of both, its `full` barriers count
+  // the bytes of both CTAs' loads and its `tempty` barriers the epilogue warps of both.
+  const int rank = PAIR ? (int)cluster_ctarank() : 0;
+  const int first_unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int unit_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 8); }
+    for (int i = 0; i < 2; i++) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], PAIR ? 16 : 8); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
+  if (PAIR) {
+    // the peer's barriers must exist before anything of this CTA can signal them
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc2(tmem_slot, TMEM_COLS); tmem_relinquish2(); }
+    else { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   }
   tc_fence_before();
   __syncthreads();
@@ -213,14 +242,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       uint32_t issued_mask = 0, last_parity = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      for (int u = first_unit; u < p.total_units && ok; u += unit_step) {
         int bz, mt, nt, kb0, kb1;
         unit_coords(u, bz, mt, nt, kb0, kb1);
-        if (below_diagonal(g, mt, nt)) continue;
+        if (below_diagonal(g, mt, nt, TILE_M)) continue;
+        const int m0 = mt * TILE_M + rank * BM;           // first row of A this CTA loads
+        const int n0 = nt * BN + rank * G::BN_LOCAL;      // first column of B this CTA loads (its half, in a pair)
         for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, g.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
+          if (PAIR) {
+            // the leader announces the bytes of both CTAs; the loads of either CTA are counted on its barrier
+            if (rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
+            if (A_K) tma_load_3d_pair(sa, &tmA, &full[stage], kb * BK, m0, bz);
+            else tma_load_4d_pair(sa, &tmA, &full[stage], 0, kb * BK, m0 / 64, bz);
+            if (B_K) tma_load_3d_pair(sb, &tmB, &full[stage], kb * BK, n0, bz);
+            else tma_load_4d_pair(sb, &tmB, &full[stage], 0, kb * BK, n0 / 64, bz);
+          } else {
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           if (A_K) {
             tma_load_3d(sa, &tmA, &full[stage], kb * BK, mt * BM, bz);
@@ -238,13 +277,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < BN / 64; j++) tma_load_3d(sb + j * 8192, &tmB, &full[stage], nt * BN + j * 64, kb * BK, bz);
           }
+          }
           issued_mask |= 1u << stage;
           last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      if (*abort_flag) {
-        // let loads already in flight land before the CTA exits
+      if (*abort_flag && !PAIR) {
+        // let loads already in flight land before the CTA exits (a pair meets at the cluster barrier below, and
+        // only the leader's barriers see the bytes)
         for (int i = 0; i < STAGES; i++)
           if (issued_mask & (1u << i))
             for (uint32_t it = 0; it < WAIT_LIMIT && !mbar_try_wait(&full[i], (last_parity >> i) & 1u); ++it) {}
@@ -252,15 +293,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16(BM, BN, !A_K, !B_K);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_bf16(TILE_M, BN, !A_K, !B_K);
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      for (int u = first_unit; u < p.total_units && ok; u += unit_step) {
         int bz, mt, nt, kb0, kb1;
         unit_coords(u, bz, mt, nt, kb0, kb1);
-        if (below_diagonal(g, mt, nt)) continue;
+        if (below_diagonal(g, mt, nt, TILE_M)) continue;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, g.status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -275,13 +316,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // MN-major: [64 k][64 mn] slabs of 8192 B, 8-k groups 1024 B apart, 16 k = 2048 B.
             const uint64_t ad = A_K ? smem_desc_sw128(sa + k * 32, 16, 1024) : smem_desc_sw128(sa + k * 2048, 8192, 1024);
             const uint64_t bd = B_K ? smem_desc_sw128(sb + k * 32, 16, 1024) : smem_desc_sw128(sb + k * 2048, 8192, 1024);
-            mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR) mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          tc_commit(&empty[stage]);
+          if (PAIR) tc_commit_pair(&empty[stage]); else tc_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&tfull[acc]);
+        if (PAIR) tc_commit_pair(&tfull[acc]); else tc_commit(&tfull[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
@@ -292,13 +334,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int half = (warp - 2) >> 2;    // the two warps of a quadrant take alternate pairs of 32-column chunks
     const int row_in_tile = quad * 32 + lane;
     int acc = 0; uint32_t acc_phase = 0;
-    for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
+    for (int u = first_unit; u < p.total_units; u += unit_step) {
       int bz, mt, nt, kb0, kb1;
       unit_coords(u, bz, mt, nt, kb0, kb1);
-      if (below_diagonal(g, mt, nt)) continue;
+      if (below_diagonal(g, mt, nt, TILE_M)) continue;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, g.status)) break;
       tc_fence_after();
-      const int m = mt * BM + row_in_tile;
+      const int m_tile0 = mt * TILE_M + rank * BM;   // first row of this CTA's 128 x 256 part of the tile
+      const int m = m_tile0 + row_in_tile;
       const int n0 = nt * BN;
       const bool row_ok = m < g.M;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
@@ -345,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
         if (p.splits > 1) {
-          float* dst = p.partial + ((long long)u * 8 + c) * (128 * 32) + row_in_tile * 32;
+          float* dst = p.partial + (((long long)u * G::SLOTS + rank) * 8 + c) * (128 * 32) + row_in_tile * 32;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
           continue;
@@ -397,7 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (tma_out) {
 #pragma unroll
               for (int j = 0; j < 32; j++) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
-              stage_store_bf16(v, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, bz, lane);
+              stage_store_bf16(v, sbuf, &tmC, sub, flush, nc_pair, m_tile0 + quad * 32, bz, lane);
             }
             float cm = -INFINITY;
 #pragma unroll
@@ -416,18 +459,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             rsum = rsum * __expf(rmax - nm) + cs;
             rmax = nm;
           } break;
-          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
-          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
-          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
-          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
-          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, mt * BM + quad * 32, lane); break;
+          case EPI_STORE: bf16_chunk<EPI_STORE>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, m_tile0 + quad * 32, lane); break;
+          case EPI_RESID: bf16_chunk<EPI_RESID>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, m_tile0 + quad * 32, lane); break;
+          case EPI_RELU2: bf16_chunk<EPI_RELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, m_tile0 + quad * 32, lane); break;
+          case EPI_DRELU2: bf16_chunk<EPI_DRELU2>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, m_tile0 + quad * 32, lane); break;
+          case EPI_AXPBY: bf16_chunk<EPI_AXPBY>(g, v, bz, m, nc, full_chunk, auxq, pre_ok, row_ok, sbuf, &tmC, sub, flush, nc_pair, m_tile0 + quad * 32, lane); break;
           default: break;
         }
       }
       if (g.epi == EPI_XENT_STATS && row_ok && p.splits == 1) g.stats[((long long)m * p.tiles_n + nt) * 2 + half] = make_float2(rmax, rsum);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (lane == 0) { if (PAIR) mbar_arrive_even(&tempty[acc]); else mbar_arrive(&tempty[acc]); }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -436,9 +479,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp >= 2 && lane == 0) bulk_wait_all();   // every TMA store of this warp has landed
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {
+    // neither CTA may free the pair's tensor memory, or leave while the peer can still signal its barriers,
+    // before both are done
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc2(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -446,19 +495,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // (tile, 32-column chunk): 128 rows x 32 columns, one float4 column group per thread and row slice.
 __global__ void __launch_bounds__(256) gemm_tc_reduce_kernel(const TcParams p) {
   const GemmArgs& g = p.g;
-  const int tile = blockIdx.x >> 3, c = blockIdx.x & 7;
+  // blockIdx.x enumerates (tile, 128-row half of it, 32-column chunk); a tile has two halves when CTA pairs made it
+  const int slots = p.pair ? 2 : 1;
+  const int c = blockIdx.x & 7, half_id = (blockIdx.x >> 3) % slots, tile = (blockIdx.x >> 3) / slots;
   const int ntile = p.tiles_m * p.tiles_n * g.batch;
   int bz, mt, nt;
   tile_coords(p, tile, bz, mt, nt);
+  const int tile_m = p.pair ? 2 * BM : BM;
 #pragma unroll
   for (int it = 0; it < 4; it++) {
     const int e = it * 256 + threadIdx.x;     // 0..1023 float4 groups of this chunk
     const int row = e >> 3, j4 = (e & 7) * 4;
-    const int m = mt * BM + row, n = nt * BN + c * 32 + j4;
+    const int m = mt * tile_m + half_id * BM + row, n = nt * BN + c * 32 + j4;
     if (m >= g.M || n >= g.N) continue;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float* src = p.partial + ((long long)tile * 8 + c) * (128 * 32) + row * 32 + j4;
-    const long long sstride = (long long)ntile * 8 * (128 * 32);
+    const float* src = p.partial + (((long long)tile * slots + half_id) * 8 + c) * (128 * 32) + row * 32 + j4;
+    const long long sstride = (long long)ntile * slots * 8 * (128 * 32);
     for (int s = 0; s < p.splits; s++) {
       const float4 q = *reinterpret_cast<const float4*>(src + s * sstride);
       acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
@@ -633,25 +685,78 @@ extern "C" int32_t femto_profile_gemm_report(double* h_ms, double* h_flops, int3
   return 0;
 }
 
+// 0 = one CTA per 128 x 256 tile, 1 = CTA pairs per 256 x 256 tile wherever the shape allows (the default).
+static int g_pair_mode = -1;
+extern "C" int32_t femto_gemm_pair_mode(int32_t mode) {
+  const int old = g_pair_mode < 0 ? 1 : g_pair_mode;
+  if (mode == 0 || mode == 1) g_pair_mode = mode;
+  return old;
+}
+
+template <bool PAIR>
+static int launch_tc(const GemmArgs& g, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const TcParams& p,
+                     int grid, cudaStream_t s) {
+  typedef Geo<PAIR> G;
+  static PerDevice attr;
+  const int dev = PerDevice::current();
+  if (dev < 0 || !attr.done[dev]) {
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, true, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, false, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, true, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, false, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    if (dev >= 0) attr.done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = G::SMEM_BYTES; cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = PAIR ? 2 : 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  cudaError_t e;
+  if (g.a_kmajor && g.b_kmajor) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, true, PAIR>, tmA, tmB, tmC, p);
+  else if (g.a_kmajor) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, false, PAIR>, tmA, tmB, tmC, p);
+  else if (g.b_kmajor) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, PAIR>, tmA, tmB, tmC, p);
+  else e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, false, PAIR>, tmA, tmB, tmC, p);
+  if (e != cudaSuccess) return femto_fail((int)e, "gemm_tc launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   if (!gemm_tc_supported(g)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "gemm_tc: shape/alignment not supported");
   TcParams p;
   p.g = g;
-  p.tiles_m = cdiv(g.M, BM);
+  const int nb = g.batch;
+  const int sms = num_sms();
+  // CTA pairs need two row-tiles to share a B tile, and an M/N-contiguous operand to be expressible as 64-wide slabs
+  CUtensorMap tmA, tmB;
+  p.a_slabs = p.b_slabs = 0;
+  bool pair = (g_pair_mode != 0) && g.M >= 2 * BM && sms >= 2;
+  if (pair) {
+    if (g.a_kmajor) pair = make_tmap_3d_bf16(&tmA, g.A, g.K, g.M, nb, g.lda, g.strideA, 64, BM) == 0;
+    else pair = make_tmap_4d_slabs_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, BK, BM / 64) == 0;
+    if (pair) {
+      if (g.b_kmajor) pair = make_tmap_3d_bf16(&tmB, g.B, g.K, g.N, nb, g.ldb, g.strideB, 64, BN / 2) == 0;
+      else pair = make_tmap_4d_slabs_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, BK, BN / 128) == 0;
+    }
+    if (pair) { p.a_slabs = !g.a_kmajor; p.b_slabs = !g.b_kmajor; }
+  }
+  p.pair = pair ? 1 : 0;
+  const int tile_m = pair ? 2 * BM : BM;
+  const int workers = pair ? sms / 2 : sms;      // CTAs, or CTA pairs, that run at once
+  p.tiles_m = cdiv(g.M, tile_m);
   p.tiles_n = cdiv(g.N, BN);
   p.kblocks = cdiv(g.K, BK);
   const int tiles = p.tiles_m * p.tiles_n * g.batch;
-  const int sms = num_sms();
   int splits = 1;
-  if (g.epi == EPI_F32 && tiles < 4 * sms) {
+  if (g.epi == EPI_F32 && tiles < 4 * workers) {
     // pick the split count that minimises (waves x k-blocks per unit), bounded by the workspace
-    const size_t per_unit = (size_t)BM * BN * 4;
-    long long best = (long long)cdiv(tiles, sms) * p.kblocks;
+    const size_t per_unit = (size_t)tile_m * BN * 4;
+    long long best = (long long)cdiv(tiles, workers) * p.kblocks;
     for (int sp = 2; sp <= 32 && sp <= p.kblocks; sp++) {
       if ((size_t)tiles * sp * per_unit > g.ws_bytes) break;
       const int kbp = cdiv(p.kblocks, sp);
       if ((sp - 1) * kbp >= p.kblocks) continue;
-      const long long cost = (long long)cdiv((long long)tiles * sp, sms) * kbp + 4;  // +4: reduce pass
+      const long long cost = (long long)cdiv((long long)tiles * sp, workers) * kbp + 4;  // +4: reduce pass
       if (cost < best) { best = cost; splits = sp; }
     }
   }
@@ -660,15 +765,14 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   p.total_units = tiles * splits;
   p.partial = reinterpret_cast<float*>(g.ws);
 
-  CUtensorMap tmA, tmB;
-  const int nb = g.batch;
-  p.a_slabs = p.b_slabs = 0;
-  if (g.a_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.K, g.M, nb, g.lda, g.strideA, 64, BM));
-  else if (make_tmap_4d_slabs_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, BK, BM / 64) == 0) p.a_slabs = 1;
-  else FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, 64, BK));
-  if (g.b_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.K, g.N, nb, g.ldb, g.strideB, 64, BN));
-  else if (make_tmap_4d_slabs_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, BK, BN / 64) == 0) p.b_slabs = 1;
-  else FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, 64, BK));
+  if (!pair) {
+    if (g.a_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.K, g.M, nb, g.lda, g.strideA, 64, BM));
+    else if (make_tmap_4d_slabs_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, BK, BM / 64) == 0) p.a_slabs = 1;
+    else FEMTO_TRY(make_tmap_3d_bf16(&tmA, g.A, g.M, g.K, nb, g.lda, g.strideA, 64, BK));
+    if (g.b_kmajor) FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.K, g.N, nb, g.ldb, g.strideB, 64, BN));
+    else if (make_tmap_4d_slabs_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, BK, BN / 64) == 0) p.b_slabs = 1;
+    else FEMTO_TRY(make_tmap_3d_bf16(&tmB, g.B, g.N, g.K, nb, g.ldb, g.strideB, 64, BK));
+  }
 
   CUtensorMap tmC = tmA;
   p.tma_store = 0;
@@ -677,25 +781,14 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
     FEMTO_TRY(make_tmap_3d_bf16_sw(&tmC, g.C, g.N, g.M, nb, g.ldc, g.strideC, 64, 32, 3));
     p.tma_store = 1;
   }
-  const int grid = std::min(p.total_units, sms);
-  static PerDevice attr;
-  const int dev = PerDevice::current();
-  if (dev < 0 || !attr.done[dev]) {
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    if (dev >= 0) attr.done[dev] = true;
-  }
+  const int grid = pair ? 2 * std::min(p.total_units, workers) : std::min(p.total_units, sms);
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (g_prof.on) {
     cudaEventCreate(&e0); cudaEventCreate(&e1);
     cudaEventRecord(e0, s);
   }
-  if (g.a_kmajor && g.b_kmajor) gemm_tc_kernel<true, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
-  else if (g.a_kmajor) gemm_tc_kernel<true, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
-  else if (g.b_kmajor) gemm_tc_kernel<false, true><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
-  else gemm_tc_kernel<false, false><<<grid, NTHREADS, SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  if (pair) FEMTO_TRY(launch_tc<true>(g, tmA, tmB, tmC, p, grid, s));
+  else FEMTO_TRY(launch_tc<false>(g, tmA, tmB, tmC, p, grid, s));
   if (g_prof.on) {
     cudaEventRecord(e1, s);
     g_prof.ev.push_back(e0); g_prof.ev.push_back(e1);
@@ -703,7 +796,7 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   }
   KERNEL_CHECK();
   if (splits > 1) {
-    gemm_tc_reduce_kernel<<<tiles * 8, 256, 0, s>>>(p);
+    gemm_tc_reduce_kernel<<<tiles * (pair ? 2 : 1) * 8, 256, 0, s>>>(p);
     KERNEL_CHECK();
   }
   return 0;

@@ -112,7 +112,21 @@ def bench_ns(small, iters):
 def bench_gemm(small, iters):
     L = _lib.lib()
     N = 16384 if small else 65536
-    for nm, M, Nn, K, ak, bk in (("Y = X W      (fc)", N, 5120, 1280, 1, 0), ("Y = X W    (proj)", N, 1280, 5120, 1, 0),
+    # fp32 weight gradient with accumulation, the form the step uses (split-K partials + ordered reduce)
+    for mode in (0, 1):
+        L.femto_gemm_pair_mode(mode)
+        A = torch.randn(N, 1280, device="cuda").bfloat16()
+        B = torch.randn(N, 5120, device="cuda").bfloat16()
+        Cf = torch.zeros(1280, 5120, device="cuda")
+        fn = lambda: _lib.check(L.femto_gemm_bf16(_lib.ptr(A), 0, 1280, _lib.ptr(B), 0, 5120, _lib.ptr(Cf), 5120, 1280, 5120, N,
+                                                  1, 0, 0, 0, 1, 1, None))
+        t = _time(fn, iters)
+        print(f"gemm dW += X^T dY (fc, fp32) 1280x5120x{N} {'CTA pairs' if mode else 'single CTAs'}: {t:7.3f} ms "
+              f"{2.0 * 1280 * 5120 * N / t / 1e9:7.0f} TFLOP/s")
+    for mode in (0, 1):
+      L.femto_gemm_pair_mode(mode)
+      print("tile mode:", "CTA pairs, 256 x 256 tiles (cta_group::2)" if mode else "single CTAs, 128 x 256 tiles")
+      for nm, M, Nn, K, ak, bk in (("Y = X W      (fc)", N, 5120, 1280, 1, 0), ("Y = X W    (proj)", N, 1280, 5120, 1, 0),
                                  ("dX = dY W^T  (fc)", N, 1280, 5120, 1, 1), ("dW = X^T dY  (fc)", 1280, 5120, N, 0, 0)):
         A = torch.randn(M, K, device="cuda").bfloat16()
         B = torch.randn(K, Nn, device="cuda").bfloat16()
@@ -123,6 +137,7 @@ def bench_gemm(small, iters):
                                                   _lib.ptr(Cc), Nn, M, Nn, K, 1, 0, 0, 0, 0, 0, None))
         t = _time(fn, iters)
         print(f"gemm {nm} {M}x{Nn}x{K}: {t:7.3f} ms {2.0 * M * Nn * K / t / 1e9:7.0f} TFLOP/s")
+    L.femto_gemm_pair_mode(1)
 
 
 def bench_stream(small, iters):

@@ -275,6 +275,11 @@ int32_t femto_gemm_bf16(const void* A, int32_t a_kmajor, int64_t lda, const void
                         int64_t ldb, void* C, int64_t ldc, int32_t M, int32_t N, int32_t K, int32_t batch,
                         int64_t strideA, int64_t strideB, int64_t strideC, int32_t out_f32,
                         int32_t accumulate, void* stream);
+/* The tensor-core GEMM computes 256 x 256 output tiles with PAIRS of CTAs (tcgen05.mma.cta_group::2: each CTA holds
+ * 128 rows of A and half of B's columns, a third less operand traffic per flop) wherever M >= 256, and 128 x 256
+ * tiles with single CTAs otherwise.  mode 0 forces single CTAs, 1 restores the default, anything else only
+ * queries; returns the previous mode.  A measurement and debugging aid with no counterpart in the reference. */
+int32_t femto_gemm_pair_mode(int32_t mode);
 /* embedding_gradient!(δ,dy,tokens) (src/kernels.jl:8-14): δ[tokens[n]] += dy[n], deterministic
  * (fixed summation order), tokens 0-based int32 [N], dy [N][D] of `dtype`, δ fp32 [rows][D]. */
 int32_t femto_embedding_gradient(int32_t dtype, float* delta_table, const void* dy, const int32_t* tokens0,

@@ -544,3 +544,46 @@ def test_feeder_delivers_batches_in_order_and_a_step_runs_from_it():
     a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
     assert L.femto_feeder_next(fd.f, None, C.byref(a), C.byref(b), C.byref(c)) == -4                       # empty
     fd.close()
+
+
+@pytest.mark.parametrize("ak", [True, False])
+@pytest.mark.parametrize("bk", [True, False])
+def test_gemm_cta_pairs_equal_single_ctas(ak, bk):
+    """256 x 256 tiles computed by CTA pairs (tcgen05.mma.cta_group::2) against 128 x 256 tiles by single CTAs: the
+    same products summed in the same order, so bf16 results are bit-identical; ragged M (the last pair has an empty
+    half), ragged N and K, a batch, and the fp32 split-K form."""
+    L = _lib.lib()
+    M, N, K, batch = 648, 520, 1288, 2
+    g = torch.Generator(device="cuda").manual_seed(17)
+    A = torch.randn(batch, M, K, generator=g, device="cuda").bfloat16()
+    B = torch.randn(batch, K, N, generator=g, device="cuda").bfloat16()
+    As = A.contiguous() if ak else A.transpose(1, 2).contiguous()
+    Bs = B.transpose(1, 2).contiguous() if bk else B.contiguous()
+    outs = []
+    for mode in (0, 1):
+        L.femto_gemm_pair_mode(mode)
+        Cc = torch.zeros(batch, M, N, device="cuda", dtype=torch.bfloat16)
+        _lib.check(L.femto_gemm_bf16(_lib.ptr(As), int(ak), K if ak else M, _lib.ptr(Bs), int(bk), K if bk else N,
+                                     _lib.ptr(Cc), N, M, N, K, batch, M * K, K * N, M * N, 0, 0, None))
+        torch.cuda.synchronize()
+        outs.append(Cc.cpu())
+    L.femto_gemm_pair_mode(1)
+    ref = torch.bmm(A.double().cpu(), B.double().cpu())
+    assert (outs[1].double() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
+    assert torch.equal(outs[0], outs[1])
+    # fp32 accumulate with split-K (one matrix, long K)
+    Kl = 8192
+    A2 = torch.randn(Kl, 512, generator=g, device="cuda").bfloat16()
+    B2 = torch.randn(Kl, 768, generator=g, device="cuda").bfloat16()
+    res = []
+    for mode in (0, 1):
+        L.femto_gemm_pair_mode(mode)
+        Cf = torch.ones(512, 768, device="cuda")
+        _lib.check(L.femto_gemm_bf16(_lib.ptr(A2), 0, 512, _lib.ptr(B2), 0, 768, _lib.ptr(Cf), 768, 512, 768, Kl, 1, 0, 0, 0, 1, 1,
+                                     None))
+        torch.cuda.synchronize()
+        res.append(Cf.cpu())
+    L.femto_gemm_pair_mode(1)
+    ref2 = 1.0 + A2.double().cpu().T @ B2.double().cpu()
+    assert (res[1].double() - ref2).abs().max() <= 1e-5 * ref2.abs().max()
+    assert (res[0] - res[1]).abs().max() <= 1e-5 * ref2.abs().max()   # split counts may differ between the modes
