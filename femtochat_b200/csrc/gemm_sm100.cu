@@ -730,6 +730,10 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   // CTA pairs need two row-tiles to share a B tile, and an M/N-contiguous operand to be expressible as 64-wide slabs
   CUtensorMap tmA, tmB;
   p.a_slabs = p.b_slabs = 0;
+  if (g_pair_mode < 0) {   // first call: FEMTO_GEMM_PAIR=0 in the environment selects single-CTA tiles (measurement aid)
+    const char* e = getenv("FEMTO_GEMM_PAIR");
+    g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+  }
   bool pair = (g_pair_mode != 0) && g.M >= 2 * BM && sms >= 2;
   if (pair) {
     if (g.a_kmajor) pair = make_tmap_3d_bf16(&tmA, g.A, g.K, g.M, nb, g.lda, g.strideA, 64, BM) == 0;

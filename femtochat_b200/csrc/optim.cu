@@ -10,15 +10,24 @@
 #include "model.cuh"
 #include "streaming.cuh"
 
-struct AdamGroup { long long off, n, moff; float alpha, b1, b2, eps, lam; int t; bool shard = false; };
+struct AdamGroup {
+  long long off, n, moff; float alpha, b1, b2, eps, lam; int t; bool shard = false;
+  void* shadow = nullptr;   // compute-type copy of this range kept by the model (tables only), same element order
+};
 struct MuonGroup {
   std::vector<long long> offs;
   std::vector<int> layers;      // block of each matrix (ascending)
+  std::vector<void*> shadow;    // host copies of d_shadow / d_shadow_ld
+  std::vector<int> shadow_ld;
   int k0 = 0, k1 = 0;           // the matrices this rank updates (all of them unless sharded)
   int out = 0, in = 0;          // Julia shape (m, n) = (out, in); stored row-major [in][out]
   long long moff = 0, voff = 0; // into muon_m / muon_v
   float alpha, mu, b2, lam;
   long long* d_offs = nullptr;
+  // where the model keeps the compute-type copy of each matrix: base pointer (of the handle's compute type) and row
+  // pitch in elements (Q, K and V of a block live side by side in one packed matrix)
+  void** d_shadow = nullptr;
+  int* d_shadow_ld = nullptr;
 };
 
 struct femto_optimizer {
@@ -40,10 +49,11 @@ struct femto_optimizer {
 
 namespace {
 
+template <typename S>
 __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const float* __restrict__ delta,
                                                float* __restrict__ m, float* __restrict__ v, long long n, float alpha,
                                                float b1, float b2, float eps, float lam, float c1, float c2,
-                                               float inv_nt) {
+                                               float inv_nt, S* __restrict__ shadow) {
   // four elements per thread, a block apart: the sixteen loads are issued before the arithmetic, which is what
   // keeps enough bytes in flight (group offsets are arbitrary, so no wider-than-4-byte access is assumed)
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -64,8 +74,31 @@ __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const 
       m[i] = mm;
       v[i] = vv;
       const float t = th[u] * (1.f - alpha * lam);
-      theta[i] = t - alpha * (mm / c1) / (sqrtf(vv / c2) + eps);
+      const float tn = t - alpha * (mm / c1) / (sqrtf(vv / c2) + eps);
+      theta[i] = tn;
+      // the model's compute-type copy of the weights is refreshed in the same pass (2 more bytes per parameter
+      // instead of a separate read-and-cast pass over Theta)
+      if (shadow) shadow[i] = from_f<S>(tn);
     }
+  }
+}
+
+// Every small AdamW group (the per-block scalars, the smear gate, ...) in ONE launch: block b takes group b.
+struct SmallAdam { long long off, moff; int n; float alpha, b1, b2, eps, lam, c1, c2; };
+constexpr int SMALL_BATCH = 64;                 // groups per launch: the batch travels in the kernel's parameter space
+struct SmallBatch { SmallAdam g[SMALL_BATCH]; };
+__global__ void __launch_bounds__(128) k_adamw_small(float* __restrict__ theta, const float* __restrict__ delta,
+                                                     float* __restrict__ m, float* __restrict__ v,
+                                                     const __grid_constant__ SmallBatch batch, float inv_nt) {
+  const SmallAdam& g = batch.g[blockIdx.x];
+  for (int i = threadIdx.x; i < g.n; i += 128) {
+    const float gg = delta[g.off + i] * inv_nt;
+    const float mm = g.b1 * m[g.moff + i] + (1.f - g.b1) * gg;
+    const float vv = g.b2 * v[g.moff + i] + (1.f - g.b2) * gg * gg;
+    m[g.moff + i] = mm;
+    v[g.moff + i] = vv;
+    const float t = theta[g.off + i] * (1.f - g.alpha * g.lam);
+    theta[g.off + i] = t - g.alpha * (mm / g.c1) / (sqrtf(vv / g.c2) + g.eps);
   }
 }
 
@@ -183,17 +216,23 @@ __global__ void __launch_bounds__(256) k_normuon_factors(const float* __restrict
 }
 
 // theta -= eta*X + eta*lam*theta*[X*theta >= 0]  (src/optim.jl:244-245; ext/FemtoChatCUDAExt.jl:108-119)
-template <typename T>
+template <typename T, typename S>
 __global__ void __launch_bounds__(256) k_muon_update(float* __restrict__ theta, const long long* __restrict__ offs,
                                                      const T* __restrict__ X, const float* __restrict__ fac,
-                                                     long long per, int out, int by_col, int dim, float eta, float lam) {
+                                                     long long per, int out, int by_col, int dim, float eta, float lam,
+                                                     void* const* __restrict__ shadow, const int* __restrict__ shadow_ld) {
   const int k = blockIdx.y;
   float* th = theta + offs[k];
+  S* sh = shadow ? reinterpret_cast<S*>(shadow[k]) : nullptr;
+  const int sld = shadow ? shadow_ld[k] : 0;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
-    int j = by_col ? (int)(i % out) : (int)(i / out);
+    const int col = (int)(i % out), row = (int)(i / out);
+    int j = by_col ? col : row;
     float x = to_f<T>(X[k * per + i]) * fac[(long long)k * dim + j];
     float t = th[i];
-    th[i] = t - (eta * x + eta * lam * t * ((x * t) >= 0.f ? 1.f : 0.f));
+    const float tn = t - (eta * x + eta * lam * t * ((x * t) >= 0.f ? 1.f : 0.f));
+    th[i] = tn;
+    if (sh) sh[(long long)row * sld + col] = from_f<S>(tn);   // the model's compute-type copy, refreshed in the same pass
   }
 }
 
@@ -201,12 +240,19 @@ inline int egrid(long long n) { return (int)std::min<long long>(cdiv(n, 256), 14
 
 }  // namespace
 
-int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
-                 float eps, float lam, int t, float n_tokens, cudaStream_t s) {
+// shadow (may be null): compute-type copy of the range, of type bf16 when shadow_bf16 else float
+static int adamw_launch_shadow(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1,
+                               float b2, float eps, float lam, int t, float n_tokens, void* shadow, bool shadow_bf16,
+                               cudaStream_t s) {
   const float c1 = 1.f - powf(b1, (float)t), c2 = 1.f - powf(b2, (float)t);
-  k_adamw<<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens);
+  if (shadow_bf16) k_adamw<bf16><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (bf16*)shadow);
+  else k_adamw<float><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (float*)shadow);
   KERNEL_CHECK();
   return 0;
+}
+int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
+                 float eps, float lam, int t, float n_tokens, cudaStream_t s) {
+  return adamw_launch_shadow(theta, delta, m, v, n, alpha, b1, b2, eps, lam, t, n_tokens, nullptr, false, s);
 }
 
 // C[b][i][j] = C[b][j][i] for i > j on a stack of r x r matrices: completes a symmetric product of which only the
@@ -356,7 +402,10 @@ template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& 
   k_normuon_factors<<<k, 256, 0, s>>>(o->vec, dim, dsize, std::min(in, out), g.b2, v, o->fac);
   KERNEL_CHECK();
   const float eta = alpha * sqrtf(std::max(1.f, (float)out / (float)in));
-  k_muon_update<T><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam);
+  void* const* sh = g.d_shadow ? g.d_shadow + g.k0 : nullptr;
+  const int* shld = g.d_shadow_ld ? g.d_shadow_ld + g.k0 : nullptr;
+  if (h->bf) k_muon_update<T, bf16><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam, sh, shld);
+  else k_muon_update<T, float><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam, sh, shld);
   KERNEL_CHECK();
   return 0;
 }
@@ -460,17 +509,18 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
   o->h = h; o->cfg = *cfg; o->adam_m = adam_m; o->adam_v = adam_v; o->muon_m = muon_m; o->muon_v = muon_v;
   const float scale = sqrtf(768.f / (float)h->d);
   long long moff = 0;
-  auto add = [&](long long off, long long n, float alpha, float b1, float b2, float lam) {
+  auto add = [&](long long off, long long n, float alpha, float b1, float b2, float lam, void* shadow = nullptr) {
     AdamGroup g{off, n, moff, alpha, b1, b2, 1e-10f, lam, 0};
+    g.shadow = shadow;
     moff += n;
     o->adam.push_back(g);
   };
   // group order of src/optim.jl:333-403
-  add(h->off_lm, (long long)h->Vp * h->d, cfg->unembedding_lr * scale, 0.8f, 0.96f, 0.01f);
-  add(h->off_wte, (long long)h->Vp * h->d, cfg->embedding_lr * scale, 0.8f, 0.995f, 0.001f);
+  add(h->off_lm, (long long)h->Vp * h->d, cfg->unembedding_lr * scale, 0.8f, 0.96f, 0.01f, h->sh_lm);
+  add(h->off_wte, (long long)h->Vp * h->d, cfg->embedding_lr * scale, 0.8f, 0.995f, 0.001f, h->sh_wte);
   for (int i = 0; i < h->L; i++) {
     const LayerP& p = h->lp[i];
-    if (p.ve) add(p.ve_table, (long long)h->Vp * h->kv, 0.5f * cfg->embedding_lr * scale, 0.8f, 0.995f, 0.01f);
+    if (p.ve) add(p.ve_table, (long long)h->Vp * h->kv, 0.5f * cfg->embedding_lr * scale, 0.8f, 0.995f, 0.01f, h->lb[i].sh_ve);
     add(p.lam_b, 1, 0.01f * cfg->scalar_lr, 0.8f, 0.95f, 0.05f);
     add(p.lam_x0, 1, cfg->scalar_lr, 0.96f, 0.95f, 0.f);
   }
@@ -478,13 +528,19 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
   add(h->off_lam_s, 1, cfg->smear_lr, 0.8f, 0.95f, 0.f);
   add(h->off_lam_y, 1, cfg->smear_lr, 0.8f, 0.95f, 0.f);
   // Muon groups by shape, in order of first appearance (src/optim.jl:405-425)
-  struct Spec { long long off; int out, in, layer; };
+  struct Spec { long long off; int out, in, layer; void* shadow; int shadow_ld; };
   std::vector<Spec> specs;
+  const size_t es_model = h->bf ? 2 : 4;
   for (int i = 0; i < h->L; i++) {
     const LayerP& p = h->lp[i];
-    specs.push_back({p.wq, h->d, h->d, i}); specs.push_back({p.wk, h->kv, h->d, i}); specs.push_back({p.wv, h->kv, h->d, i});
-    specs.push_back({p.wo, h->d, h->d, i}); specs.push_back({p.fc, 4 * h->d, h->d, i}); specs.push_back({p.proj, h->d, 4 * h->d, i});
-    if (p.ve) specs.push_back({p.ve_gate, h->Hkv, 12, i});
+    const LayerBuf& l = h->lb[i];
+    char* qkv = reinterpret_cast<char*>(l.sh_wqkv);   // [d][d + 2 kv]: Q | K | V side by side
+    specs.push_back({p.wq, h->d, h->d, i, qkv, h->dq});
+    specs.push_back({p.wk, h->kv, h->d, i, qkv + es_model * h->d, h->dq});
+    specs.push_back({p.wv, h->kv, h->d, i, qkv + es_model * (h->d + h->kv), h->dq});
+    specs.push_back({p.wo, h->d, h->d, i, l.sh_wo, h->d}); specs.push_back({p.fc, 4 * h->d, h->d, i, l.sh_fc, 4 * h->d});
+    specs.push_back({p.proj, h->d, 4 * h->d, i, l.sh_proj, h->d});
+    if (p.ve) specs.push_back({p.ve_gate, h->Hkv, 12, i, nullptr, 0});   // the gate is read from Theta in fp32
   }
   long long mo = 0, vo = 0;
   size_t max_stack = 0, max_rr = 0, max_vec = 0;
@@ -498,6 +554,8 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
     }
     g->offs.push_back(sp.off);
     g->layers.push_back(sp.layer);
+    g->shadow.push_back(sp.shadow);
+    g->shadow_ld.push_back(sp.shadow_ld);
   }
   for (auto& g : o->muon) {
     const size_t k = g.offs.size();
@@ -511,6 +569,10 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
     max_vec = std::max(max_vec, k * (size_t)std::max(g.in, g.out));
     CUDA_TRY(cudaMalloc(&g.d_offs, sizeof(long long) * k));
     CUDA_TRY(cudaMemcpy(g.d_offs, g.offs.data(), sizeof(long long) * k, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMalloc(&g.d_shadow, sizeof(void*) * k));
+    CUDA_TRY(cudaMemcpy(g.d_shadow, g.shadow.data(), sizeof(void*) * k, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMalloc(&g.d_shadow_ld, sizeof(int) * k));
+    CUDA_TRY(cudaMemcpy(g.d_shadow_ld, g.shadow_ld.data(), sizeof(int) * k, cudaMemcpyHostToDevice));
   }
   const size_t es = cfg->compute_dtype == FEMTO_BF16 ? 2 : 4;
   auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
@@ -530,7 +592,7 @@ int optimizer_create(femto_handle* h, const femto_optimizer_config* cfg, float* 
 
 int optimizer_destroy(femto_optimizer* o) {
   if (!o) return 0;
-  for (auto& g : o->muon) cudaFree(g.d_offs);
+  for (auto& g : o->muon) { cudaFree(g.d_offs); cudaFree(g.d_shadow); cudaFree(g.d_shadow_ld); }
   cudaFree(o->ws);
   delete o;
   return 0;
@@ -541,13 +603,34 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
   if (!o || !theta || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
   if (!(n_tokens > 0.f)) return femto_fail(FEMTO_ERR_ARG, "n_tokens must be positive");
   const bool sharded = o->shard_world > 1;
+  femto_handle* h = o->h;
+  const size_t es_model = h->bf ? 2 : 4;
+  SmallBatch batch;
+  int nsmall = 0;
+  auto flush_small = [&]() -> int {
+    if (nsmall == 0) return 0;
+    k_adamw_small<<<nsmall, 128, 0, s>>>(theta, delta, o->adam_m, o->adam_v, batch, 1.f / n_tokens);
+    KERNEL_CHECK();
+    nsmall = 0;
+    return 0;
+  };
   for (auto& g : o->adam) {  // src/optim.jl:431-433
     g.t += 1;
+    if (!g.shard && !g.shadow && g.n <= 4096) {
+      // the scalars and gates: all of them in one launch (the order of the groups does not matter, they are disjoint)
+      SmallAdam& sg = batch.g[nsmall++];
+      sg.off = g.off; sg.moff = g.moff; sg.n = (int)g.n; sg.alpha = eta * g.alpha; sg.b1 = g.b1; sg.b2 = g.b2; sg.eps = g.eps;
+      sg.lam = g.lam; sg.c1 = 1.f - powf(g.b1, (float)g.t); sg.c2 = 1.f - powf(g.b2, (float)g.t);
+      if (nsmall == SMALL_BATCH) FEMTO_TRY(flush_small());
+      continue;
+    }
     // a sharded table: this rank updates slice shard_rank of shard_world equal slices
     const long long n = g.shard ? g.n / o->shard_world : g.n, o0 = g.shard ? n * o->shard_rank : 0;
-    FEMTO_TRY(adamw_launch(theta + g.off + o0, delta + g.off + o0, o->adam_m + g.moff + o0, o->adam_v + g.moff + o0, n,
-                           eta * g.alpha, g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, s));
+    void* shadow = g.shadow ? reinterpret_cast<char*>(g.shadow) + es_model * (size_t)o0 : nullptr;
+    FEMTO_TRY(adamw_launch_shadow(theta + g.off + o0, delta + g.off + o0, o->adam_m + g.moff + o0, o->adam_v + g.moff + o0, n,
+                                  eta * g.alpha, g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, shadow, h->bf, s));
   }
+  FEMTO_TRY(flush_small());
   for (auto& g : o->muon) {  // src/optim.jl:434-438
     const float m_ = has_mu ? mu : g.mu, l_ = has_lambda ? lambda : g.lam;
     if (o->cfg.compute_dtype == FEMTO_BF16)
@@ -561,8 +644,12 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
     for (size_t i = 0; i + 1 < o->foreign.size(); i += 2)
       CUDA_TRY(cudaMemsetAsync(theta + o->foreign[i], 0, sizeof(float) * (size_t)o->foreign[i + 1], s));
     FEMTO_TRY(dp_allreduce_sum_f32(o->h->dp, theta, o->h->nparams, s));   // x + 0 + ... + 0 is exact
+    return model_refresh(o->h, theta, s);   // the ranges other ranks updated arrive as fp32 only
   }
-  return model_refresh(o->h, theta, s);
+  if (sharded) return model_refresh(o->h, theta, s);   // no communicator: the caller merges Theta and refreshes again
+  // every weight the model reads in its compute type was rewritten by the update kernels above
+  o->h->weights_valid = true;
+  return 0;
 }
 
 int optimizer_get_t(femto_optimizer* o, int* t, int cap) {

@@ -405,3 +405,27 @@ def test_generate_with_cache_equals_generate_by_recompute():
     e = fb.generate(model, list(range(1, 61)), max_new_tokens=8, temperature=0.0)
     f = fb.generate(model, list(range(1, 61)), max_new_tokens=8, temperature=0.0, use_cache=False)
     assert e == f and len(e) == 68
+
+
+@pytest.mark.parametrize("cfgkw,ctype", [(MID, "float32"), (TC, "bfloat16")])
+def test_update_kernels_refresh_the_compute_type_weights(cfgkw, ctype):
+    """The AdamW and Muon update kernels write the model's compute-type copy of every weight in the same pass as
+    Theta.  That copy must be exactly what a fresh cast of Theta gives: the loss right after an update equals, bit
+    for bit, the loss after an explicit femto_refresh_weights."""
+    cfg = fb.GPTConfig(**cfgkw)
+    lay = fb.parameter_layout(cfg)
+    th = torch.zeros(lay.nparams)
+    fo.initialize(th, fo.GPTConfig(**cfgkw), fo.parameter_layout(fo.GPTConfig(**cfgkw)), 3, all_nonzero=True)
+    tok, tgt, pos = inputs(cfgkw, 2, 5)
+    params = fb.Params(th.cuda())
+    st = fb.gradient_state(params, cfg, lay, tok, tgt, pos, compute_type=ctype)
+    opt = fb.MuonAdamW(params, lay, st, compute_type=ctype, weight_decay=0.1)
+    for step in range(2):
+        fb.loss_and_gradient_(params, st, lay, tok, tgt, pos)
+        opt.step(eta=1.0, Nt=float(tok.numel()))
+        after_update = fb.loss_and_gradient_(params, st, lay, tok, tgt, pos)
+        delta_a = params.delta.clone()
+        st.refresh_weights(params.theta)
+        after_refresh = fb.loss_and_gradient_(params, st, lay, tok, tgt, pos)
+        assert after_update == after_refresh, step
+        assert torch.equal(delta_a, params.delta)
