@@ -225,6 +225,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched no global memory: it may overlap the tail of the previous kernel in the stream.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   auto unit_coords = [&](int u, int& bz, int& mt, int& nt, int& kb0, int& kb1) {
     // split-major: all tiles of one k-range run together, so the 148 CTAs stream the same rows of
@@ -708,10 +711,14 @@ static int launch_tc(const GemmArgs& g, const CUtensorMap& tmA, const CUtensorMa
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = G::SMEM_BYTES; cfg.stream = s;
-  cudaLaunchAttribute at[1];
+  static int pdl = -1;   // FEMTO_PDL=0 in the environment launches fully serialised (measurement aid)
+  if (pdl < 0) { const char* e = getenv("FEMTO_PDL"); pdl = (e && e[0] == '0') ? 0 : 1; }
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = PAIR ? 2 : 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-  cfg.attrs = at; cfg.numAttrs = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = pdl ? 2 : 1;
   cudaError_t e;
   if (g.a_kmajor && g.b_kmajor) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, true, PAIR>, tmA, tmB, tmC, p);
   else if (g.a_kmajor) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, false, PAIR>, tmA, tmB, tmC, p);

@@ -138,6 +138,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---- programmatic dependent launch ------------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the
+// stream still runs: everything before grid_dependency_wait() (barrier set-up, tensor-memory allocation, descriptor
+// prefetch) overlaps the predecessor's tail; nothing the predecessor wrote may be touched before it.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel of the stream be scheduled as this grid's CTAs retire (it still waits for this grid's
+// completion inside its own grid_dependency_wait()).
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- CTA pairs (cta_group::2): two CTAs of a cluster run one 256-row MMA --------------------------------------
 // A shared::cluster address with bit 24 cleared names the same offset in the even CTA of the pair.
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;
