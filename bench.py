@@ -210,6 +210,8 @@ def run_ours(args):
     opt = fb.MuonAdamW(params, lay, st, compute_type="bfloat16", weight_decay=0.01)
     if world > 1 and args.shard_optimizer:
         opt.shard(rank, world)   # each rank updates its share of Theta, then the shares are exchanged
+        if args.exchange_weights:
+            opt.set_exchange(1)  # ... as compute-type weights only; the fp32 Theta is completed on demand (below)
     total = args.steps + args.warmup
     pk = fb.PackedBatches(cfg.vocab_size, T, B, max_document_tokens=cfg.max_document_tokens, rank=rank)
     host = []
@@ -299,6 +301,8 @@ def run_ours(args):
     # Theta must still be the same on every rank (the sharded update exchanges each rank's share)
     replicated = True
     if world > 1:
+        if args.shard_optimizer and args.exchange_weights:
+            opt.gather_theta()
         cs = torch.stack([params.theta.sum(dtype=torch.float64), params.theta.abs().sum(dtype=torch.float64)])
         hi, lo = cs.clone(), cs.clone()
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
@@ -319,6 +323,8 @@ def run_ours(args):
                                  f"document mask on",
                         parallelism=f"dp{world}",
                         optimizer=("owner-sharded" if world > 1 and args.shard_optimizer else "replicated"),
+                        exchange=("compute-type weights per step, fp32 Theta on demand"
+                                  if world > 1 and args.shard_optimizer and args.exchange_weights else "fp32 Theta per step"),
                         theta_replicated=replicated, l2="inputs and activations per step far exceed the 126 MB L2",
                         mfu_nominal_2p25e15=value * flops_tok / (world * 2.25e15), flops_per_token=flops_tok,
                         loss_per_token=final_loss, device_status=status),
@@ -393,6 +399,9 @@ def main():
     ap.add_argument("--replicated-optimizer", dest="shard_optimizer", action="store_false",
                     help="N > 1: every rank repeats the whole Muon/AdamW update instead of updating its share of "
                          "Theta and exchanging the shares (the default)")
+    ap.add_argument("--exchange-theta", dest="exchange_weights", action="store_false",
+                    help="N > 1, sharded update: exchange the fp32 Theta after every update instead of only the "
+                         "compute-type weights (the default; Theta is then completed once, before it is read)")
     ap.add_argument("--phases", action="store_true",
                     help="N > 1: after the bench line, time reverse pass / gradient sum / update separately for the "
                          "owner-sharded and the replicated update (stderr)")

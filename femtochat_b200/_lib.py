@@ -81,12 +81,17 @@ SIGNATURES = {
     "femto_feeder_next": (I32, [P, P, C.POINTER(P), C.POINTER(P), C.POINTER(P)]),
     "femto_feeder_release": (I32, [P, P]),
     "femto_grad_sync": (I32, [P, P, P, P, P]),
+    "femto_comm_check": (I32, [P]),
+    "femto_comm_abort": (I32, [P]),
+    "femto_selftest_bounded_wait": (I32, [I32, C.POINTER(I32), C.POINTER(I32)]),
     "femto_set_overlap": (I32, [P, I32]),
     "femto_optimizer_state_sizes": (I32, [P, C.POINTER(I64)]),
     "femto_optimizer_create": (I32, [P, C.POINTER(OptimizerConfig), P, P, P, P, C.POINTER(P)]),
     "femto_optimizer_destroy": (I32, [P]),
     "femto_optimizer_step": (I32, [P, P, P, F, I32, F, I32, F, F, P]),
     "femto_optimizer_set_shard": (I32, [P, I32, I32]),
+    "femto_optimizer_set_exchange": (I32, [P, I32]),
+    "femto_optimizer_gather_theta": (I32, [P, P, P]),
     "femto_optimizer_grad_sync": (I32, [P, P, P, P, P]),
     "femto_optimizer_state_ranges": (I32, [P, I32, C.POINTER(I64), I32]),
     "femto_optimizer_gather_state": (I32, [P, P]),

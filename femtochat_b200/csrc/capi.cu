@@ -21,6 +21,8 @@ int optimizer_grad_sync(femto_optimizer* o, float* delta, cudaStream_t s);
 femto_handle* optimizer_handle(femto_optimizer* o);
 int optimizer_state_ranges(femto_optimizer* o, int which, long long* out, int cap);
 int optimizer_gather_state(femto_optimizer* o, cudaStream_t s);
+int optimizer_set_exchange(femto_optimizer* o, int mode);
+int optimizer_gather_theta(femto_optimizer* o, float* theta, cudaStream_t s);
 int adamw_launch(float* theta, const float* delta, float* m, float* v, long long n, float alpha, float b1, float b2,
                  float eps, float lam, int t, float n_tokens, cudaStream_t s);
 template <typename T>
@@ -250,6 +252,15 @@ int32_t femto_grad_sync(femto_handle* h, float* delta, float* loss_inout, int32_
   return 0;
 }
 
+int32_t femto_comm_check(femto_handle* h) {
+  if (!h) return femto_fail(FEMTO_ERR_ARG, "NULL handle");
+  return dp_async_error(h->dp);
+}
+int32_t femto_comm_abort(femto_handle* h) {
+  if (!h) return femto_fail(FEMTO_ERR_ARG, "NULL handle");
+  return dp_abort(h->dp);
+}
+
 int32_t femto_set_overlap(femto_handle* h, int32_t enable) {
   if (!h) return femto_fail(FEMTO_ERR_ARG, "NULL handle");
   h->overlap_sync = enable != 0;
@@ -285,6 +296,10 @@ int32_t femto_optimizer_state_ranges(femto_optimizer* o, int32_t which, int64_t*
 int32_t femto_optimizer_gather_state(femto_optimizer* o, void* stream) {
   if (!o) return femto_fail(FEMTO_ERR_ARG, "NULL optimizer");
   return optimizer_gather_state(o, (cudaStream_t)stream);
+}
+int32_t femto_optimizer_set_exchange(femto_optimizer* o, int32_t mode) { return optimizer_set_exchange(o, mode); }
+int32_t femto_optimizer_gather_theta(femto_optimizer* o, float* theta, void* stream) {
+  return optimizer_gather_theta(o, theta, (cudaStream_t)stream);
 }
 int32_t femto_optimizer_grad_sync(femto_optimizer* o, float* delta, float* loss_inout, int32_t* n_valid_inout, void* stream) {
   if (!o || !delta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");

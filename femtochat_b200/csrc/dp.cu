@@ -18,6 +18,8 @@ typedef int (*fn_reduce_scatter)(const void*, void*, size_t, int, int, nccl_comm
 typedef int (*fn_reduce)(const void*, void*, size_t, int, int, int, nccl_comm, cudaStream_t);
 typedef int (*fn_group)(void);
 typedef const char* (*fn_errstr)(int);
+typedef int (*fn_async_err)(nccl_comm, int*);
+typedef int (*fn_abort)(nccl_comm);
 
 struct Nccl {
   void* lib = nullptr;
@@ -25,6 +27,7 @@ struct Nccl {
   fn_allreduce allreduce = nullptr; fn_reduce_scatter reduce_scatter = nullptr;
   fn_reduce reduce = nullptr; fn_group group_start = nullptr, group_end = nullptr;
   fn_errstr errstr = nullptr;
+  fn_async_err async_err = nullptr; fn_abort abort = nullptr;
 };
 Nccl g_nccl;
 
@@ -45,13 +48,15 @@ int nccl_load() {
   g_nccl.group_start = (fn_group)dlsym(g_nccl.lib, "ncclGroupStart");
   g_nccl.group_end = (fn_group)dlsym(g_nccl.lib, "ncclGroupEnd");
   g_nccl.errstr = (fn_errstr)dlsym(g_nccl.lib, "ncclGetErrorString");
+  g_nccl.async_err = (fn_async_err)dlsym(g_nccl.lib, "ncclCommGetAsyncError");
+  g_nccl.abort = (fn_abort)dlsym(g_nccl.lib, "ncclCommAbort");
   if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.reduce_scatter ||
       !g_nccl.reduce || !g_nccl.group_start || !g_nccl.group_end)
     return femto_fail(FEMTO_ERR_UNSUPPORTED, "libnccl is missing required symbols");
   return 0;
 }
 // ncclDataType_t / ncclRedOp_t values of the public nccl.h
-constexpr int NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_SUM = 0;
+constexpr int NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_BFLOAT16 = 9, NCCL_SUM = 0;
 int nccl_check(int r, const char* what) {
   if (r == 0) return 0;
   return femto_fail(200000 + r, "%s failed: %s", what, g_nccl.errstr ? g_nccl.errstr(r) : "nccl error");
@@ -96,6 +101,7 @@ int dp_create(DpState** out, int rank, int world, const void* id128) {
 // everything already enqueued on `compute`.
 int dp_bucket_allreduce(DpState* d, float* buf, long long n, cudaStream_t compute) {
   if (!d || n <= 0) return 0;
+  if (!d->comm) return femto_fail(FEMTO_ERR_STATE, "the communicator was aborted");
   CUDA_TRY(cudaEventRecord(d->ready, compute));
   CUDA_TRY(cudaStreamWaitEvent(d->cs, d->ready, 0));
   FEMTO_TRY(nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_FLOAT32, NCCL_SUM, d->comm, d->cs), "ncclAllReduce"));
@@ -123,10 +129,17 @@ void dp_destroy(DpState* d) {
 
 int dp_allreduce_sum_f32(DpState* d, float* buf, long long n, cudaStream_t s) {
   if (!d) return 0;
+  if (!d->comm) return femto_fail(FEMTO_ERR_STATE, "the communicator was aborted");
   return nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_FLOAT32, NCCL_SUM, d->comm, s), "ncclAllReduce");
+}
+int dp_allreduce_sum_bf16(DpState* d, void* buf, long long n, cudaStream_t s) {
+  if (!d) return 0;
+  if (!d->comm) return femto_fail(FEMTO_ERR_STATE, "the communicator was aborted");
+  return nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_BFLOAT16, NCCL_SUM, d->comm, s), "ncclAllReduce");
 }
 int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s) {
   if (!d) return 0;
+  if (!d->comm) return femto_fail(FEMTO_ERR_STATE, "the communicator was aborted");
   return nccl_check(g_nccl.allreduce(buf, buf, (size_t)n, NCCL_INT32, NCCL_SUM, d->comm, s), "ncclAllReduce");
 }
 // Gradient sum for the owner-sharded update: every range of delta is summed over ranks, but a range that one rank alone
@@ -136,6 +149,7 @@ int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s) {
 int dp_reduce_ranges(DpState* d, float* delta, const long long* gathers, int n_gathers, const long long* bcasts,
                      int n_bcasts, const long long* gaps, int n_gaps, cudaStream_t s) {
   if (!d) return 0;
+  if (!d->comm) return femto_fail(FEMTO_ERR_STATE, "the communicator was aborted");
   FEMTO_TRY(nccl_check(g_nccl.group_start(), "ncclGroupStart"));
   int r = 0;
   for (int i = 0; i < n_gathers && !r; i++) {
@@ -155,5 +169,25 @@ int dp_reduce_ranges(DpState* d, float* delta, const long long* gathers, int n_g
   FEMTO_TRY(nccl_check(r, "ncclReduceScatter / ncclReduce / ncclAllReduce"));
   return nccl_check(e, "ncclGroupEnd");
 }
+// Asynchronous errors of the communicator (a peer that died, a network fault): collectives are only checked when they
+// are enqueued, so a host loop polls this between steps.  0 = healthy or still in progress (ncclInProgress = 7).
+int dp_async_error(DpState* d) {
+  if (!d || !d->comm || !g_nccl.async_err) return 0;
+  int state = 0;
+  const int r = g_nccl.async_err(d->comm, &state);
+  if (r != 0) return nccl_check(r, "ncclCommGetAsyncError");
+  if (state == 0 || state == 7) return 0;
+  return nccl_check(state, "NCCL communicator (asynchronous error)");
+}
+// Tear the communicator down without waiting for outstanding collectives (after dp_async_error reported a fault or a
+// host-side timeout expired): afterwards the handle has no communicator and data-parallel calls fail cleanly.
+int dp_abort(DpState* d) {
+  if (!d || !d->comm) return 0;
+  int r = 0;
+  if (g_nccl.abort) r = g_nccl.abort(d->comm);
+  d->comm = nullptr;
+  return nccl_check(r, "ncclCommAbort");
+}
+bool dp_alive(const DpState* d) { return d && d->comm; }
 int dp_world(const DpState* d) { return d ? d->world : 1; }
 int dp_rank(const DpState* d) { return d ? d->rank : 0; }

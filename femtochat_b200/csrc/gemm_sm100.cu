@@ -688,6 +688,49 @@ extern "C" int32_t femto_profile_gemm_report(double* h_ms, double* h_flops, int3
   return 0;
 }
 
+// ---- bounded-wait self test ---------------------------------------------------------------------------------------
+// Runs the wait primitive of every warp-specialised kernel on a barrier that nothing will ever complete, with a
+// small poll limit: the waiting thread must give up, raise the abort flag and status bit 2, the other role must see
+// the flag and unwind, and the kernel must return normally (no trap, no hang).  result[0] = 1 when the waiter timed
+// out, result[1] = 1 when the second role left through the abort flag.
+namespace {
+__global__ void k_bounded_wait_selftest(uint32_t limit, unsigned int* status, int* result) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); *abort_flag = 0; fence_barrier_init(); }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_limit(&bar, 0, abort_flag, status, limit);
+    result[0] = ok ? 0 : 1;
+  } else if (threadIdx.x == 32) {
+    // a second role waiting on the same dead barrier with the full limit: it must leave early through the abort flag
+    const bool ok = mbar_wait(&bar, 0, abort_flag, nullptr);
+    result[1] = (!ok && *abort_flag) ? 1 : 0;
+  }
+}
+}  // namespace
+
+extern "C" int32_t femto_selftest_bounded_wait(int32_t polls, int32_t* h_status, int32_t* h_result2) {
+  if (polls <= 0 || !h_status || !h_result2) return femto_fail(FEMTO_ERR_ARG, "bad argument");
+  unsigned int* status = nullptr;
+  FEMTO_TRY(standalone_status(&status));
+  int* result = nullptr;
+  char* scratch = nullptr;
+  FEMTO_TRY(standalone_scratch(256, &scratch));
+  result = reinterpret_cast<int*>(scratch);
+  CUDA_TRY(cudaMemset(result, 0, 2 * sizeof(int)));
+  k_bounded_wait_selftest<<<1, 64>>>((uint32_t)polls, status, result);
+  KERNEL_CHECK();
+  CUDA_TRY(cudaDeviceSynchronize());                 // the kernel returned by itself
+  unsigned int w = 0;
+  CUDA_TRY(cudaMemcpy(&w, status, sizeof(w), cudaMemcpyDeviceToHost));
+  CUDA_TRY(cudaMemset(status, 0, sizeof(w)));
+  CUDA_TRY(cudaMemcpy(h_result2, result, 2 * sizeof(int), cudaMemcpyDeviceToHost));
+  *h_status = (int32_t)w;
+  return 0;
+}
+
 // 0 = one CTA per 128 x 256 tile, 1 = CTA pairs per 256 x 256 tile wherever the shape allows (the default).
 static int g_pair_mode = -1;
 extern "C" int32_t femto_gemm_pair_mode(int32_t mode) {

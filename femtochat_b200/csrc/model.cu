@@ -162,18 +162,25 @@ void carve(femto_handle* h, Bump& b) {
   b.take(h->sin_t, sizeof(float) * h->cfg.max_document_tokens * half);
   b.take(h->cos_t, sizeof(float) * h->cfg.max_document_tokens * half);
   b.take(h->status, 256);
-  b.take(h->sh_wte, es * Vp * d);
-  b.take(h->sh_lm, es * Vp * d);
-  b.take(h->tok0, 4 * N); b.take(h->tgt0, 4 * N); b.take(h->pos, 4 * N); b.take(h->doc_start, 4 * N);
-  b.take(h->raw_tok, 4 * N); b.take(h->raw_tgt, 4 * N); b.take(h->raw_pos, 4 * N);
-  b.take(h->xe, es * N * d); b.take(h->x0, es * N * d); b.take(h->xm, es * N * d); b.take(h->xnf, es * N * d);
-  b.take(h->sg, 4 * N); b.take(h->rf, 4 * N);
+  // The compute-type copies of every weight lie in ONE contiguous range [weights_begin, weights_end): the
+  // data-parallel update exchanges them with a single collective.
   h->lb.resize(h->L);
+  b.take(h->sh_wte, es * Vp * d);
+  h->weights_begin = reinterpret_cast<char*>(h->sh_wte);
+  b.take(h->sh_lm, es * Vp * d);
   for (int i = 0; i < h->L; i++) {
     LayerBuf& l = h->lb[i];
     b.take(l.sh_wqkv, es * d * dq); b.take(l.sh_wo, es * d * d); b.take(l.sh_fc, es * d * 4 * d);
     b.take(l.sh_proj, es * 4 * d * d);
     if (h->lp[i].ve) b.take(l.sh_ve, es * Vp * kv); else l.sh_ve = nullptr;
+  }
+  { char* end = nullptr; b.take(end, 0); h->weights_end = end; }
+  b.take(h->tok0, 4 * N); b.take(h->tgt0, 4 * N); b.take(h->pos, 4 * N); b.take(h->doc_start, 4 * N);
+  b.take(h->raw_tok, 4 * N); b.take(h->raw_tgt, 4 * N); b.take(h->raw_pos, 4 * N);
+  b.take(h->xe, es * N * d); b.take(h->x0, es * N * d); b.take(h->xm, es * N * d); b.take(h->xnf, es * N * d);
+  b.take(h->sg, 4 * N); b.take(h->rf, 4 * N);
+  for (int i = 0; i < h->L; i++) {
+    LayerBuf& l = h->lb[i];
     b.take(l.xout, es * N * d); b.take(l.xn1, es * N * d); b.take(l.qkv, es * N * dq); b.take(l.att, es * N * d);
     b.take(l.xn2, es * N * d); b.take(l.a, es * N * 4 * d);
     b.take(l.r1, 4 * N); b.take(l.r2, 4 * N); b.take(l.rqk, 4 * N * (h->H + h->Hkv)); b.take(l.sv, 4 * N * h->Hkv);

@@ -37,6 +37,7 @@ struct femto_handle {
   float *sin_t = nullptr, *cos_t = nullptr;
   unsigned int* status = nullptr;
   void *sh_wte = nullptr, *sh_lm = nullptr;
+  char *weights_begin = nullptr, *weights_end = nullptr;   // the contiguous range holding every compute-type weight
   bool weights_valid = false;
   int *tok0 = nullptr, *tgt0 = nullptr, *pos = nullptr, *doc_start = nullptr, *raw_tok = nullptr, *raw_tgt = nullptr,
       *raw_pos = nullptr;
@@ -90,9 +91,12 @@ void dp_destroy(DpState* d);
 int dp_unique_id(void* id128);
 int dp_allreduce_sum_f32(DpState* d, float* buf, long long n, cudaStream_t s);
 int dp_allreduce_sum_i32(DpState* d, int* buf, long long n, cudaStream_t s);
+int dp_allreduce_sum_bf16(DpState* d, void* buf, long long n, cudaStream_t s);
 int dp_bucket_allreduce(DpState* d, float* buf, long long n, cudaStream_t compute);
 int dp_join(DpState* d, cudaStream_t compute);
 int dp_reduce_ranges(DpState* d, float* delta, const long long* gathers, int n_gathers, const long long* bcasts,
                      int n_bcasts, const long long* gaps, int n_gaps, cudaStream_t s);
+int dp_async_error(DpState* d);
+int dp_abort(DpState* d);
 int dp_world(const DpState* d);
 int dp_rank(const DpState* d);

@@ -45,6 +45,9 @@ struct femto_optimizer {
   std::vector<long long> bcasts;    // (offset, count, owner)
   std::vector<long long> gaps;      // (offset, count): what lies between them, replicated
   std::vector<long long> foreign;   // (offset, count): what this rank clears before the exchange of Theta
+  // the same for the model's compute-type weights: (byte offset from weights_begin, bytes) of what other ranks own
+  std::vector<size_t> foreign_weights;
+  int exchange_mode = 0;            // 0: fp32 Theta after every update; 1: compute-type weights only (Theta on demand)
 };
 
 namespace {
@@ -640,6 +643,18 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
   }
   // every rank now holds the new values of the ranges it owns; fetch the others' (a handle without a
   // communicator skips this: the caller merges the ranges itself, as the single-GPU emulation test does)
+  if (sharded && o->h->dp && o->exchange_mode == 1) {
+    // The update kernels wrote this rank's share of the compute-type weights.  Clear the shares of the others and
+    // add everybody's up: x + 0 + ... + 0 is exact in any type, and one large all-reduce is the collective NCCL
+    // runs fastest.  The fp32 Theta of foreign ranges is NOT refreshed here (optimizer_gather_theta does that).
+    for (size_t i = 0; i + 1 < o->foreign_weights.size(); i += 2)
+      CUDA_TRY(cudaMemsetAsync(h->weights_begin + o->foreign_weights[i], 0, o->foreign_weights[i + 1], s));
+    const long long n = (long long)((h->weights_end - h->weights_begin) / (h->bf ? 2 : 4));
+    if (h->bf) FEMTO_TRY(dp_allreduce_sum_bf16(h->dp, h->weights_begin, n, s));
+    else FEMTO_TRY(dp_allreduce_sum_f32(h->dp, reinterpret_cast<float*>(h->weights_begin), n, s));
+    o->h->weights_valid = true;
+    return 0;
+  }
   if (sharded && o->h->dp) {
     for (size_t i = 0; i + 1 < o->foreign.size(); i += 2)
       CUDA_TRY(cudaMemsetAsync(theta + o->foreign[i], 0, sizeof(float) * (size_t)o->foreign[i + 1], s));
@@ -686,10 +701,22 @@ int optimizer_set_shard(femto_optimizer* o, int rank, int world) {
   }
   struct R { long long off, n; int owner; };
   std::vector<R> rs;
+  const size_t es_model = h->bf ? 2 : 4;
+  auto clear_w = [&](const void* ptr, size_t bytes) {
+    if (!ptr || bytes == 0) return;
+    const size_t off = (size_t)(reinterpret_cast<const char*>(ptr) - h->weights_begin);
+    const size_t m = o->foreign_weights.size();
+    if (m && o->foreign_weights[m - 2] + o->foreign_weights[m - 1] == off) o->foreign_weights[m - 1] += bytes;
+    else { o->foreign_weights.push_back(off); o->foreign_weights.push_back(bytes); }
+  };
+  o->foreign_weights.clear();
   for (auto& g : o->muon) {
     const int k = (int)g.offs.size();
     g.k0 = 0; g.k1 = k;
     if (world == 1) continue;
+    // the value-embedding gates (n_kv_head x 12) are read from Theta in fp32 by the forward pass and cost nothing
+    // to update: every rank keeps updating all of them, like the scalars
+    if ((long long)g.in * g.out < 1024) continue;
     g.k0 = k; g.k1 = k;
     for (int i = 0; i < k; i++) {
       const int owner = (int)((long long)g.layers[i] * world / h->L);
@@ -731,7 +758,46 @@ int optimizer_set_shard(femto_optimizer* o, int rank, int world) {
   for (size_t i = 0; i + 1 < o->gaps.size(); i += 2) all.push_back({o->gaps[i], o->gaps[i + 1], 0});
   std::sort(all.begin(), all.end(), [](const Q& a, const Q& b) { return a.off < b.off; });
   for (const auto& q : all) if (q.owner != rank) clear(q.off, q.n);
+  // the compute-type weights this rank does not write: foreign slices of the tables, every matrix of foreign blocks
+  if (world > 1) {
+    for (const auto& g : o->adam) {
+      if (!g.shard || !g.shadow) continue;
+      const size_t slice = (size_t)(g.n / world) * es_model;
+      for (int r = 0; r < world; r++)
+        if (r != rank) clear_w(reinterpret_cast<char*>(g.shadow) + (size_t)r * slice, slice);
+    }
+    for (int i = 0; i < h->L; i++) {
+      if ((int)((long long)i * world / h->L) == rank) continue;
+      const LayerBuf& l = h->lb[i];
+      clear_w(l.sh_wqkv, es_model * (size_t)h->d * h->dq); clear_w(l.sh_wo, es_model * (size_t)h->d * h->d);
+      clear_w(l.sh_fc, es_model * (size_t)4 * h->d * h->d); clear_w(l.sh_proj, es_model * (size_t)4 * h->d * h->d);
+    }
+    std::vector<std::pair<size_t, size_t>> fw;
+    for (size_t i = 0; i + 1 < o->foreign_weights.size(); i += 2) fw.push_back({o->foreign_weights[i], o->foreign_weights[i + 1]});
+    std::sort(fw.begin(), fw.end());
+    o->foreign_weights.clear();
+    for (const auto& q : fw) { o->foreign_weights.push_back(q.first); o->foreign_weights.push_back(q.second); }
+  }
   return 0;
+}
+
+// How the owner-sharded update publishes its results.  mode 0 (default): the fp32 Theta is exchanged after every
+// update, so the caller's parameter vector is complete on every rank at all times (what a single-GPU host expects).
+// mode 1: only the model's compute-type weights are exchanged (half the bytes in a bf16 model, and no re-cast of
+// Theta afterwards); the fp32 values of ranges owned elsewhere then lag behind until optimizer_gather_theta.
+int optimizer_set_exchange(femto_optimizer* o, int mode) {
+  if (!o || (mode != 0 && mode != 1)) return femto_fail(FEMTO_ERR_ARG, "mode must be 0 or 1");
+  o->exchange_mode = mode;
+  return 0;
+}
+// Completes the fp32 Theta on every rank: each rank clears what it does not own, one all-reduce adds the owners' values
+// to zeros (exact).  Needed in exchange mode 1 before Theta is read by the host (checkpoint, evaluation elsewhere).
+int optimizer_gather_theta(femto_optimizer* o, float* theta, cudaStream_t s) {
+  if (!o || !theta) return femto_fail(FEMTO_ERR_ARG, "NULL argument");
+  if (o->shard_world <= 1 || !o->h->dp) return 0;
+  for (size_t i = 0; i + 1 < o->foreign.size(); i += 2)
+    CUDA_TRY(cudaMemsetAsync(theta + o->foreign[i], 0, sizeof(float) * (size_t)o->foreign[i + 1], s));
+  return dp_allreduce_sum_f32(o->h->dp, theta, o->h->nparams, s);
 }
 // Sum delta over ranks for this sharding: a range that one rank alone consumes is summed only onto that rank (on
 // the others it keeps the local gradient), the rest is all-reduced.
@@ -776,7 +842,8 @@ static void state_cover(femto_optimizer* o, int which, std::vector<long long>& o
       const long long per = which == 2 ? (long long)g.in * g.out : (long long)(g.out >= g.in ? g.out : g.in);
       const long long base = which == 2 ? g.moff : g.voff;
       for (size_t i = 0; i < g.offs.size(); i++)
-        put(base + (long long)i * per, per, world > 1 ? (long long)g.layers[i] * world / L : 0);
+        put(base + (long long)i * per, per,
+            (world > 1 && (long long)g.in * g.out >= 1024) ? (long long)g.layers[i] * world / L : 0);   // gates: replicated
     }
   }
 }

@@ -38,14 +38,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  abort_flag lives in shared memory; status in global memory (may be null).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned int* status) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned int* status,
+                                                uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
   if (status) atomicOr(status, ST_WAIT_TIMEOUT);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned int* status) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, WAIT_LIMIT);
 }
 
 // 2^x on the special-function unit (ex2.approx.ftz: relative error about 2^-22, flushes denormals).

@@ -9,7 +9,10 @@ columns of one global batch; rank 0 also runs a second, single-rank handle on al
 three updates: the loss sum and the token count, the summed gradient (on its owner where the sharded sum sends a
 range to one rank only), Theta, and (after femto_optimizer_gather_state) the four moment buffers.  Cases: owner-
 sharded and replicated update, two micro-steps with the sum taken after the last one only, and the bucketed sum that
-overlaps the reverse pass.  Plain NCCL collectives only.  Prints ONE JSON line on rank 0; exit code 0 iff every
+overlaps the reverse pass; the sharded update with both forms of its exchange (fp32 Theta every step, or only the
+compute-type weights with Theta completed on demand).  After every update the loss of a forward pass over each
+rank's columns, summed over ranks, is compared with the single-rank model's: the weights a rank computes with must be
+complete and current.  Plain NCCL collectives only.  Prints ONE JSON line on rank 0; exit code 0 iff every
 check passed.
 """
 from __future__ import annotations
@@ -50,7 +53,7 @@ def rel_err(a, b):
     return float((a.double() - b.double()).abs().max() / (b.double().abs().max() + 1e-30))
 
 
-def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
+def run_case(name, spec, rank, world, sharded, micro_steps, overlap, exchange=0):
     cfg = fb.GPTConfig(**spec["cfg"])
     lay = fb.parameter_layout(cfg)
     T, Bl = cfg.sequence_len, 2
@@ -76,6 +79,7 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
     opt = fb.MuonAdamW(params, lay, st, compute_type=spec["ctype"], weight_decay=0.1)
     if sharded:
         opt.shard(rank, world)
+        opt.set_exchange(exchange)
     ranges = opt.shard_ranges() if sharded else []
 
     ref = None
@@ -86,7 +90,7 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
         ropt = fb.MuonAdamW(rp, lay, rst, compute_type=spec["ctype"], weight_decay=0.1)
         ref = (rp, rst, ropt)
 
-    worst = dict(loss=0.0, delta=0.0, theta=0.0, moments=0.0)
+    worst = dict(loss=0.0, delta=0.0, theta=0.0, moments=0.0, loss_after_update=0.0)
     nt_exact = True
     replicated = True
     loss_acc = torch.zeros(1, device="cuda")
@@ -109,6 +113,17 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
         delta_local = params.delta.clone()
         kw = dict(eta=0.5 + 0.25 * step, mu=0.9, lam=0.05, Nt=float(nt))
         opt.step(**kw)
+        # The weights every rank now computes with (exchanged by the step) must be complete and current: the loss of a
+        # forward pass over this rank's columns, summed over ranks, against the single-rank model after ITS update.
+        tok, tgt, pos = batches[step * micro_steps]
+        sl = slice(rank * Bl, (rank + 1) * Bl)
+        fwd = torch.zeros(1, device="cuda")
+        _lib.check(_lib.lib().femto_forward_loss(st.h, _lib.ptr(params.theta), _lib.ptr(tok[sl].contiguous()),
+                                                 _lib.ptr(tgt[sl].contiguous()), _lib.ptr(pos[sl].contiguous()), Bl, 0,
+                                                 _lib.ptr(fwd), _lib.ptr(st._nvalid), _lib.stream_ptr()))
+        dist.all_reduce(fwd)
+        if sharded and exchange == 1:
+            opt.gather_theta()     # the fp32 Theta is completed on demand in this mode
         opt.gather_state()
         torch.cuda.synchronize()
         # Theta identical on every rank (bitwise) after the exchange, before anything else touches it
@@ -139,7 +154,11 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
                 merged[off:off + n] = buf
             worst["delta"] = max(worst["delta"], rel_err(merged, rp.delta))
             ropt.step(**{**kw, "Nt": float(rnv)})
+            rf = torch.zeros(1, device="cuda")
+            _lib.check(_lib.lib().femto_forward_loss(rst.h, _lib.ptr(rp.theta), _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), B, 0,
+                                                     _lib.ptr(rf), _lib.ptr(rst._nvalid), _lib.stream_ptr()))
             torch.cuda.synchronize()
+            worst["loss_after_update"] = max(worst["loss_after_update"], abs(float(fwd.item()) - float(rf.item())) / abs(float(rf.item())))
             worst["theta"] = max(worst["theta"], rel_err(params.theta, rp.theta))
             for a, b in ((opt.adam_m, ropt.adam_m), (opt.adam_v, ropt.adam_v), (opt.muon_m, ropt.muon_m),
                          (opt.muon_v, ropt.muon_v)):
@@ -151,13 +170,15 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap):
     status = st.status_word()
     tol = spec["tol"]
     ok = (nt_exact and replicated and status == 0 and worst["loss"] <= 1e-5 + tol * 1e-2 and worst["delta"] <= spec["tol_delta"] and
-          worst["theta"] <= tol and worst["moments"] <= tol)
+          worst["theta"] <= tol and worst["moments"] <= tol and worst["loss_after_update"] <= tol and
+          int(_lib.lib().femto_comm_check(st.h)) == 0)
     opt.close()
     st.close()
     if ref is not None:
         ref[2].close()
         ref[1].close()
-    return dict(case=name, sharded=sharded, micro_steps=micro_steps, overlap=overlap, ok=bool(ok), nt_exact=nt_exact,
+    return dict(case=name, sharded=sharded, micro_steps=micro_steps, overlap=overlap,
+                exchange=("compute-type weights" if (sharded and exchange == 1) else "fp32 Theta"), ok=bool(ok), nt_exact=nt_exact,
                 theta_bitwise_replicated=replicated, status=status, **{k: float(v) for k, v in worst.items()})
 
 
@@ -168,8 +189,9 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     results = []
     for name, spec in CASES.items():
-        for sharded, micro, overlap in ((True, 1, False), (False, 1, False), (True, 2, False), (False, 1, True)):
-            results.append(run_case(name, spec, rank, world, sharded, micro, overlap))
+        for sharded, micro, overlap, exchange in ((True, 1, False, 0), (True, 1, False, 1), (False, 1, False, 0),
+                                                  (True, 2, False, 1), (False, 1, True, 0)):
+            results.append(run_case(name, spec, rank, world, sharded, micro, overlap, exchange))
     ok = torch.tensor([1 if all(r["ok"] for r in results) else 0], device="cuda")
     dist.broadcast(ok, 0)
     if rank == 0:

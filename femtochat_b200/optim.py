@@ -26,7 +26,8 @@ SHARD_MIN_TABLE = 1 << 20
 def shard_plan(layout, world: int, min_table: int = SHARD_MIN_TABLE):
     """The partition `MuonAdamW.shard` uses, as sorted (offset, count, owner) triplets: every AdamW table of at
     least 2^20 elements whose size divides by 4*world is cut into `world` equal slices (slice r to rank r); the Muon
-    matrices of block i belong to rank i*world // n_layer, adjacent matrices of one owner merged into one range.
+    matrices of block i (of at least 1024 elements: the value-embedding gates are excepted) belong to rank
+    i*world // n_layer, adjacent matrices of one owner merged into one range.
     Everything else (scalars, gates, small or indivisible tables) is updated by every rank (`min_table` is the
     library's fixed 2^20; tests lower it to cut small tables).  The reference has no
     data-parallel path (scripts/train.jl:13); the ranges follow its parameter layout (src/parameters.jl:219-337)."""
@@ -47,7 +48,7 @@ def shard_plan(layout, world: int, min_table: int = SHARD_MIN_TABLE):
     mats = []
     for i, b in enumerate(layout.blocks):
         for k in ("wq", "wk", "wv", "wo", "fc", "proj", "ve_gate"):
-            if b[k] is not None:
+            if b[k] is not None and size(b[k]) >= 1024:      # the tiny value-embedding gates stay with every rank
                 mats.append((int(b[k].offset), size(b[k]), i * world // L))
     merged = []
     for off, n, owner in sorted(mats):
@@ -149,6 +150,15 @@ class MuonAdamW:
         updates slice `rank` of every large AdamW table and the Muon matrices of its share of the blocks, and `step`
         exchanges the results over the handle's communicator.  `world == 1` restores the full update."""
         _lib.check(_lib.lib().femto_optimizer_set_shard(self.o, int(rank), int(world)))
+
+    def set_exchange(self, mode: int):
+        """What a sharded `step` exchanges: 0 = the fp32 Theta (complete on every rank after every update), 1 = only the
+        model's compute-type weights (cheaper; call `gather_theta` before reading Theta on the host)."""
+        _lib.check(_lib.lib().femto_optimizer_set_exchange(self.o, int(mode)))
+
+    def gather_theta(self):
+        """Under `shard` with exchange mode 1: complete the fp32 Theta on every rank."""
+        _lib.check(_lib.lib().femto_optimizer_gather_theta(self.o, _lib.ptr(self.params.theta), _lib.stream_ptr()))
 
     def grad_sync(self, loss=None, n_valid=None):
         """Sum `params.delta` (and the device scalars `loss`, `n_valid`) over the ranks before `step`.  Under `shard`

@@ -179,6 +179,14 @@ int32_t femto_feeder_release(femto_feeder* f, void* compute_stream);
 int32_t femto_grad_sync(femto_handle* h, float* delta, float* loss_inout, int32_t* n_valid_inout,
                         void* stream);
 
+/* Health of the handle's communicator between steps: 0 while every collective enqueued so far succeeded or is still
+ * running, otherwise 200000 + the NCCL result (a peer died, a link fault).  Collectives report errors only when
+ * they are enqueued, so a training loop polls this (with its own wall-clock limit) and, on an error or a timeout,
+ * calls femto_comm_abort, which tears the communicator down without waiting; data-parallel calls then return
+ * FEMTO_ERR_STATE instead of blocking.  The reference has no counterpart (single process, single GPU). */
+int32_t femto_comm_check(femto_handle* h);
+int32_t femto_comm_abort(femto_handle* h);
+
 /* When enabled (world > 1), femto_loss_and_gradient sums each finished range of delta over ranks on a
  * communication stream while the rest of the reverse pass runs; femto_grad_sync then only waits for
  * those reductions.  Enable it for the LAST micro-step of an update only: earlier micro-steps must
@@ -208,13 +216,22 @@ int32_t femto_optimizer_step(femto_optimizer* o, float* theta, const float* delt
 /* Owner-sharded update for data parallelism (no counterpart in the reference, which is single-GPU:
  * scripts/train.jl:13).  After femto_grad_sync every rank holds the same delta, so rank `rank` of `world`
  * updates only slice `rank` of every large AdamW table (:333-390) and the Muon matrices (:405-425) of the
- * blocks [rank L / world, (rank+1) L / world); femto_optimizer_step then exchanges the new values over the
+ * blocks [rank L / world, (rank+1) L / world) (the tiny value-embedding gates excepted: every rank updates
+ * those); femto_optimizer_step then exchanges the new values over the
  * handle's communicator (each rank clears what it does not own, then one all-reduce of Theta), so Theta stays
  * replicated.
  * Small AdamW groups (scalars, gates) stay replicated.  The moments of ranges a rank does not own are not
  * advanced on that rank.  world == 1 restores the full update.  On a handle without a communicator the
  * exchange is skipped and the caller merges the ranges itself (femto_optimizer_shard_ranges). */
 int32_t femto_optimizer_set_shard(femto_optimizer* o, int32_t rank, int32_t world);
+/* What the sharded femto_optimizer_step exchanges.  mode 0 (default): the fp32 Theta, complete on every rank after
+ * every update.  mode 1: only the model's compute-type weights (one all-reduce over half the bytes in a bf16 model,
+ * and no second pass that re-casts Theta); the fp32 values of ranges owned by other ranks are then stale until
+ * femto_optimizer_gather_theta, which a host calls before it reads Theta (a checkpoint, src/checkpoints.jl:27-36).
+ * Training itself never reads them: a rank's optimiser touches only the ranges it owns, and the forward and reverse
+ * passes read the compute-type weights (the fp32 scalars and gates are updated by every rank). */
+int32_t femto_optimizer_set_exchange(femto_optimizer* o, int32_t mode);
+int32_t femto_optimizer_gather_theta(femto_optimizer* o, float* theta, void* stream);
 /* femto_grad_sync for a sharded optimiser: a range of delta that one rank alone consumes is summed only onto
  * that rank (in-place reduce-scatter per table, reduce to the owner per block), which moves half the bytes of
  * the all-reduce; on the other ranks such a range keeps the local gradient.  Everything else, the loss and
@@ -343,6 +360,12 @@ int32_t femto_status_word(femto_handle* h, int32_t* h_out);
 int32_t femto_sync(femto_handle* h, void* stream);
 /* Number of kernels launched by this handle since creation (host counter). */
 int64_t femto_launch_count(femto_handle* h);
+
+/* Self test of the bounded waits that every warp-specialised kernel uses: one thread waits, with a poll limit of
+ * `polls`, on a barrier that nothing completes.  It must give up and raise status bit 2 (*h_status), a second role
+ * waiting on the same barrier must leave through the abort flag, and the kernel must return by itself:
+ * h_result2[0] = waiter timed out, h_result2[1] = second role unwound.  Nothing traps or hangs. */
+int32_t femto_selftest_bounded_wait(int32_t polls, int32_t* h_status, int32_t* h_result2);
 
 /* Measurement aid (no counterpart in the reference): when enabled, every launch of the tensor-core
  * GEMM kernel is bracketed by CUDA events on its stream; the report returns the summed kernel time,

@@ -587,3 +587,18 @@ def test_gemm_cta_pairs_equal_single_ctas(ak, bk):
     ref2 = 1.0 + A2.double().cpu().T @ B2.double().cpu()
     assert (res[1].double() - ref2).abs().max() <= 1e-5 * ref2.abs().max()
     assert (res[0] - res[1]).abs().max() <= 1e-5 * ref2.abs().max()   # split counts may differ between the modes
+
+
+def test_bounded_wait_runs_out_cleanly():
+    """Every mbarrier wait in the tensor-core kernels is bounded.  The self test waits 1024 polls on a barrier nobody
+    arrives at: the waiter gives up and raises status bit 2, a second role waiting without a small limit unwinds
+    through the abort flag, the kernel returns by itself and the context stays usable."""
+    L = _lib.lib()
+    status, res = C.c_int32(-1), (C.c_int32 * 2)()
+    _lib.check(L.femto_selftest_bounded_wait(1024, C.byref(status), res))
+    assert status.value == 2 and list(res) == [1, 1]
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0                      # the device still answers
+    w = C.c_int32(-1)
+    _lib.check(L.femto_status_word(None, C.byref(w)))
+    assert w.value == 0                                      # the self test cleared the word it raised

@@ -240,7 +240,7 @@ def test_owner_sharded_update_matches_full_update(cfgkw, ctype, world, tol):
         assert 0 <= owner < world and n > 0
         owned[off:off + n] += 1
     assert int(owned.max()) == 1                       # disjoint
-    muon_elems = sum(sp.size for grp in opt_full.muon for sp in grp.specs)
+    muon_elems = sum(sp.size for grp in opt_full.muon for sp in grp.specs if sp.size >= 1024)   # gates: every rank
     big_tables = sum(gv.spec.size for gv in opt_full.adamw if gv.spec.size >= 1 << 20 and gv.spec.size % (4 * world) == 0)
     assert int(owned.sum()) == muon_elems + big_tables  # every Muon matrix and every divisible large table has one owner
     assert {o for _, _, o in ranges} == set(range(world))
@@ -276,7 +276,7 @@ def test_owner_sharded_update_matches_full_update(cfgkw, ctype, world, tol):
             at += n
         assert at == want.numel()
         if which >= 2:                                 # every rank owns some block's matrices
-            assert {o for _, _, o in cover} == set(range(world))
+            assert {o for _, _, o in cover} >= set(range(world))
         err = float((merged - want).abs().max())
         assert err <= tol * max(1.0, float(want.abs().max())), (name, err)
     opts[0].shard(0, 1)                                # back to the full update
