@@ -761,7 +761,12 @@ int optimizer_set_shard(femto_optimizer* o, int rank, int world) {
   // the compute-type weights this rank does not write: foreign slices of the tables, every matrix of foreign blocks
   if (world > 1) {
     for (const auto& g : o->adam) {
-      if (!g.shard || !g.shadow) continue;
+      if (!g.shadow) continue;
+      if (!g.shard) {
+        // a table too small to slice is updated by every rank: in the exchange (a sum over ranks) it counts as rank 0's
+        if (rank != 0) clear_w(g.shadow, (size_t)g.n * es_model);
+        continue;
+      }
       const size_t slice = (size_t)(g.n / world) * es_model;
       for (int r = 0; r < world; r++)
         if (r != rank) clear_w(reinterpret_cast<char*>(g.shadow) + (size_t)r * slice, slice);

@@ -115,7 +115,8 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap, exchange=0)
         opt.step(**kw)
         # The weights every rank now computes with (exchanged by the step) must be complete and current: the loss of a
         # forward pass over this rank's columns, summed over ranks, against the single-rank model after ITS update.
-        tok, tgt, pos = batches[step * micro_steps]
+        ftok, ftgt, fpos = batches[step * micro_steps]
+        tok, tgt, pos = ftok, ftgt, fpos
         sl = slice(rank * Bl, (rank + 1) * Bl)
         fwd = torch.zeros(1, device="cuda")
         _lib.check(_lib.lib().femto_forward_loss(st.h, _lib.ptr(params.theta), _lib.ptr(tok[sl].contiguous()),
@@ -155,7 +156,7 @@ def run_case(name, spec, rank, world, sharded, micro_steps, overlap, exchange=0)
             worst["delta"] = max(worst["delta"], rel_err(merged, rp.delta))
             ropt.step(**{**kw, "Nt": float(rnv)})
             rf = torch.zeros(1, device="cuda")
-            _lib.check(_lib.lib().femto_forward_loss(rst.h, _lib.ptr(rp.theta), _lib.ptr(tok), _lib.ptr(tgt), _lib.ptr(pos), B, 0,
+            _lib.check(_lib.lib().femto_forward_loss(rst.h, _lib.ptr(rp.theta), _lib.ptr(ftok), _lib.ptr(ftgt), _lib.ptr(fpos), B, 0,
                                                      _lib.ptr(rf), _lib.ptr(rst._nvalid), _lib.stream_ptr()))
             torch.cuda.synchronize()
             worst["loss_after_update"] = max(worst["loss_after_update"], abs(float(fwd.item()) - float(rf.item())) / abs(float(rf.item())))
