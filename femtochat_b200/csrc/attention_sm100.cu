@@ -12,6 +12,8 @@
 // each): they read S with tcgen05.ld, keep the running max / sum, rescale the TMEM-resident O only
 // when the max grew by more than 2^8, and write P with tcgen05.st.  S of tile j+1 is computed
 // while the softmax of tile j runs.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "sm100_ptx.cuh"
@@ -300,6 +302,334 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// Persistent forward kernel.  A kernel that allocates tensor memory runs ONE CTA per SM (measured: the runtime reports
+// an occupancy of one for any kernel containing tcgen05.alloc, whatever its other resources), so in the kernel above
+// every (query tile, head) pays its launch, barrier set-up, tensor-memory allocation, the latency of its first
+// loads and its final store with nothing else running on the SM: about as long as five key tiles of work, and a
+// query tile of the benchmark (documents of ~512 tokens, windows) sees only three to five key tiles.  Here one CTA
+// per SM walks a list of (query tile, head, batch row) items, heaviest first.  The roles are the same as above, but
+// they run through the item list asynchronously: the producer is already loading Q, K and V of the next item (Q is
+// double-buffered) while the threads finish the current one, the S issuer starts the next item's first products as
+// soon as their buffers are free, and only the first P V of an item waits until the threads have taken the previous
+// item's O out of tensor memory.
+constexpr int PF_SMEM = TILE_BYTES * 6 + 1024 + 256 + 3 * NS * 128 * 4;
+
+__device__ __forceinline__ void pf_item(const AttnArgs& a, int item, int nqt, int& qt, int& h, int& b) {
+  // heavy (late) query tiles first; within a query tile all heads and batch rows cost about the same
+  const int hb = a.H * a.B;
+  qt = nqt - 1 - item / hb;
+  const int rem = item % hb;
+  h = rem % a.H;
+  b = rem / a.H;
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                           const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                    // 2 stages (items)
+  uint8_t* sK = smem + 2 * TILE_BYTES;   // 2 stages (tiles)
+  uint8_t* sV = smem + 4 * TILE_BYTES;   // 2 stages (tiles)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* q_full = bars;        // [2] Q of an item (and its first key tile index) is in place
+  uint64_t* q_free = bars + 2;    // [2] every role has taken the item's parameters and its last S has been issued
+  uint64_t* k_full = bars + 4;    // [2]
+  uint64_t* v_full = bars + 6;    // [2]
+  uint64_t* s_full = bars + 8;    // [2] S of a tile is in TMEM; also frees the tile's K stage
+  uint64_t* p_ready = bars + 10;  // [2]
+  uint64_t* pv_done = bars + 12;  // [2] P V of a tile has been accumulated; also frees its V stage and its S/P buffer
+  uint64_t* o_free = bars + 14;   // [1] the threads have read the item's O out of tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* item_jlo = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2] first key tile of the item in each Q stage
+  float* xmax = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 256);  // [2 parities][NS][128 rows]
+  float* xl = xmax + 2 * NS * 128;                                      // [NS][128 rows]
+
+  const AttnArgs& a = p.a;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqt = a.T / BQ;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&q_full[i], 1); mbar_init(&q_free[i], 1 + NS * 4 + 1);
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], NS * 4); mbar_init(&pv_done[i], 1);
+    }
+    mbar_init(o_free, NS * 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO = tmem_base + 256;
+
+  // Every role walks the same items in the same order.  n = number of this CTA's items so far (Q stage n & 1, phase
+  // (n >> 1) & 1); tc = number of key tiles so far (K / V / S stage tc & 1, phase (tc >> 1) & 1).
+  if (warp == 0) {
+    // ---------------- TMA producer (whole warp: the 128 document starts of an item are reduced by the 32 lanes) ----------------
+    int tc = 0;
+    bool ok = true;
+    for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
+      int qt, h, b;
+      pf_item(a, item, nqt, qt, h, b);
+      const int kvh = h / (a.H / a.Hkv);
+      const int q0 = qt * BQ;
+      const long long row0 = (long long)b * a.T;
+      const int jhi = (q0 + BQ - 1) / BKV;
+      int jlo = max(0, q0 - a.window_left) / BKV;
+      if (a.doc_start) {
+        // key tiles that lie before the earliest document start of these 128 queries are fully masked
+        const int4 v = *reinterpret_cast<const int4*>(a.doc_start + row0 + q0 + lane * 4);
+        const int mn = __reduce_min_sync(0xffffffffu, min(min(v.x, v.y), min(v.z, v.w)));
+        jlo = max(jlo, mn / BKV);
+      }
+      const int ntile = jhi - jlo + 1;
+      if (lane == 0) {
+        const int qs = n & 1;
+        if (n >= 2 && !mbar_wait(&q_free[qs], ((n - 2) >> 1) & 1, abort_flag, a.status)) ok = false;
+        if (ok) {
+          item_jlo[qs] = jlo;
+          mbar_expect_tx(&q_full[qs], TILE_BYTES);   // the arrive publishes item_jlo to the roles that wait on q_full
+          tma_load_2d(sQ + qs * TILE_BYTES, &tmQ, &q_full[qs], p.q_col0 + h * HD, (int)(row0 + q0));
+          tma_load_2d(sQ + qs * TILE_BYTES + TILE_BYTES / 2, &tmQ, &q_full[qs], p.q_col0 + h * HD + 64, (int)(row0 + q0));
+          for (int i = 0; i < ntile; i++, tc++) {
+            const int st = tc & 1;
+            const uint32_t ph2 = ((tc - 2) >> 1) & 1;   // phase of tile tc-2, the previous user of this stage
+            const int krow = (int)(row0 + (jlo + i) * BKV);
+            if (tc >= 2 && !mbar_wait(&s_full[st], ph2, abort_flag, a.status)) { ok = false; break; }
+            mbar_expect_tx(&k_full[st], TILE_BYTES);
+            tma_load_2d(sK + st * TILE_BYTES, &tmK, &k_full[st], p.k_col0 + kvh * HD, krow);
+            tma_load_2d(sK + st * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[st], p.k_col0 + kvh * HD + 64, krow);
+            if (tc >= 2 && !mbar_wait(&pv_done[st], ph2, abort_flag, a.status)) { ok = false; break; }
+            mbar_expect_tx(&v_full[st], TILE_BYTES);
+            tma_load_2d(sV + st * TILE_BYTES, &tmV, &v_full[st], p.v_col0 + kvh * HD, krow);
+            tma_load_2d(sV + st * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[st], p.v_col0 + kvh * HD + 64, krow);
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      tc = __shfl_sync(0xffffffffu, tc, 0);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- S = Q K^T issuer ----------------
+      constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // both operands K-major
+      int tc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
+        int qt, h, b;
+        pf_item(a, item, nqt, qt, h, b);
+        const int qs = n & 1;
+        if (!mbar_wait(&q_full[qs], (n >> 1) & 1, abort_flag, a.status)) break;
+        const int ntile = (qt * BQ + BQ - 1) / BKV - item_jlo[qs] + 1;
+        const uint32_t q_addr = smem_u32(sQ + qs * TILE_BYTES);
+        for (int i = 0; i < ntile; i++, tc++) {
+          const int st = tc & 1;
+          if (!mbar_wait(&k_full[st], (tc >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
+          // S overwrites the buffer that held P of tile tc-2: its P V must have been executed
+          if (tc >= 2 && !mbar_wait(&pv_done[st], ((tc - 2) >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < HD / 16; k++) {
+            const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+            mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0);
+          }
+          tc_commit(&s_full[st]);
+        }
+        if (ok) tc_commit(&q_free[qs]);   // the item's last S has been issued: its Q stage may be refilled once it completes
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      // ---------------- O += P V issuer ----------------
+      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // V is N-contiguous
+      int tc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
+        int qt, h, b;
+        pf_item(a, item, nqt, qt, h, b);
+        const int qs = n & 1;
+        if (!mbar_wait(&q_full[qs], (n >> 1) & 1, abort_flag, a.status)) break;
+        const int ntile = (qt * BQ + BQ - 1) / BKV - item_jlo[qs] + 1;
+        mbar_arrive(&q_free[qs]);
+        // the accumulator still holds the previous item's O until the threads have read it
+        if (n >= 1 && !mbar_wait(o_free, (n - 1) & 1, abort_flag, a.status)) break;
+        for (int i = 0; i < ntile; i++, tc++) {
+          const int st = tc & 1;
+          const uint32_t ph = (tc >> 1) & 1;
+          if (!mbar_wait(&p_ready[st], ph, abort_flag, a.status)) { ok = false; break; }
+          if (!mbar_wait(&v_full[st], ph, abort_flag, a.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BKV / 16; k++)
+            mma_ts(tO, tS[st] + k * 8, smem_desc_sw128(v_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&pv_done[st]);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- softmax: NS threads per query row, each owns CW = 128 / NS of the keys of a tile ----------------
+    const int quad = warp & 3;
+    const int hs = (warp - 4) >> 2;        // which CW keys of each tile
+    const int r = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float c = rsqrtf((float)HD) * LOG2E;
+    int tc = 0;
+    bool ok = true;
+    for (int item = blockIdx.x, n = 0; item < nitems; item += gridDim.x, n++) {
+      int qt, h, b;
+      pf_item(a, item, nqt, qt, h, b);
+      const int qs = n & 1;
+      const int q0 = qt * BQ;
+      const int q = q0 + r;
+      const long long row0 = (long long)b * a.T;
+      // After a timed-out wait a warp keeps walking the items and tiles (skipping the work) so that it still meets
+      // its partner warp at every row barrier; both read the same tile count from shared memory.
+      if (ok && !mbar_wait(&q_full[qs], (n >> 1) & 1, abort_flag, a.status)) ok = false;
+      const int jlo = item_jlo[qs];
+      const int ntile = min(max((q0 + BQ - 1) / BKV - jlo + 1, 0), nqt);
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&q_free[qs]);
+      int lo = max(0, q - a.window_left);
+      if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
+      float m_used = -INFINITY, l = 0.f;
+      for (int i = 0; i < ntile; i++, tc++) {
+        const int st = tc & 1;
+        const uint32_t ph = (tc >> 1) & 1;
+        const int k0 = (jlo + i) * BKV + hs * CW;
+        // After a timed-out wait the warp keeps walking the loop (skipping the work) so that it still
+        // meets its partner warps at every row barrier.
+        if (ok && !mbar_wait(&s_full[st], ph, abort_flag, a.status)) ok = false;
+        if (!ok) { asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory"); continue; }
+        tc_fence_after();
+        float x[CW];
+#pragma unroll
+        for (int u = 0; u < CW / 32; u++)
+          tmem_ld32(tS[st] + lane_off + hs * CW + u * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[u * 32]));
+        tmem_ld_wait();
+        const bool need_mask = (k0 + CW - 1 > q) || (k0 < lo);
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < CW; j++) {
+            const int k = k0 + j;
+            x[j] = (k <= q && k >= lo) ? x[j] : -INFINITY;
+          }
+        }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < CW; j += 4) {
+          mx[0] = fmaxf(mx[0], x[j]); mx[1] = fmaxf(mx[1], x[j + 1]);
+          mx[2] = fmaxf(mx[2], x[j + 2]); mx[3] = fmaxf(mx[3], x[j + 3]);
+        }
+        float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;
+        xmax[(tc & 1) * (NS * 128) + hs * 128 + r] = mt;
+        asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+#pragma unroll
+        for (int o = 1; o < NS; o++) mt = fmaxf(mt, xmax[(tc & 1) * (NS * 128) + ((hs + o) % NS) * 128 + r]);
+        const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_used, mt);
+          const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+          l *= alpha;
+          m_used = m_new;
+          if (i > 0) {
+            // O lives in TMEM and is being accumulated by the tensor core: wait for the previous tile's P V
+            if (!mbar_wait(&pv_done[(tc - 1) & 1], ((tc - 1) >> 1) & 1, abort_flag, a.status)) { ok = false; continue; }
+            tc_fence_after();
+#pragma unroll
+            for (int u = 0; u < CW / 32; u++) {
+              uint32_t rr[32];
+              tmem_ld32(tO + lane_off + hs * CW + u * 32, rr);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; j++) rr[j] = __float_as_uint(__uint_as_float(rr[j]) * alpha);
+              tmem_st32(tO + lane_off + hs * CW + u * 32, rr);
+            }
+            tmem_st_wait();
+          }
+        }
+        const float mm = (m_used == -INFINITY) ? 0.f : m_used;
+        float sm[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int u = 0; u < CW / 32; u++) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const float p0 = fast_exp2(fmaf(x[u * 32 + 2 * j], c, -mm)), p1 = fast_exp2(fmaf(x[u * 32 + 2 * j + 1], c, -mm));
+            const float p2 = fast_exp2(fmaf(x[u * 32 + 2 * j + 2], c, -mm)), p3 = fast_exp2(fmaf(x[u * 32 + 2 * j + 3], c, -mm));
+            sm[0] += p0; sm[1] += p1; sm[2] += p2; sm[3] += p3;
+            pk[j] = pack_bf16(p0, p1);
+            pk[j + 1] = pack_bf16(p2, p3);
+          }
+          tmem_st16(tS[st] + lane_off + hs * (CW / 2) + u * 16, pk);
+        }
+        l += (sm[0] + sm[1]) + (sm[2] + sm[3]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[st]);
+      }
+      // ---- the item's O: out of tensor memory first (so that the next item's products can start), then to global memory ----
+      xl[hs * 128 + r] = l;
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+#pragma unroll
+      for (int o = 1; o < NS; o++) l += xl[((hs + o) % NS) * 128 + r];
+      if (ok && !mbar_wait(&pv_done[(tc - 1) & 1], ((tc - 1) >> 1) & 1, abort_flag, a.status)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        uint32_t rr[CW / 32][32];
+#pragma unroll
+        for (int u = 0; u < CW / 32; u++) tmem_ld32(tO + lane_off + (hs * (CW / 32) + u) * 32, rr[u]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_free);
+        const float inv = 1.f / l;
+        bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
+#pragma unroll
+        for (int u = 0; u < CW / 32; u++) {
+          const int cc = hs * (CW / 32) + u;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 qv;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&qv);
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+              w[e] = pack_bf16(__uint_as_float(rr[u][j + 2 * e]) * inv, __uint_as_float(rr[u][j + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(o + cc * 32 + j) = qv;
+          }
+        }
+        if (hs == 0) {
+          const long long si = ((long long)b * a.H + h) * a.T + q;
+          const float ln2 = 0.6931471805599453f;
+          if (a.lse) a.lse[si] = (m_used + log2f(l)) * ln2;
+          if (a.l) a.l[si] = l;
+          if (a.m) a.m[si] = m_used * ln2;
+        }
+      }
+      // the row's partner reads xl of this item before either thread may overwrite it for the next one
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace
 
 bool attention_tc_supported(const AttnArgs& a) {
@@ -326,10 +656,20 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
   const int dev = PerDevice::current();
   if (dev < 0 || !attr.done[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
+    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
     if (dev >= 0) attr.done[dev] = true;
   }
-  dim3 grid(a.T / BQ, a.H, a.B);
-  attn_fwd_tc_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
+  static int variant = -1;   // FEMTO_ATTN_FWD=1 in the environment selects the one-CTA-per-item kernel (measurement aid)
+  if (variant < 0) { const char* e = getenv("FEMTO_ATTN_FWD"); variant = (e && e[0] == '1') ? 1 : 2; }
+  // the persistent kernel assumes every query tile is full and starts on a 16-byte boundary of the document starts
+  if (variant == 2) {
+    const int nitems = (a.T / BQ) * a.H * a.B;
+    const int grid = std::min(nitems, device_sm_count());
+    attn_fwd_persistent_kernel<<<grid, FWD_THREADS, PF_SMEM, s>>>(tmQ, tmK, tmV, p, nitems);
+  } else {
+    dim3 grid(a.T / BQ, a.H, a.B);
+    attn_fwd_tc_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
+  }
   KERNEL_CHECK();
   return 0;
 }
