@@ -803,14 +803,20 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
   const int tiles = p.tiles_m * p.tiles_n * g.batch;
   int splits = 1;
   if (g.epi == EPI_F32 && tiles < 4 * workers) {
-    // pick the split count that minimises (waves x k-blocks per unit), bounded by the workspace
+    // Pick the split count that minimises waves x k-blocks per unit PLUS what the partials cost: every split writes
+    // and re-reads one fp32 copy of the result (8 bytes per element through HBM, the reduce pass not overlapped with
+    // anything).  Both terms in units of one k-block of one worker, with round figures for the two rates.
     const size_t per_unit = (size_t)tile_m * BN * 4;
-    long long best = (long long)cdiv(tiles, workers) * p.kblocks;
+    const double kblock_s = 2.0 * tile_m * BN * BK / (1.3e15 / workers);
+    static int charge = -1;
+    if (charge < 0) { const char* e = getenv("FEMTO_SPLIT_COST"); charge = (e && e[0] == '0') ? 0 : 1; }
+    const double per_split = charge ? 8.0 * g.M * (double)g.N * g.batch / 6.5e12 / kblock_s : 0.0;
+    double best = (double)cdiv(tiles, workers) * p.kblocks;
     for (int sp = 2; sp <= 32 && sp <= p.kblocks; sp++) {
       if ((size_t)tiles * sp * per_unit > g.ws_bytes) break;
       const int kbp = cdiv(p.kblocks, sp);
       if ((sp - 1) * kbp >= p.kblocks) continue;
-      const long long cost = (long long)cdiv((long long)tiles * sp, workers) * kbp + 4;  // +4: reduce pass
+      const double cost = (double)cdiv((long long)tiles * sp, workers) * kbp + sp * per_split;
       if (cost < best) { best = cost; splits = sp; }
     }
   }
