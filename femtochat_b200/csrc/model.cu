@@ -3,7 +3,6 @@
 #include "model.cuh"
 
 #include <math.h>
-#include <stdlib.h>
 #include <stdarg.h>
 #include <string.h>
 
@@ -141,7 +140,6 @@ int model_fill(femto_handle* h, const femto_config* cfg) {
   for (int i = 0; i < h->L; i++) { h->lp[i].ve = ve[i] != 0; h->lp[i].window = left[i]; }
   h->backout = h->L / 2;  // 1-based n_layer/2+1 (src/gpt.jl:145)
   h->xchunk = std::min(h->maxN, 16384);
-
   return 0;
 }
 

@@ -825,8 +825,8 @@ __global__ void __launch_bounds__(256) k_xent_dlogit_inplace(bf16* __restrict__ 
                                                              const float* __restrict__ lse_rows,
                                                              const int* __restrict__ tgt0, int V, float w_host,
                                                              const float* __restrict__ w_dev) {
-  const long long row = blockIdx.x;   // rows on the x axis: a chunk may hold more than 65 535 of them
-  const int col0 = blockIdx.y * 8192 + threadIdx.x * 8;
+  const long long row = blockIdx.y;
+  const int col0 = blockIdx.x * 8192 + threadIdx.x * 8;
   const int tg = tgt0[row];
   const float w = tg >= 0 ? w_host * (w_dev ? w_dev[0] : 1.f) : 0.f;
   const float lse = lse_rows[row];
@@ -1036,7 +1036,7 @@ int xent_finalize(const float2* stats, int ntile, const float* tz, const int* tg
 int xent_dlogit_inplace(void* logits_bf16, long long ld, const float* lse_rows, const int* tgt0, int n, int V, float w,
                         const float* w_dev, cudaStream_t s) {
   if ((ld & 7) || (V & 7)) return femto_fail(FEMTO_ERR_ALIGN, "xent_dlogit_inplace: row pitch and vocabulary must be multiples of 8");
-  k_xent_dlogit_inplace<<<dim3(n, cdiv(V, 8192)), 256, 0, s>>>(reinterpret_cast<bf16*>(logits_bf16), ld, lse_rows, tgt0, V, w, w_dev);
+  k_xent_dlogit_inplace<<<dim3(cdiv(V, 8192), n), 256, 0, s>>>(reinterpret_cast<bf16*>(logits_bf16), ld, lse_rows, tgt0, V, w, w_dev);
   KERNEL_CHECK();
   return 0;
 }
