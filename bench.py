@@ -37,6 +37,12 @@ CONFIGS = {
 }
 
 
+# DRAM traffic of the dominant kernel from one ncu capture of the full-size step (dram__bytes_read.sum +
+# dram__bytes_write.sum over the 312 gemm_tc_kernel launches of a step; profiles/gemm_tc_kernel_d20_step_dram.md),
+# and the algorithmic bytes of the same launches (operands and results once, fp32 weight gradients read-modify-write).
+NCU_GEMM_TRAFFIC = {("d20", 32, 1): dict(bytes_per_launch=922.5e6, algorithmic_bytes_per_launch=729.3e6, launches=312)}
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -333,7 +339,10 @@ def run_ours(args):
             gpu_launches=int(launches),
             clocks=clk,
             roofline=dict(bound="tensor", achieved=ach, peak=peak_tf, unit="TFLOP/s", frac=ach / peak_tf if peak_tf else None,
-                          traffic=None, kernel="gemm_tc_kernel", launches_per_step=gl.value,
+                          traffic=(NCU_GEMM_TRAFFIC.get((args.config, B, micro)) or {}).get("bytes_per_launch"),
+                          traffic_algorithmic=(NCU_GEMM_TRAFFIC.get((args.config, B, micro)) or {}).get("algorithmic_bytes_per_launch"),
+                          traffic_source="ncu, one capture of the full-size step: profiles/gemm_tc_kernel_d20_step_dram.md",
+                          kernel="gemm_tc_kernel", launches_per_step=gl.value,
                           kernel_ms_per_step=gms.value, peak_source=f"{peaks['source']} (sustained cuBLAS bf16)"),
         )
         if args.cpu_baseline and world == 1:   # the host baseline belongs to the one-GPU line only
