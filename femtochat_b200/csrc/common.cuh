@@ -142,6 +142,8 @@ struct GemmArgs {
   // square symmetric result: tiles that lie entirely below the diagonal are not computed (the caller mirrors
   // the upper triangle afterwards); honoured by the tensor-core kernel, ignored by the SIMT fallback
   bool upper_only = false;
+  int ring = 0;   // depth of the operand ring of the tensor-core kernel; 0 = the deepest that fits (fewer stages leave
+                  // shared memory free for kernels of another stream to run on the same SMs)
   // cross-entropy statistics epilogue
   const int* targets0 = nullptr;   // [M] 0-based target or -1
   float2* stats = nullptr;         // [M][2 * ntiles_n] partial (max, sumexp)
@@ -217,5 +219,10 @@ struct XentArgs {
   float2* stats = nullptr; float* tz = nullptr; float* lse_rows = nullptr; float* loss_rows = nullptr;
   void* dlogit = nullptr;       // [chunk][ldw] of T
   void* ws = nullptr; size_t ws_bytes = 0; unsigned int* status = nullptr;
+  // Optional second stream for the weight-gradient GEMM of each chunk (with its own split-K workspace, a second
+  // dlogit buffer so that the next chunk's logits do not wait for it, and two events + one fork event).
+  cudaStream_t side = nullptr; void* ws2 = nullptr; void* dlogit2 = nullptr;
+  cudaEvent_t ev_read[2] = {nullptr, nullptr}; cudaEvent_t ev_fork[2] = {nullptr, nullptr};
 };
 template <typename T> int xent_tail(const XentArgs& x, cudaStream_t s);
+bool gemm_profiling();   // per-launch GEMM timing is on: every launch stays on one stream so that the times add up

@@ -49,6 +49,7 @@ struct TcParams {
   int tma_store;   // bf16 results leave through shared memory and TMA tiled stores
   int pair;        // units are 256-row tiles computed by CTA pairs
   int a_slabs, b_slabs;  // an M/N-contiguous operand arrives with one 4-d copy per k-block instead of one per 64-wide slab
+  int stages;      // depth of the operand ring (<= Geo::STAGES; fewer stages leave shared memory to co-resident kernels)
 };
 
 // Tile rasterisation: groups of GROUP_M row-tiles are walked column by column, so one wave of CTAs
@@ -183,7 +184,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const TcParams p) {
   typedef Geo<PAIR> G;
-  constexpr int STAGES = G::STAGES, STAGE_BYTES = G::STAGE_BYTES, TILE_M = G::TILE_M;
+  constexpr int STAGE_BYTES = G::STAGE_BYTES, TILE_M = G::TILE_M;
+  const int STAGES = p.stages;
   extern __shared__ uint8_t smem_raw[];
   // the same offsets in both CTAs of a pair: the shared-memory window of every CTA starts on the same alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -667,6 +669,7 @@ struct GemmProfile {
 } g_prof;
 }  // namespace
 
+bool gemm_profiling() { return g_prof.on; }
 extern "C" int32_t femto_profile_gemm(int32_t enable) {
   for (auto e : g_prof.ev) cudaEventDestroy(e);
   g_prof.ev.clear();
@@ -753,7 +756,8 @@ static int launch_tc(const GemmArgs& g, const CUtensorMap& tmA, const CUtensorMa
     if (dev >= 0) attr.done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = G::SMEM_BYTES; cfg.stream = s;
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NTHREADS); cfg.stream = s;
+  cfg.dynamicSmemBytes = G::SMEM_BYTES - (G::STAGES - p.stages) * G::STAGE_BYTES;
   static int pdl = -1;   // FEMTO_PDL=0 in the environment launches fully serialised (measurement aid)
   if (pdl < 0) { const char* e = getenv("FEMTO_PDL"); pdl = (e && e[0] == '0') ? 0 : 1; }
   cudaLaunchAttribute at[2];
@@ -795,6 +799,13 @@ int gemm_tc_bf16(const GemmArgs& g, cudaStream_t s) {
     if (pair) { p.a_slabs = !g.a_kmajor; p.b_slabs = !g.b_kmajor; }
   }
   p.pair = pair ? 1 : 0;
+  {
+    // FEMTO_GEMM_STAGES in the environment shortens the operand ring (measurement aid)
+    static int want = -1;
+    if (want < 0) { const char* e = getenv("FEMTO_GEMM_STAGES"); want = e ? atoi(e) : 0; }
+    const int full = pair ? Geo<true>::STAGES : Geo<false>::STAGES;
+    p.stages = (want >= 2 && want <= full) ? want : (g.ring >= 2 && g.ring <= full) ? g.ring : full;
+  }
   const int tile_m = pair ? 2 * BM : BM;
   const int workers = pair ? sms / 2 : sms;      // CTAs, or CTA pairs, that run at once
   p.tiles_m = cdiv(g.M, tile_m);

@@ -188,6 +188,7 @@ void carve(femto_handle* h, Bump& b) {
   }
   b.take(h->dx, es * N * d); b.take(h->dxn, es * N * d); b.take(h->dqkv, es * N * dq); b.take(h->datt, es * N * d);
   b.take(h->du, es * N * 4 * d); b.take(h->dx0, es * N * d); b.take(h->dxf, es * N * d); b.take(h->dve, es * N * kv);
+  b.take(h->dx_b, es * N * d); b.take(h->dx_c, es * N * d); b.take(h->du_b, es * N * 4 * d); b.take(h->dqkv_b, es * N * dq);
   b.take(h->dpre, 4 * N * h->Hkv); b.take(h->dpre_s, 4 * N);
   b.take(h->partial, 4 * (size_t)std::max<size_t>(1024 * 32, (N / 256 + 1) * 12 * h->Hkv));
   const size_t xc = h->xchunk;
@@ -195,9 +196,11 @@ void carve(femto_handle* h, Bump& b) {
   b.take(h->xstats, sizeof(float2) * xc * (2 * ((h->V + 255) / 256) + 2));
   b.take(h->tz, 4 * N); b.take(h->lse_rows, 4 * N); b.take(h->loss_rows, 4 * N); b.take(h->inv_nvalid, 256);
   b.take(h->dlogit, es * xc * Vp);
+  b.take(h->dlogit_b, es * xc * Vp);
   b.take(h->loss_dev, 256); b.take(h->nvalid_dev, 256);
   h->gemm_ws_bytes = (size_t)160 << 20;
   b.take(h->gemm_ws, h->gemm_ws_bytes);
+  b.take(h->gemm_ws2, h->gemm_ws_bytes);
   h->attn_ws_bytes = std::max(sizeof(float) * N * h->H * 2, attention_bwd_tc_ws_bytes(h->maxB, h->T, h->H, h->hd));
   b.take(h->attn_ws, h->attn_ws_bytes);
 }
@@ -231,11 +234,25 @@ int model_alloc(femto_handle* h) {
   KERNEL_CHECK();
   int maxcols = std::max(h->d, h->kv);
   FEMTO_TRY(scatter_plan_create(&h->plan, h->maxN, maxcols));
+  // FEMTO_SIDE_STREAM=0 in the environment keeps every launch on the caller's stream (measurement aid)
+  const char* env = getenv("FEMTO_SIDE_STREAM");
+  if (!(env && env[0] == '0')) {
+    int least = 0, greatest = 0;
+    CUDA_TRY(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    CUDA_TRY(cudaStreamCreateWithPriority(&h->hi, cudaStreamNonBlocking, greatest));
+    CUDA_TRY(cudaStreamCreateWithPriority(&h->lo, cudaStreamNonBlocking, least));
+    for (auto& e : h->ev_fork) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    for (auto& e : h->ev_side) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
   CUDA_TRY(cudaDeviceSynchronize());
   return 0;
 }
 
 void model_free(femto_handle* h) {
+  if (h->hi) { cudaStreamSynchronize(h->hi); cudaStreamDestroy(h->hi); h->hi = nullptr; }
+  if (h->lo) { cudaStreamSynchronize(h->lo); cudaStreamDestroy(h->lo); h->lo = nullptr; }
+  for (auto& e : h->ev_fork) if (e) { cudaEventDestroy(e); e = nullptr; }
+  for (auto& e : h->ev_side) if (e) { cudaEventDestroy(e); e = nullptr; }
   if (h->plan) scatter_plan_destroy(h->plan);
   h->plan = nullptr;
   if (h->arena) cudaFree(h->arena);
@@ -283,14 +300,16 @@ __global__ void __launch_bounds__(1024) k_inv_nvalid(const int* tgt0, int n, flo
 template <typename T>
 static int step_t(femto_handle* h, const float* theta, float* delta, const int* tokens, const int* targets,
                   const int* positions, int B, int reduction, bool backward, bool accumulate, float* loss_out,
-                  int* nvalid_out, cudaStream_t s, float* logits_out, float* token_losses_out, const StepExtra* ex) {
+                  int* nvalid_out, cudaStream_t s, cudaStream_t side, float* logits_out, float* token_losses_out,
+                  const StepExtra* ex) {
   typedef Stream<T> S;
   const int Tl = (ex && ex->T > 0) ? ex->T : h->T;
   const int N = B * Tl, d = h->d, dq = h->dq, kv = h->kv, H = h->H, Hkv = h->Hkv, hd = h->hd, Vp = h->Vp, V = h->V;
   const int L = h->L;
   const float eps = h->eps;
   const bool mean = reduction == FEMTO_REDUCTION_MEAN;
-  auto GA = [&]() { GemmArgs g; g.ws = h->gemm_ws; g.ws_bytes = h->gemm_ws_bytes; g.status = h->status; return g; };
+  // with a side stream the GEMMs give up one ring stage (32 KB), so that streaming kernels of the other stream fit beside them
+  auto GA = [&]() { GemmArgs g; g.ws = h->gemm_ws; g.ws_bytes = h->gemm_ws_bytes; g.status = h->status; g.ring = (backward && side) ? 5 : 0; return g; };
   // Y[N][out] = X[N][in] * W[in][out]
   auto lin_fwd = [&](const void* X, int in, const void* W, int out, void* Y, int ldy, int epi, const void* aux) {
     GemmArgs g = GA();
@@ -305,17 +324,56 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     g.C = dX; g.ldc = in; g.M = N; g.N = in; g.K = out; g.epi = epi; g.aux = aux; g.ldaux = in;
     return gemm<T>(g, s);
   };
+  // The weight-gradient GEMMs, the zero fill of delta: on the side stream when the handle has one (`s` is then the
+  // handle's chain stream).  fork(): the side stream waits for everything queued on the chain so far.
+  // side_read(slot): the side stream's last launch read gradient buffer `slot`; chain_write(slot): the chain is
+  // about to overwrite that buffer and waits for that reader.
+  cudaStream_t s2 = (backward && side) ? side : s;
+  const bool two = s2 != s;
+  enum { SL_DX = 0, SL_DU = 3, SL_DQKV = 5, SL_FILL = 7 };
+  auto fork = [&]() -> int {
+    if (!two) return 0;
+    cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    CUDA_TRY(cudaEventRecord(e, s));
+    CUDA_TRY(cudaStreamWaitEvent(s2, e, 0));
+    return 0;
+  };
+  auto side_read = [&](int slot) -> int {
+    if (!two) return 0;
+    CUDA_TRY(cudaEventRecord(h->ev_side[slot], s2));
+    h->side_armed[slot] = true;
+    return 0;
+  };
+  auto chain_write = [&](int slot) -> int {
+    if (!two || !h->side_armed[slot]) return 0;
+    CUDA_TRY(cudaStreamWaitEvent(s, h->ev_side[slot], 0));
+    h->side_armed[slot] = false;
+    return 0;
+  };
+  auto join = [&]() -> int {   // the chain waits for everything queued on the side stream
+    if (!two) return 0;
+    cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    CUDA_TRY(cudaEventRecord(e, s2));
+    CUDA_TRY(cudaStreamWaitEvent(s, e, 0));
+    for (bool& a : h->side_armed) a = false;
+    return 0;
+  };
   // dW[in][out] += X[N][in]^T * dY[N][out]
   auto lin_dw = [&](const void* X, int in, const void* dY, int ldy, int out, float* dW) {
     GemmArgs g = GA();
+    if (two) g.ws = h->gemm_ws2;
     g.A = X; g.lda = in; g.a_kmajor = false; g.B = dY; g.ldb = ldy; g.b_kmajor = false;
     g.C = dW; g.ldc = out; g.M = in; g.N = out; g.K = N; g.epi = EPI_F32; g.beta = 1.f;
-    return gemm<T>(g, s);
+    return gemm<T>(g, s2);
   };
 
   FEMTO_TRY(S::prep_tokens(tokens, targets, positions, B, Tl, h->cfg.index_base, V, h->cfg.max_document_tokens,
                            h->tok0, h->tgt0, h->pos, h->doc_start, h->status, s));
-  if (backward && !accumulate) FEMTO_TRY(fill_zero(delta, sizeof(float) * (size_t)h->nparams, s));
+  if (backward && !accumulate) {   // off the chain: nothing reads or writes delta before the lm_head tail
+    FEMTO_TRY(fork());
+    FEMTO_TRY(fill_zero(delta, sizeof(float) * (size_t)h->nparams, s2));
+    FEMTO_TRY(side_read(SL_FILL));
+  }
   const int* docs = h->cfg.doc_mask ? h->doc_start : nullptr;
 
   // ---- forward (src/gpt.jl:129-170) ----
@@ -377,6 +435,12 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     x.dw = backward ? delta + h->off_lm : nullptr; x.chunk = h->xchunk; x.logits_f32 = h->logits_f32;
     x.stats = h->xstats; x.tz = h->tz; x.lse_rows = h->lse_rows; x.loss_rows = h->loss_rows; x.dlogit = h->dlogit;
     x.ws = h->gemm_ws; x.ws_bytes = h->gemm_ws_bytes; x.status = h->status;
+    if (two) {
+      x.side = s2; x.ws2 = h->gemm_ws2; x.dlogit2 = h->dlogit_b;
+      x.ev_read[0] = h->ev_side[8]; x.ev_read[1] = h->ev_side[9];
+      x.ev_fork[0] = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+      x.ev_fork[1] = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    }
     FEMTO_TRY(xent_tail<T>(x, s));
   }
   if (token_losses_out)   // reduction=:none (src/gpt.jl:191-193): one loss per token slot, 0 where the target is ignored
@@ -390,58 +454,87 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   // reverse pass runs.
   const bool ov = h->overlap_sync && h->dp != nullptr;
   h->delta_synced = false;
-  if (ov) FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_lm, (long long)Vp * d, s));
+  FEMTO_TRY(chain_write(SL_FILL));   // the chain's first write into delta follows the zero fill
+  if (ov) {
+    FEMTO_TRY(join());
+    FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_lm, (long long)Vp * d, s));
+  }
   int nb = 0;
   FEMTO_TRY(scatter_plan_build(h->plan, h->tok0, N, Vp, s));
   FEMTO_TRY(S::head_bwd(dxnf, (const T*)h->xnf, h->rf, xb, (T*)h->dxf, N, d, h->partial, &nb, s));
   FEMTO_TRY(reduce_partials(h->partial, nb, 1, delta + h->off_lam_y, nullptr, 1.f, true, s));
-  CUDA_TRY(cudaMemcpyAsync(h->dx, h->dxf, sizeof(T) * (size_t)N * d, cudaMemcpyDeviceToDevice, s));
-  T* dx = (T*)h->dx;
+  // The gradient of the residual stream rotates through three buffers, d(MLP pre-activation) and d(QKV) through
+  // two each: a weight-gradient GEMM on the side stream may still be reading one while the chain writes the next.
+  T* dxr[3] = {(T*)h->dx, (T*)h->dx_b, (T*)h->dx_c};
+  T* dur[2] = {(T*)h->du, (T*)h->du_b};
+  T* dqr[2] = {(T*)h->dqkv, (T*)h->dqkv_b};
+  int ci = 0;
+  CUDA_TRY(cudaMemcpyAsync(dxr[0], h->dxf, sizeof(T) * (size_t)N * d, cudaMemcpyDeviceToDevice, s));
   T* dxn = (T*)h->dxn;
   for (int i = L - 1; i >= 0; i--) {
     const LayerP& p = h->lp[i];
     LayerBuf& l = h->lb[i];
     const T* xin = i == 0 ? (const T*)h->x0 : (const T*)h->lb[i - 1].xout;
+    const int c1 = (ci + 1) % 3, c2 = (ci + 2) % 3, par = i & 1;
+    T *dx = dxr[ci], *dx1 = dxr[c1], *dx2 = dxr[c2], *du = dur[par], *dqkv = dqr[par];
     if (i == h->backout) FEMTO_TRY(S::axpy(dx, (const T*)h->dxf, theta + h->off_lam_y, -1.f, (long long)N * d, s));
     // MLP (ext/FemtoChatEnzymeExt.jl:121-134)
+    FEMTO_TRY(fork());
     FEMTO_TRY(lin_dw(l.a, 4 * d, dx, d, d, delta + p.proj));
-    FEMTO_TRY(lin_dx(dx, d, d, l.sh_proj, 4 * d, h->du, EPI_DRELU2, l.a));
-    FEMTO_TRY(lin_dw(l.xn2, d, h->du, 4 * d, 4 * d, delta + p.fc));
-    FEMTO_TRY(lin_dx(h->du, 4 * d, 4 * d, l.sh_fc, d, dxn, EPI_STORE, nullptr));
-    FEMTO_TRY(S::norm_bwd_resid(dxn, (const T*)l.xn2, l.r2, dx, dx, N, d, s));
+    FEMTO_TRY(side_read(SL_DX + ci));
+    FEMTO_TRY(chain_write(SL_DU + par));
+    FEMTO_TRY(lin_dx(dx, d, d, l.sh_proj, 4 * d, du, EPI_DRELU2, l.a));
+    FEMTO_TRY(fork());
+    FEMTO_TRY(lin_dw(l.xn2, d, du, 4 * d, 4 * d, delta + p.fc));
+    FEMTO_TRY(side_read(SL_DU + par));
+    FEMTO_TRY(lin_dx(du, 4 * d, 4 * d, l.sh_fc, d, dxn, EPI_STORE, nullptr));
+    FEMTO_TRY(chain_write(SL_DX + c1));
+    FEMTO_TRY(S::norm_bwd_resid(dxn, (const T*)l.xn2, l.r2, dx, dx1, N, d, s));
     // attention block
-    FEMTO_TRY(lin_dw(l.att, d, dx, d, d, delta + p.wo));
-    FEMTO_TRY(lin_dx(dx, d, d, l.sh_wo, d, h->datt, EPI_STORE, nullptr));
+    FEMTO_TRY(fork());
+    FEMTO_TRY(lin_dw(l.att, d, dx1, d, d, delta + p.wo));
+    FEMTO_TRY(side_read(SL_DX + c1));
+    FEMTO_TRY(lin_dx(dx1, d, d, l.sh_wo, d, h->datt, EPI_STORE, nullptr));
+    FEMTO_TRY(chain_write(SL_DQKV + par));
     AttnArgs a;
     a.Q = l.qkv; a.K = (const T*)l.qkv + d; a.V = (const T*)l.qkv + d + kv; a.q_stride = dq; a.kv_stride = dq;
     a.O = l.att; a.o_stride = d; a.lse = l.lse; a.dO = h->datt; a.do_stride = d;
-    a.dQ = h->dqkv; a.dK = (T*)h->dqkv + d; a.dV = (T*)h->dqkv + d + kv; a.dq_stride = dq; a.dkv_stride = dq;
+    a.dQ = dqkv; a.dK = dqkv + d; a.dV = dqkv + d + kv; a.dq_stride = dq; a.dkv_stride = dq;
     a.B = B; a.T = Tl; a.H = H; a.Hkv = Hkv; a.hd = hd; a.window_left = p.window; a.doc_start = docs;
     a.ws = h->attn_ws; a.ws_bytes = h->attn_ws_bytes; a.status = h->status;
     FEMTO_TRY(attention_bwd<T>(a, s));
-    FEMTO_TRY(S::qkv_post_bwd((T*)h->dqkv, (const T*)l.qkv, dq, p.ve ? (const T*)l.sh_ve : nullptr, h->tok0, h->pos,
+    FEMTO_TRY(S::qkv_post_bwd(dqkv, (const T*)l.qkv, dq, p.ve ? (const T*)l.sh_ve : nullptr, h->tok0, h->pos,
                               h->sin_t, h->cos_t, N, H, Hkv, hd, l.rqk, l.sv, (T*)h->dve, h->dpre, s));
+    FEMTO_TRY(fork());
     {
       GemmArgs g = GA();  // fused dW of Q, K, V: three destinations in delta
-      g.A = l.xn1; g.lda = d; g.a_kmajor = false; g.B = h->dqkv; g.ldb = dq; g.b_kmajor = false;
+      if (two) g.ws = h->gemm_ws2;
+      g.A = l.xn1; g.lda = d; g.a_kmajor = false; g.B = dqkv; g.ldb = dq; g.b_kmajor = false;
       g.M = d; g.N = dq; g.K = N; g.epi = EPI_F32; g.beta = 1.f; g.nseg = 3;
       g.seg_col0[0] = 0; g.seg_ncol[0] = d; g.seg_ptr[0] = delta + p.wq; g.seg_ld[0] = d;
       g.seg_col0[1] = d; g.seg_ncol[1] = kv; g.seg_ptr[1] = delta + p.wk; g.seg_ld[1] = kv;
       g.seg_col0[2] = d + kv; g.seg_ncol[2] = kv; g.seg_ptr[2] = delta + p.wv; g.seg_ld[2] = kv;
       g.C = delta + p.wq; g.ldc = d;
-      FEMTO_TRY(gemm<T>(g, s));
+      FEMTO_TRY(gemm<T>(g, s2));
     }
-    FEMTO_TRY(lin_dx(h->dqkv, dq, dq, l.sh_wqkv, d, dxn, EPI_STORE, nullptr));
+    FEMTO_TRY(side_read(SL_DQKV + par));
+    FEMTO_TRY(lin_dx(dqkv, dq, dq, l.sh_wqkv, d, dxn, EPI_STORE, nullptr));
     if (p.ve) {
       FEMTO_TRY(S::ve_gate_bwd((const T*)l.xn1, d, h->dpre, theta + p.ve_gate, dxn, N, Hkv, h->partial, &nb, s));
       FEMTO_TRY(reduce_partials(h->partial, nb, 12 * Hkv, delta + p.ve_gate, nullptr, 1.f, true, s));
       FEMTO_TRY(scatter_rows<T>(h->plan, delta + p.ve_table, (const T*)h->dve, kv, kv, s));
     }
-    FEMTO_TRY(S::mix_bwd(dx, dxn, (const T*)l.xn1, l.r1, xin, (const T*)h->x0, theta + p.lam_b, theta + p.lam_x0,
+    FEMTO_TRY(chain_write(SL_DX + c2));
+    FEMTO_TRY(S::mix_bwd(dx1, dx2, dxn, (const T*)l.xn1, l.r1, xin, (const T*)h->x0, theta + p.lam_b, theta + p.lam_x0,
                          (T*)h->dx0, i == L - 1, N, d, h->partial, &nb, s));
     FEMTO_TRY(reduce_partials(h->partial, nb, 2, delta + p.lam_b, nullptr, 1.f, true, s));
-    if (ov) FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + p.wq, p.lam_x0 + 1 - p.wq, s));   // the block's range is contiguous
+    ci = c2;
+    if (ov) {
+      FEMTO_TRY(join());
+      FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + p.wq, p.lam_x0 + 1 - p.wq, s));   // the block's range is contiguous
+    }
   }
+  T* dx = dxr[ci];
   FEMTO_TRY(S::add((T*)h->dx0, dx, (long long)N * d, s));
   FEMTO_TRY(S::smear_gate_bwd((const T*)h->dx0, (const T*)h->xe, h->sg, theta + h->off_lam_s, N, Tl, d, h->dpre_s,
                               h->partial, &nb, s));
@@ -449,6 +542,7 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   FEMTO_TRY(S::embed_bwd((const T*)h->dx0, (const T*)h->sh_wte, h->tok0, (const T*)h->xe, h->sg, h->dpre_s,
                          theta + h->off_smear, theta + h->off_lam_s, N, Tl, d, eps, dxn, s));
   FEMTO_TRY(scatter_rows<T>(h->plan, delta + h->off_wte, dxn, d, d, s));
+  FEMTO_TRY(join());
   if (ov) {
     FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_wte, (long long)Vp * d, s));
     FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_smear, 26, s));   // smear gate (24), lam_s, lam_y
@@ -471,8 +565,27 @@ int model_step(femto_handle* h, const float* theta, float* delta, const int* tok
     return femto_fail(FEMTO_ERR_ARG, "reduction must be FEMTO_REDUCTION_SUM or FEMTO_REDUCTION_MEAN");
   if (!h->weights_valid) return femto_fail(FEMTO_ERR_STATE, "call femto_refresh_weights before the first step");
   if (!aligned16(theta) || (delta && !aligned16(delta))) return femto_fail(FEMTO_ERR_ALIGN, "Theta/delta must be 16-byte aligned");
-  return h->bf ? step_t<bf16>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate, loss_out,
-                              nvalid_out, s, logits_out, token_losses_out, ex)
-               : step_t<float>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate,
-                               loss_out, nvalid_out, s, logits_out, token_losses_out, ex);
+  // A training step runs on the handle's own two streams, bracketed by the caller's stream on both sides; every
+  // other call (loss only, logits, a prompt) is one dependency chain and stays on the caller's stream.
+  const bool two = backward && h->hi && h->lo && !gemm_profiling();
+  cudaStream_t chain = two ? h->hi : s;
+  if (two) {
+    cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    CUDA_TRY(cudaEventRecord(e, s));
+    CUDA_TRY(cudaStreamWaitEvent(chain, e, 0));
+  }
+  const int r = h->bf ? step_t<bf16>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate,
+                                     loss_out, nvalid_out, chain, two ? h->lo : nullptr, logits_out, token_losses_out, ex)
+                      : step_t<float>(h, theta, delta, tokens, targets, positions, B, reduction, backward, accumulate,
+                                      loss_out, nvalid_out, chain, two ? h->lo : nullptr, logits_out, token_losses_out, ex);
+  if (two) {   // also after an error: whatever was queued is ordered before the caller's next work
+    cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    cudaEventRecord(e, h->lo);
+    cudaStreamWaitEvent(chain, e, 0);
+    cudaEvent_t e2 = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    cudaEventRecord(e2, chain);
+    cudaStreamWaitEvent(s, e2, 0);
+    for (bool& a : h->side_armed) a = false;
+  }
+  return r;
 }

@@ -55,6 +55,18 @@ struct femto_handle {
   int* nvalid_dev = nullptr;
   void* gemm_ws = nullptr;
   size_t gemm_ws_bytes = 0;
+  // Two internal streams for the training step: `hi` (highest priority) carries the dependency chain of the
+  // forward and reverse pass, `lo` (lowest priority) the weight-gradient GEMMs, the zero fill of delta and the
+  // AdamW tables of the update.  Nothing on the chain waits for that work within a block, so it fills the tensor
+  // pipe while the chain runs its HBM-streaming kernels.  The caller's stream is joined on both sides of a call.
+  cudaStream_t hi = nullptr, lo = nullptr;
+  static constexpr int N_FORK = 16, N_SIDE = 10;
+  cudaEvent_t ev_fork[N_FORK] = {};   // chain -> side, used round-robin (a wait keeps the record it was given)
+  int ev_next = 0;
+  cudaEvent_t ev_side[N_SIDE] = {};   // side -> chain: the last side reader of a gradient buffer has finished
+  bool side_armed[N_SIDE] = {};
+  void* gemm_ws2 = nullptr;           // split-K partials of the side stream's GEMMs
+  void *dx_b = nullptr, *dx_c = nullptr, *du_b = nullptr, *dqkv_b = nullptr, *dlogit_b = nullptr;  // rotation partners
   void* attn_ws = nullptr;
   size_t attn_ws_bytes = 0;
   struct ScatterPlan* plan = nullptr;

@@ -86,6 +86,46 @@ __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const 
   }
 }
 
+// The same on 8-byte vectors: every range of Theta starts at an even element offset (the layout only ever inserts pairs
+// of scalars between tensors), so two adjacent elements are always 8-byte aligned; four vectors per thread in flight.
+template <typename S>
+__global__ void __launch_bounds__(256) k_adamw2(float2* __restrict__ theta, const float2* __restrict__ delta,
+                                                float2* __restrict__ m, float2* __restrict__ v, long long n2, float alpha,
+                                                float b1, float b2, float eps, float lam, float c1, float c2,
+                                                float inv_nt, S* __restrict__ shadow) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n2; i0 += 4 * stride) {
+    float2 g[4], mo[4], vo[4], th[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const long long i = i0 + u * stride;
+      if (i < n2) { g[u] = delta[i]; mo[u] = m[i]; vo[u] = v[i]; th[u] = theta[i]; }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const long long i = i0 + u * stride;
+      if (i >= n2) continue;
+      const float gg[2] = {g[u].x * inv_nt, g[u].y * inv_nt};
+      const float mi[2] = {mo[u].x, mo[u].y}, vi[2] = {vo[u].x, vo[u].y}, ti[2] = {th[u].x, th[u].y};
+      float mm[2], vv[2], tn[2];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        mm[e] = b1 * mi[e] + (1.f - b1) * gg[e];
+        vv[e] = b2 * vi[e] + (1.f - b2) * gg[e] * gg[e];
+        const float t = ti[e] * (1.f - alpha * lam);
+        tn[e] = t - alpha * (mm[e] / c1) / (sqrtf(vv[e] / c2) + eps);
+      }
+      m[i] = make_float2(mm[0], mm[1]);
+      v[i] = make_float2(vv[0], vv[1]);
+      theta[i] = make_float2(tn[0], tn[1]);
+      if (shadow) {
+        if constexpr (sizeof(S) == 2) *reinterpret_cast<__nv_bfloat162*>(shadow + 2 * i) = __floats2bfloat162_rn(tn[0], tn[1]);
+        else *reinterpret_cast<float2*>(shadow + 2 * i) = make_float2(tn[0], tn[1]);
+      }
+    }
+  }
+}
+
 // Every small AdamW group (the per-block scalars, the smear gate, ...) in ONE launch: block b takes group b.
 struct SmallAdam { long long off, moff; int n; float alpha, b1, b2, eps, lam, c1, c2; };
 constexpr int SMALL_BATCH = 64;                 // groups per launch: the batch travels in the kernel's parameter space
@@ -185,6 +225,28 @@ __global__ void __launch_bounds__(256) k_scale_cols_cast(const float* __restrict
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x)
     Y[k * per + i] = from_f<T>(X[k * per + i] * fac[(long long)k * out + (int)(i % out)]);
 }
+// The same with four adjacent columns per thread (out a multiple of 4, 16-byte aligned stacks): 16-byte loads, 32-bit
+// index arithmetic inside a matrix.
+template <typename T>
+__global__ void __launch_bounds__(256) k_scale_cols_cast4(const float* __restrict__ X, const float* __restrict__ fac,
+                                                          T* __restrict__ Y, int per4, int out4) {
+  const int k = blockIdx.y;
+  const float4* x4 = reinterpret_cast<const float4*>(X) + (long long)k * per4;
+  const float4* f4 = reinterpret_cast<const float4*>(fac) + (long long)k * out4;
+  T* y = Y + (long long)k * per4 * 4;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < per4; i += gridDim.x * blockDim.x) {
+    const float4 v = x4[i], f = f4[i % out4];
+    const float r[4] = {v.x * f.x, v.y * f.y, v.z * f.z, v.w * f.w};
+    if constexpr (sizeof(T) == 2) {
+      uint2 q;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+      h[0] = __floats2bfloat162_rn(r[0], r[1]); h[1] = __floats2bfloat162_rn(r[2], r[3]);
+      *reinterpret_cast<uint2*>(y + 4ll * i) = q;
+    } else {
+      *reinterpret_cast<float4*>(y + 4ll * i) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+  }
+}
 
 // Muon+ and NorMuon factors (src/optim.jl:218-233), one block per matrix.  vec = sums of X^2 along
 // the reduced axis (length dim, each over dsize elements); v is the persistent second moment.
@@ -239,6 +301,56 @@ __global__ void __launch_bounds__(256) k_muon_update(float* __restrict__ theta, 
   }
 }
 
+// The same with two adjacent columns per thread (matrices of even width; every range of Theta starts at an even
+// element offset, so the pairs are 8-byte aligned), 32-bit index arithmetic inside a matrix.  by_col: the factor
+// belongs to the column.
+template <typename T, typename S>
+__global__ void __launch_bounds__(256) k_muon_update2(float* __restrict__ theta, const long long* __restrict__ offs,
+                                                      const T* __restrict__ X, const float* __restrict__ fac,
+                                                      int per2, int out2, int by_col, int dim, float eta, float lam,
+                                                      void* const* __restrict__ shadow, const int* __restrict__ shadow_ld) {
+  const int k = blockIdx.y;
+  float2* th = reinterpret_cast<float2*>(theta + offs[k]);
+  S* sh = shadow ? reinterpret_cast<S*>(shadow[k]) : nullptr;
+  const int sld = shadow ? shadow_ld[k] : 0;
+  const T* x = X + (long long)k * per2 * 2;
+  const float* fk = fac + (long long)k * dim;
+  const int stride = gridDim.x * blockDim.x;
+  for (int i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < per2; i0 += 4 * stride) {
+    float2 t2[4], xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int i = i0 + u * stride;
+      if (i >= per2) continue;
+      t2[u] = th[i];
+      if constexpr (sizeof(T) == 2) {
+        const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(x + 2ll * i);
+        xv[u] = make_float2(__bfloat162float(q.x), __bfloat162float(q.y));
+      } else {
+        xv[u] = *reinterpret_cast<const float2*>(x + 2ll * i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int i = i0 + u * stride;
+      if (i >= per2) continue;
+      const int row = i / out2, c2 = i % out2;
+      float2 f;
+      if (by_col) f = *reinterpret_cast<const float2*>(fk + 2 * c2);
+      else { const float q = fk[row]; f = make_float2(q, q); }
+      const float x0 = xv[u].x * f.x, x1 = xv[u].y * f.y;
+      const float r0 = t2[u].x - (eta * x0 + eta * lam * t2[u].x * ((x0 * t2[u].x) >= 0.f ? 1.f : 0.f));
+      const float r1 = t2[u].y - (eta * x1 + eta * lam * t2[u].y * ((x1 * t2[u].y) >= 0.f ? 1.f : 0.f));
+      th[i] = make_float2(r0, r1);
+      if (sh) {
+        S* dst = sh + (long long)row * sld + 2 * c2;
+        if constexpr (sizeof(S) == 2) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(r0, r1);
+        else *reinterpret_cast<float2*>(dst) = make_float2(r0, r1);
+      }
+    }
+  }
+}
+
 inline int egrid(long long n) { return (int)std::min<long long>(cdiv(n, 256), 148 * 8); }
 
 }  // namespace
@@ -248,6 +360,16 @@ static int adamw_launch_shadow(float* theta, const float* delta, float* m, float
                                float b2, float eps, float lam, int t, float n_tokens, void* shadow, bool shadow_bf16,
                                cudaStream_t s) {
   const float c1 = 1.f - powf(b1, (float)t), c2 = 1.f - powf(b2, (float)t);
+  auto al8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
+  const bool vec = (n & 1) == 0 && al8(theta) && al8(delta) && al8(m) && al8(v) && (!shadow || (reinterpret_cast<uintptr_t>(shadow) & (shadow_bf16 ? 3u : 7u)) == 0);
+  if (vec) {
+    const long long n2 = n / 2;
+    const int grid = (int)std::min<long long>(cdiv(n2, 1024), 148 * 8);
+    if (shadow_bf16) k_adamw2<bf16><<<grid, 256, 0, s>>>((float2*)theta, (const float2*)delta, (float2*)m, (float2*)v, n2, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (bf16*)shadow);
+    else k_adamw2<float><<<grid, 256, 0, s>>>((float2*)theta, (const float2*)delta, (float2*)m, (float2*)v, n2, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (float*)shadow);
+    KERNEL_CHECK();
+    return 0;
+  }
   if (shadow_bf16) k_adamw<bf16><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (bf16*)shadow);
   else k_adamw<float><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (float*)shadow);
   KERNEL_CHECK();
@@ -392,7 +514,11 @@ template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& 
   KERNEL_CHECK();
   k_muoneq_factors<<<k, 256, 0, s>>>(o->vec, out, o->fac);
   KERNEL_CHECK();
-  k_scale_cols_cast<T><<<eg, 256, 0, s>>>(o->X, o->fac, (T*)o->Xa, per, out);
+  if ((out & 3) == 0 && per / 4 < (1ll << 30)) {
+    k_scale_cols_cast4<T><<<dim3((unsigned)std::min<long long>(cdiv(per / 4, 256), 148 * 8), k), 256, 0, s>>>(o->X, o->fac, (T*)o->Xa, (int)(per / 4), out / 4);
+  } else {
+    k_scale_cols_cast<T><<<eg, 256, 0, s>>>(o->X, o->fac, (T*)o->Xa, per, out);
+  }
   KERNEL_CHECK();
   FEMTO_TRY(newton_schulz_t<T>((T*)o->Xa, (T*)o->Xb, (T*)o->A, (T*)o->B2, k, in, out, o->cfg.ns_coeffs,
                                o->cfg.ns_steps, h->gemm_ws, h->gemm_ws_bytes, h->status, s));
@@ -407,8 +533,18 @@ template <typename T> static int muon_group_step(femto_optimizer* o, MuonGroup& 
   const float eta = alpha * sqrtf(std::max(1.f, (float)out / (float)in));
   void* const* sh = g.d_shadow ? g.d_shadow + g.k0 : nullptr;
   const int* shld = g.d_shadow_ld ? g.d_shadow_ld + g.k0 : nullptr;
-  if (h->bf) k_muon_update<T, bf16><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam, sh, shld);
-  else k_muon_update<T, float><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam, sh, shld);
+  bool pairs = (out & 1) == 0 && per / 2 < (1ll << 30) && (reinterpret_cast<uintptr_t>(theta) & 7u) == 0;
+  for (int i = g.k0; i < g.k1 && pairs; i++)
+    pairs = (g.offs[i] & 1) == 0 && (g.shadow_ld[i] & 1) == 0 && (reinterpret_cast<uintptr_t>(g.shadow[i]) & (h->bf ? 3u : 7u)) == 0;
+  if (pairs) {
+    dim3 eg2((unsigned)std::min<long long>(cdiv(per / 2, 1024), 148 * 8), k);
+    if (h->bf) k_muon_update2<T, bf16><<<eg2, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, (int)(per / 2), out / 2, by_col ? 1 : 0, dim, eta, lam, sh, shld);
+    else k_muon_update2<T, float><<<eg2, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, (int)(per / 2), out / 2, by_col ? 1 : 0, dim, eta, lam, sh, shld);
+  } else if (h->bf) {
+    k_muon_update<T, bf16><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam, sh, shld);
+  } else {
+    k_muon_update<T, float><<<eg, 256, 0, s>>>(theta, d_offs, (const T*)o->Xa, o->fac, per, out, by_col ? 1 : 0, dim, eta, lam, sh, shld);
+  }
   KERNEL_CHECK();
   return 0;
 }
@@ -608,11 +744,20 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
   const bool sharded = o->shard_world > 1;
   femto_handle* h = o->h;
   const size_t es_model = h->bf ? 2 : 4;
+  // The AdamW tables are pure HBM streaming and touch nothing the Muon groups touch: on the handle's low-priority
+  // stream they run under the Polar Express GEMMs of the Muon groups instead of before them.
+  cudaStream_t sa = s;
+  if (h->lo && !gemm_profiling()) {
+    cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    CUDA_TRY(cudaEventRecord(e, s));
+    CUDA_TRY(cudaStreamWaitEvent(h->lo, e, 0));
+    sa = h->lo;
+  }
   SmallBatch batch;
   int nsmall = 0;
   auto flush_small = [&]() -> int {
     if (nsmall == 0) return 0;
-    k_adamw_small<<<nsmall, 128, 0, s>>>(theta, delta, o->adam_m, o->adam_v, batch, 1.f / n_tokens);
+    k_adamw_small<<<nsmall, 128, 0, sa>>>(theta, delta, o->adam_m, o->adam_v, batch, 1.f / n_tokens);
     KERNEL_CHECK();
     nsmall = 0;
     return 0;
@@ -631,16 +776,22 @@ int optimizer_step(femto_optimizer* o, float* theta, const float* delta, float e
     const long long n = g.shard ? g.n / o->shard_world : g.n, o0 = g.shard ? n * o->shard_rank : 0;
     void* shadow = g.shadow ? reinterpret_cast<char*>(g.shadow) + es_model * (size_t)o0 : nullptr;
     FEMTO_TRY(adamw_launch_shadow(theta + g.off + o0, delta + g.off + o0, o->adam_m + g.moff + o0, o->adam_v + g.moff + o0, n,
-                                  eta * g.alpha, g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, shadow, h->bf, s));
+                                  eta * g.alpha, g.b1, g.b2, g.eps, g.lam, g.t, n_tokens, shadow, h->bf, sa));
   }
   FEMTO_TRY(flush_small());
+  int rc = 0;
   for (auto& g : o->muon) {  // src/optim.jl:434-438
     const float m_ = has_mu ? mu : g.mu, l_ = has_lambda ? lambda : g.lam;
-    if (o->cfg.compute_dtype == FEMTO_BF16)
-      FEMTO_TRY(muon_group_step<bf16>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s));
-    else
-      FEMTO_TRY(muon_group_step<float>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s));
+    if (o->cfg.compute_dtype == FEMTO_BF16) rc = muon_group_step<bf16>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s);
+    else rc = muon_group_step<float>(o, g, theta, delta, eta * g.alpha, m_, l_, n_tokens, s);
+    if (rc) break;
   }
+  if (sa != s) {   // join, also after an error
+    cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
+    cudaEventRecord(e, sa);
+    cudaStreamWaitEvent(s, e, 0);
+  }
+  if (rc) return rc;
   // every rank now holds the new values of the ranges it owns; fetch the others' (a handle without a
   // communicator skips this: the caller merges the ranges itself, as the single-GPU emulation test does)
   if (sharded && o->h->dp && o->exchange_mode == 1) {

@@ -503,11 +503,11 @@ __global__ void __launch_bounds__(256) k_norm_bwd_resid(const T* __restrict__ dy
   }
 }
 
-// dxm = dx + normbwd(dxn; xn1, r1); partial sums of dxm*xin and dxm*x0; dx <- lam_b*dxm;
+// dxm = dx_in + normbwd(dxn; xn1, r1); partial sums of dxm*xin and dxm*x0; dx <- lam_b*dxm (dx may be dx_in);
 // dx0 (+)= lam_x0*dxm.  Rows are assigned to warps in a fixed pattern so the partials are
 // reproducible.
 template <typename T, int V>
-__global__ void __launch_bounds__(256) k_mix_bwd(T* __restrict__ dx, const T* __restrict__ dxn,
+__global__ void __launch_bounds__(256) k_mix_bwd(const T* dx_in, T* dx, const T* __restrict__ dxn,
                                                  const T* __restrict__ xn1, const float* __restrict__ r1,
                                                  const T* __restrict__ xin, const T* __restrict__ x0,
                                                  const float* __restrict__ lam_b, const float* __restrict__ lam_x0,
@@ -534,7 +534,7 @@ __global__ void __launch_bounds__(256) k_mix_bwd(T* __restrict__ dx, const T* __
       float f[V], g[V], q[V], xi[V], xz[V], z[V];
       load_vec<T, V>(a + c, f);
       load_vec<T, V>(b + c, g);
-      load_vec<T, V>(dx + row * D + c, q);
+      load_vec<T, V>(dx_in + row * D + c, q);
       load_vec<T, V>(xin + row * D + c, xi);
       load_vec<T, V>(x0 + row * D + c, xz);
       if (!first) load_vec<T, V>(dx0 + row * D + c, z);
@@ -938,11 +938,11 @@ int Stream<T>::norm_bwd_resid(const T* dy, const T* y, const float* r, const T* 
   return 0;
 }
 template <typename T>
-int Stream<T>::mix_bwd(T* dx, const T* dxn, const T* xn1, const float* r1, const T* xin, const T* x0,
+int Stream<T>::mix_bwd(const T* dx_in, T* dx, const T* dxn, const T* xn1, const float* r1, const T* xin, const T* x0,
                        const float* lam_b, const float* lam_x0, T* dx0, bool first, int N, int D, float* partial,
                        int* nblocks_out, cudaStream_t s) {
   int nb = red_grid(N);
-  DISPATCH_V(D % VecN<T>::n == 0, k_mix_bwd<T, V><<<nb, 256, 0, s>>>(dx, dxn, xn1, r1, xin, x0, lam_b, lam_x0, dx0,
+  DISPATCH_V(D % VecN<T>::n == 0, k_mix_bwd<T, V><<<nb, 256, 0, s>>>(dx_in, dx, dxn, xn1, r1, xin, x0, lam_b, lam_x0, dx0,
                                                                     first ? 1 : 0, N, D, partial);)
   KERNEL_CHECK();
   *nblocks_out = nb;

@@ -23,7 +23,7 @@ template <typename T> struct Stream {
                          float* partial, int* nblocks_out, cudaStream_t s);
   static int norm_bwd_resid(const T* dy, const T* y, const float* r, const T* resid, T* out, int N, int D,
                             cudaStream_t s);
-  static int mix_bwd(T* dx, const T* dxn, const T* xn1, const float* r1, const T* xin, const T* x0,
+  static int mix_bwd(const T* dx_in, T* dx, const T* dxn, const T* xn1, const float* r1, const T* xin, const T* x0,
                      const float* lam_b, const float* lam_x0, T* dx0, bool first, int N, int D, float* partial,
                      int* nblocks_out, cudaStream_t s);
   static int backout_norm(const T* xl, const T* xb, const float* lam_y, T* xf_scratch, T* xnf, float* rf, int N,

@@ -12,42 +12,55 @@
 template <typename T> int xent_tail(const XentArgs& x, cudaStream_t s) {
   const int N = x.N, d = x.D, V = x.V;
   const long long ld = x.ldw;
-  for (int c0 = 0; c0 < N; c0 += x.chunk) {
+  const bool two = x.backward && x.side && x.ws2 && x.dlogit2 && x.ev_read[0] && x.ev_read[1] && x.ev_fork[0] && x.ev_fork[1];
+  bool armed[2] = {false, false};
+  int ci = 0;
+  for (int c0 = 0; c0 < N; c0 += x.chunk, ci++) {
     const int cn = std::min(x.chunk, N - c0);
     const T* xc = (const T*)x.x + (size_t)c0 * d;
+    void* dlogit = (two && (ci & 1)) ? x.dlogit2 : x.dlogit;
+    // the chunk two back handed this buffer to the side stream's weight-gradient GEMM: wait for that reader
+    if (two && armed[ci & 1]) { CUDA_TRY(cudaStreamWaitEvent(s, x.ev_read[ci & 1], 0)); armed[ci & 1] = false; }
     GemmArgs g;
-    g.ws = x.ws; g.ws_bytes = x.ws_bytes; g.status = x.status;
+    g.ws = x.ws; g.ws_bytes = x.ws_bytes; g.status = x.status; g.ring = two ? 5 : 0;
     g.A = xc; g.lda = d; g.B = x.W; g.ldb = ld; g.b_kmajor = false; g.M = cn; g.N = V; g.K = d;
     g.targets0 = x.targets0 + c0; g.vocab = V;
     g.epi = EPI_XENT_STATS; g.stats = x.stats; g.tz = x.tz + c0;
     // reverse pass: the statistics GEMM also keeps the chunk's logits in bf16 (as the reference materialises
     // them) and a streaming pass turns them into d loss/d logit in place
-    if (x.backward) { g.C = x.dlogit; g.ldc = ld; }
+    if (x.backward) { g.C = dlogit; g.ldc = ld; }
     const bool tc = sizeof(T) == 2 && gemm_tc_supported(g);
     if (tc) {
       FEMTO_TRY(gemm_tc_bf16(g, s));
       FEMTO_TRY(xent_finalize(x.stats, 2 * ((V + 255) / 256), x.tz + c0, x.targets0 + c0, cn, x.lse_rows + c0,
                               x.loss_rows + c0, s));
       if (x.backward)
-        FEMTO_TRY(xent_dlogit_inplace(x.dlogit, ld, x.lse_rows + c0, x.targets0 + c0, cn, V, x.scale, x.scale_dev, s));
+        FEMTO_TRY(xent_dlogit_inplace(dlogit, ld, x.lse_rows + c0, x.targets0 + c0, cn, V, x.scale, x.scale_dev, s));
     } else {
       if (!x.logits_f32) return femto_fail(FEMTO_ERR_UNSUPPORTED, "lm_head tail: no fp32 logits workspace for this shape");
       g.epi = EPI_F32; g.beta = 0.f; g.C = x.logits_f32; g.ldc = ld;
       FEMTO_TRY(gemm<T>(g, s));
-      FEMTO_TRY(Stream<T>::xent_rows(x.logits_f32, ld, x.targets0 + c0, cn, V, x.scale, x.scale_dev, (T*)x.dlogit, ld,
+      FEMTO_TRY(Stream<T>::xent_rows(x.logits_f32, ld, x.targets0 + c0, cn, V, x.scale, x.scale_dev, (T*)dlogit, ld,
                                      x.loss_rows + c0, s));
     }
     if (x.backward) {
+      cudaStream_t sw = s;
+      if (two) {   // the side stream may start once d loss/d logit of this chunk is complete
+        CUDA_TRY(cudaEventRecord(x.ev_fork[ci & 1], s));
+        CUDA_TRY(cudaStreamWaitEvent(x.side, x.ev_fork[ci & 1], 0));
+        sw = x.side;
+      }
       GemmArgs gx;  // dx[cn][d] = dlogit[cn][V] * W[d][V]^T
-      gx.ws = x.ws; gx.ws_bytes = x.ws_bytes; gx.status = x.status;
-      gx.A = x.dlogit; gx.lda = ld; gx.B = x.W; gx.ldb = ld; gx.b_kmajor = true; gx.C = (T*)x.dx + (size_t)c0 * d;
+      gx.ws = x.ws; gx.ws_bytes = x.ws_bytes; gx.status = x.status; gx.ring = two ? 5 : 0;
+      gx.A = dlogit; gx.lda = ld; gx.B = x.W; gx.ldb = ld; gx.b_kmajor = true; gx.C = (T*)x.dx + (size_t)c0 * d;
       gx.ldc = d; gx.M = cn; gx.N = d; gx.K = V;
       FEMTO_TRY(gemm<T>(gx, s));
-      GemmArgs gw;  // dW[d][ld] += x[cn][d]^T * dlogit[cn][V]
-      gw.ws = x.ws; gw.ws_bytes = x.ws_bytes; gw.status = x.status;
-      gw.A = xc; gw.lda = d; gw.a_kmajor = false; gw.B = x.dlogit; gw.ldb = ld; gw.b_kmajor = false;
+      GemmArgs gw;  // dW[d][ld] += x[cn][d]^T * dlogit[cn][V]   (the chunks' sums stay in order: one stream)
+      gw.ws = two ? x.ws2 : x.ws; gw.ws_bytes = x.ws_bytes; gw.status = x.status; gw.ring = two ? 5 : 0;
+      gw.A = xc; gw.lda = d; gw.a_kmajor = false; gw.B = dlogit; gw.ldb = ld; gw.b_kmajor = false;
       gw.C = x.dw; gw.ldc = ld; gw.M = d; gw.N = V; gw.K = cn; gw.epi = EPI_F32; gw.beta = 1.f;
-      FEMTO_TRY(gemm<T>(gw, s));
+      FEMTO_TRY(gemm<T>(gw, sw));
+      if (two) { CUDA_TRY(cudaEventRecord(x.ev_read[ci & 1], x.side)); armed[ci & 1] = true; }
     }
   }
   return 0;
