@@ -86,46 +86,6 @@ __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const 
   }
 }
 
-// The same on 8-byte vectors: every range of Theta starts at an even element offset (the layout only ever inserts pairs
-// of scalars between tensors), so two adjacent elements are always 8-byte aligned; four vectors per thread in flight.
-template <typename S>
-__global__ void __launch_bounds__(256) k_adamw2(float2* __restrict__ theta, const float2* __restrict__ delta,
-                                                float2* __restrict__ m, float2* __restrict__ v, long long n2, float alpha,
-                                                float b1, float b2, float eps, float lam, float c1, float c2,
-                                                float inv_nt, S* __restrict__ shadow) {
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n2; i0 += 4 * stride) {
-    float2 g[4], mo[4], vo[4], th[4];
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-      const long long i = i0 + u * stride;
-      if (i < n2) { g[u] = delta[i]; mo[u] = m[i]; vo[u] = v[i]; th[u] = theta[i]; }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-      const long long i = i0 + u * stride;
-      if (i >= n2) continue;
-      const float gg[2] = {g[u].x * inv_nt, g[u].y * inv_nt};
-      const float mi[2] = {mo[u].x, mo[u].y}, vi[2] = {vo[u].x, vo[u].y}, ti[2] = {th[u].x, th[u].y};
-      float mm[2], vv[2], tn[2];
-#pragma unroll
-      for (int e = 0; e < 2; e++) {
-        mm[e] = b1 * mi[e] + (1.f - b1) * gg[e];
-        vv[e] = b2 * vi[e] + (1.f - b2) * gg[e] * gg[e];
-        const float t = ti[e] * (1.f - alpha * lam);
-        tn[e] = t - alpha * (mm[e] / c1) / (sqrtf(vv[e] / c2) + eps);
-      }
-      m[i] = make_float2(mm[0], mm[1]);
-      v[i] = make_float2(vv[0], vv[1]);
-      theta[i] = make_float2(tn[0], tn[1]);
-      if (shadow) {
-        if constexpr (sizeof(S) == 2) *reinterpret_cast<__nv_bfloat162*>(shadow + 2 * i) = __floats2bfloat162_rn(tn[0], tn[1]);
-        else *reinterpret_cast<float2*>(shadow + 2 * i) = make_float2(tn[0], tn[1]);
-      }
-    }
-  }
-}
-
 // Every small AdamW group (the per-block scalars, the smear gate, ...) in ONE launch: block b takes group b.
 struct SmallAdam { long long off, moff; int n; float alpha, b1, b2, eps, lam, c1, c2; };
 constexpr int SMALL_BATCH = 64;                 // groups per launch: the batch travels in the kernel's parameter space
@@ -360,16 +320,6 @@ static int adamw_launch_shadow(float* theta, const float* delta, float* m, float
                                float b2, float eps, float lam, int t, float n_tokens, void* shadow, bool shadow_bf16,
                                cudaStream_t s) {
   const float c1 = 1.f - powf(b1, (float)t), c2 = 1.f - powf(b2, (float)t);
-  auto al8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
-  const bool vec = (n & 1) == 0 && al8(theta) && al8(delta) && al8(m) && al8(v) && (!shadow || (reinterpret_cast<uintptr_t>(shadow) & (shadow_bf16 ? 3u : 7u)) == 0);
-  if (vec) {
-    const long long n2 = n / 2;
-    const int grid = (int)std::min<long long>(cdiv(n2, 1024), 148 * 8);
-    if (shadow_bf16) k_adamw2<bf16><<<grid, 256, 0, s>>>((float2*)theta, (const float2*)delta, (float2*)m, (float2*)v, n2, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (bf16*)shadow);
-    else k_adamw2<float><<<grid, 256, 0, s>>>((float2*)theta, (const float2*)delta, (float2*)m, (float2*)v, n2, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (float*)shadow);
-    KERNEL_CHECK();
-    return 0;
-  }
   if (shadow_bf16) k_adamw<bf16><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (bf16*)shadow);
   else k_adamw<float><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (float*)shadow);
   KERNEL_CHECK();
