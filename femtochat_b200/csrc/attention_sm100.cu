@@ -630,6 +630,417 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA in ping-pong.  In the kernels above the two threads of a query row work on the same S
+// tile, meet at a barrier to exchange their maxima and therefore run their phases in lockstep: while they load S and
+// take the maximum the special-function unit idles, while they evaluate 2^x nothing else of theirs can run, and the
+// tensor pipe waits for P.  Here one CTA owns TWO 128-query tiles X = A, B that read the same keys and values: the two
+// query heads of one key/value head at the same positions (grouped-query attention with an even group), or two
+// adjacent query tiles of one head.  Tensor memory holds S_A, S_B (P overwrites S in place as bf16) and O_A, O_B,
+// 128 columns each.  One thread owns one query row (no exchange between threads, no barrier per tile) in one of two
+// softmax warpgroups, and one thread issues every product in the order
+//     S_A(0) S_B(0)   { O_A += P_A(j) V(j);  S_A(j+1);  O_B += P_B(j) V(j);  S_B(j+1) }  j = 0, 1, ...
+// so that the softmax of one tile runs while the tensor pipe works for the other, and every K / V tile is loaded once
+// for both.  A thread reads its row of S twice from tensor memory (maximum, then exponentials; 64 columns at a time)
+// instead of holding 128 values in registers.  Persistent: one CTA per SM walks the items, heaviest first.
+constexpr int PP_SMEM = TILE_BYTES * 6 + 1024 + 512;
+
+struct PairItem {
+  int qt[2], h[2], b, kvh;
+  bool valid_b;
+};
+__device__ __forceinline__ PairItem pp_item(const AttnArgs& a, int item, int nqt, bool gqa) {
+  PairItem it;
+  if (gqa) {   // heads 2g and 2g+1 of one key/value head, same query tile
+    const int per = (a.H / 2) * a.B;
+    const int qt = nqt - 1 - item / per, rem = item % per;
+    const int hp = rem % (a.H / 2);
+    it.b = rem / (a.H / 2);
+    it.qt[0] = it.qt[1] = qt;
+    it.h[0] = 2 * hp; it.h[1] = 2 * hp + 1;
+    it.valid_b = true;
+  } else {     // query tiles 2p and 2p+1 of one head
+    const int per = a.H * a.B;
+    const int qp = (nqt + 1) / 2 - 1 - item / per, rem = item % per;
+    it.b = rem / a.H;
+    it.h[0] = it.h[1] = rem % a.H;
+    it.qt[0] = 2 * qp; it.qt[1] = 2 * qp + 1;
+    it.valid_b = it.qt[1] < nqt;
+  }
+  it.kvh = it.h[0] / (a.H / a.Hkv);
+  return it;
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems, const int gqa) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                    // Q_A, Q_B
+  uint8_t* sK = smem + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* sV = smem + 4 * TILE_BYTES;   // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* q_full = bars;          // both Q tiles and the item's key ranges are in place
+  uint64_t* q_free = bars + 1;      // the item's last S has been executed and every softmax warp has read the ranges
+  uint64_t* k_full = bars + 2;      // [2]
+  uint64_t* v_full = bars + 4;      // [2]
+  uint64_t* k_free = bars + 6;      // [2] both S products of the stage's tile have been executed
+  uint64_t* v_free = bars + 8;      // [2] both P V products of the stage's tile have been executed
+  uint64_t* s_full = bars + 10;     // [2: A, B]
+  uint64_t* p_ready = bars + 12;    // [2: A, B]
+  uint64_t* pv_done = bars + 14;    // [2: A, B]
+  uint64_t* o_free = bars + 16;     // [2: A, B] the warpgroup has read the item's O out of tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* rng = reinterpret_cast<volatile int*>(tmem_slot + 2);   // jlo_A, jhi_A, jlo_B, jhi_B of the item in sQ
+
+  const AttnArgs& a = p.a;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqt = a.T / BQ;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1); mbar_init(q_free, 1 + 8);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_free[i], 1); mbar_init(&v_free[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 4); mbar_init(&pv_done[i], 1); mbar_init(&o_free[i], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Every role walks the same items in the same order.  n = items of this CTA so far (phase n & 1 of q_full / q_free);
+  // tu = key tiles loaded so far (K / V stage tu & 1, phase (tu >> 1) & 1); tcX = key tiles tile X has processed so
+  // far (phase tcX & 1 of s_full / p_ready / pv_done [X]); nX = items in which X had any key tile (o_free[X]).
+  if (warp < 4) {
+  if (warp == 0) {
+    // ---------------- TMA producer (whole warp: the document starts of a query tile are reduced by the 32 lanes) ----------------
+    int tu = 0;
+    bool ok = true;
+    for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
+      const PairItem it = pp_item(a, item, nqt, gqa != 0);
+      const long long row0 = (long long)it.b * a.T;
+      int jlo[2], jhi[2];
+#pragma unroll
+      for (int X = 0; X < 2; X++) {
+        const int q0 = it.qt[X] * BQ;
+        jhi[X] = it.qt[X];
+        jlo[X] = max(0, q0 - a.window_left) / BKV;
+        if (a.doc_start && (X == 0 || it.valid_b)) {
+          // key tiles that lie before the earliest document start of these 128 queries are fully masked
+          const int4 v = *reinterpret_cast<const int4*>(a.doc_start + row0 + q0 + lane * 4);
+          const int mn = __reduce_min_sync(0xffffffffu, min(min(v.x, v.y), min(v.z, v.w)));
+          jlo[X] = max(jlo[X], mn / BKV);
+        }
+      }
+      if (!it.valid_b) { jlo[1] = 1; jhi[1] = 0; }
+      const int jmin = it.valid_b ? min(jlo[0], jlo[1]) : jlo[0];
+      const int jmax = it.valid_b ? max(jhi[0], jhi[1]) : jhi[0];
+      const int nu = jmax - jmin + 1;
+      if (lane == 0) {
+        if (n >= 1 && !mbar_wait(q_free, (n - 1) & 1, abort_flag, a.status)) ok = false;
+        if (ok) {
+          rng[0] = jlo[0]; rng[1] = jhi[0]; rng[2] = jlo[1]; rng[3] = jhi[1];
+          mbar_expect_tx(q_full, it.valid_b ? 2 * TILE_BYTES : TILE_BYTES);   // the arrive publishes rng
+#pragma unroll
+          for (int X = 0; X < 2; X++) {
+            if (X == 1 && !it.valid_b) break;
+            const int qrow = (int)(row0 + it.qt[X] * BQ);
+            tma_load_2d(sQ + X * TILE_BYTES, &tmQ, q_full, p.q_col0 + it.h[X] * HD, qrow);
+            tma_load_2d(sQ + X * TILE_BYTES + TILE_BYTES / 2, &tmQ, q_full, p.q_col0 + it.h[X] * HD + 64, qrow);
+          }
+          for (int u = 0; u < nu; u++, tu++) {
+            const int st = tu & 1;
+            const uint32_t ph2 = ((tu - 2) >> 1) & 1;   // phase of tile tu-2, the previous user of this stage
+            const int krow = (int)(row0 + (jmin + u) * BKV);
+            if (tu >= 2 && !mbar_wait(&k_free[st], ph2, abort_flag, a.status)) { ok = false; break; }
+            mbar_expect_tx(&k_full[st], TILE_BYTES);
+            tma_load_2d(sK + st * TILE_BYTES, &tmK, &k_full[st], p.k_col0 + it.kvh * HD, krow);
+            tma_load_2d(sK + st * TILE_BYTES + TILE_BYTES / 2, &tmK, &k_full[st], p.k_col0 + it.kvh * HD + 64, krow);
+            if (tu >= 2 && !mbar_wait(&v_free[st], ph2, abort_flag, a.status)) { ok = false; break; }
+            mbar_expect_tx(&v_full[st], TILE_BYTES);
+            tma_load_2d(sV + st * TILE_BYTES, &tmV, &v_full[st], p.v_col0 + it.kvh * HD, krow);
+            tma_load_2d(sV + st * TILE_BYTES + TILE_BYTES / 2, &tmV, &v_full[st], p.v_col0 + it.kvh * HD + 64, krow);
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      tu = __shfl_sync(0xffffffffu, tu, 0);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- the one issuer of every product ----------------
+      constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // both operands K-major
+      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // V is N-contiguous
+      int tu = 0, tcx[2] = {0, 0}, nx[2] = {0, 0};
+      bool ok = true;
+      for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
+        if (!mbar_wait(q_full, n & 1, abort_flag, a.status)) break;
+        const int jlo[2] = {rng[0], rng[2]}, jhi[2] = {rng[1], rng[3]};
+        const bool has[2] = {jlo[0] <= jhi[0], jlo[1] <= jhi[1]};
+        const int jmin = has[1] ? min(jlo[0], jlo[1]) : jlo[0];
+        const int jmax = has[1] ? max(jhi[0], jhi[1]) : jhi[0];
+        const int nu = jmax - jmin + 1;
+        auto in = [&](int X, int u) { const int j = jmin + u; return j >= jlo[X] && j <= jhi[X]; };
+        auto issue_s = [&](int X, int st) {
+          const uint32_t q_addr = smem_u32(sQ + X * TILE_BYTES), k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < HD / 16; k++) {
+            const uint32_t off = (k >> 2) * (TILE_BYTES / 2) + (k & 3) * 32;
+            mma_ss(tmem_base + X * 128, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0);
+          }
+          tc_commit(&s_full[X]);
+        };
+        bool first[2] = {true, true};   // X's next P V is the first of the item: it overwrites O_X
+        // first key tile of the item
+        if (!mbar_wait(&k_full[tu & 1], (tu >> 1) & 1, abort_flag, a.status)) break;
+        tc_fence_after();
+        if (in(0, 0)) issue_s(0, tu & 1);
+        if (in(1, 0)) issue_s(1, tu & 1);
+        tc_commit(&k_free[tu & 1]);
+        if (nu == 1) tc_commit(q_free);
+        for (int u = 0; u < nu && ok; u++) {
+          const int st = (tu + u) & 1, st1 = (tu + u + 1) & 1;
+          const uint32_t ph = ((tu + u) >> 1) & 1, ph1 = ((tu + u + 1) >> 1) & 1;
+          bool v_seen = false, k_seen = false;
+#pragma unroll
+          for (int X = 0; X < 2; X++) {
+            if (in(X, u)) {
+              if (!mbar_wait(&p_ready[X], tcx[X] & 1, abort_flag, a.status)) { ok = false; break; }
+              if (!v_seen && !mbar_wait(&v_full[st], ph, abort_flag, a.status)) { ok = false; break; }
+              v_seen = true;
+              // O_X still holds the previous item's result until its warpgroup has read it
+              if (first[X] && nx[X] >= 1 && !mbar_wait(&o_free[X], (nx[X] - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+              for (int k = 0; k < BKV / 16; k++)
+                mma_ts(tmem_base + 256 + X * 128, tmem_base + X * 128 + k * 8, smem_desc_sw128(v_addr + k * 2048, TILE_BYTES / 2, 1024),
+                       idesc_o, (!first[X] || k > 0) ? 1u : 0u);
+              tc_commit(&pv_done[X]);
+              first[X] = false;
+              tcx[X]++;
+            }
+            if (X == 1) tc_commit(&v_free[st]);
+            if (u + 1 < nu) {
+              if (in(X, u + 1)) {
+                if (!k_seen && !mbar_wait(&k_full[st1], ph1, abort_flag, a.status)) { ok = false; break; }
+                k_seen = true;
+                tc_fence_after();
+                issue_s(X, st1);
+              }
+              if (X == 1) {
+                tc_commit(&k_free[st1]);
+                if (u + 1 == nu - 1) tc_commit(q_free);   // the item's last S: Q may be replaced once it has been executed
+              }
+            }
+          }
+        }
+        tu += nu;
+        if (has[0]) nx[0]++;
+        if (has[1]) nx[1]++;
+      }
+    }
+  }
+  } else {
+    // ---------------- softmax warpgroups: X = 0 (warps 4-7) and 1 (warps 8-11), one thread per query row ----------------
+    const int X = (warp - 4) >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const uint32_t tS = tmem_base + X * 128 + lane_off, tO = tmem_base + 256 + X * 128 + lane_off;
+    const float c = rsqrtf((float)HD) * LOG2E;
+    const uint64_t c2 = pack2(c, c);
+    int tc = 0, nX = 0;
+    bool ok = true;
+    for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
+      const PairItem it = pp_item(a, item, nqt, gqa != 0);
+      if (!mbar_wait(q_full, n & 1, abort_flag, a.status)) break;
+      const int jlo = rng[2 * X], jhi = rng[2 * X + 1];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_free);
+      if (jlo > jhi) continue;
+      const int q = it.qt[X] * BQ + r, h = it.h[X];
+      const long long row0 = (long long)it.b * a.T;
+      int lo = max(0, q - a.window_left);
+      if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = jlo; j <= jhi; j++, tc++) {
+        const int k0 = j * BKV;
+        if (!mbar_wait(&s_full[X], tc & 1, abort_flag, a.status)) { ok = false; break; }
+        tc_fence_after();
+        // Masks.  The keys this row may see in the tile are the columns ca..cb.  Per group of 32 columns the warp
+        // decides together: every lane sees all of it (no work), no lane sees any of it (P = 0, no exponentials), or
+        // mixed (element-wise select).  On a diagonal tile one group of four is mixed and those right of it are empty.
+        const int ca = max(lo - k0, 0), cb = min(q - k0, BKV - 1);
+        const bool any_mask = __any_sync(0xffffffffu, ca > 0 || cb < BKV - 1);
+        unsigned empty = 0, mixed = 0;   // bit g: no lane of the warp sees a key of group g / some do, some do not
+        if (any_mask) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const bool all_in = __all_sync(0xffffffffu, ca <= g * 32 && cb >= g * 32 + 31);
+            const bool none_in = __all_sync(0xffffffffu, cb < g * 32 || ca > g * 32 + 31);
+            if (none_in) empty |= 1u << g;
+            else if (!all_in) mixed |= 1u << g;
+          }
+        }
+        // ---- pass 1: the row maximum (three-input maxima, four chains), 64 columns at a time ----
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          if (((empty >> (2 * hf)) & 3u) == 3u) continue;
+          float x[64];
+          tmem_ld32(tS + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+          tmem_ld32(tS + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+          tmem_ld_wait();
+#pragma unroll
+          for (int gg = 0; gg < 2; gg++) {
+            const int g = 2 * hf + gg;
+            if (empty & (1u << g)) continue;
+            if (mixed & (1u << g)) {
+#pragma unroll
+              for (int e = 0; e < 32; e++) x[gg * 32 + e] = (g * 32 + e >= ca && g * 32 + e <= cb) ? x[gg * 32 + e] : -INFINITY;
+            }
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              mx[0] = max3(mx[0], x[gg * 32 + e], x[gg * 32 + e + 1]); mx[1] = max3(mx[1], x[gg * 32 + e + 2], x[gg * 32 + e + 3]);
+              mx[2] = max3(mx[2], x[gg * 32 + e + 4], x[gg * 32 + e + 5]); mx[3] = max3(mx[3], x[gg * 32 + e + 6], x[gg * 32 + e + 7]);
+            }
+          }
+        }
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;
+        const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_used, mt);
+          const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+          l *= alpha;
+          m_used = m_new;
+          if (j > jlo) {
+            // O_X is being accumulated by the tensor core: wait for the previous tile's P V, then rescale the row
+            if (!mbar_wait(&pv_done[X], (tc - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              uint32_t rr[32];
+              tmem_ld32(tO + u * 32, rr);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; e++) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
+              tmem_st32(tO + u * 32, rr);
+            }
+            tmem_st_wait();
+          }
+        }
+        // ---- pass 2: P = 2^(c S - m) as bf16 over S, and the row sum; two elements per fma / add ----
+        const float mm = (m_used == -INFINITY) ? 0.f : m_used;
+        const uint64_t nm2 = pack2(-mm, -mm);
+        uint64_t sm2[2] = {0ull, 0ull};   // (+0, +0)
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          float x[64];
+          if (((empty >> (2 * hf)) & 3u) != 3u) {
+            tmem_ld32(tS + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+            tmem_ld32(tS + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+            tmem_ld_wait();
+          }
+#pragma unroll
+          for (int gg = 0; gg < 2; gg++) {
+            const int g = 2 * hf + gg;
+            uint32_t pk[16];
+            if (empty & (1u << g)) {
+#pragma unroll
+              for (int e = 0; e < 16; e++) pk[e] = 0u;
+            } else {
+              if (mixed & (1u << g)) {
+#pragma unroll
+                for (int e = 0; e < 32; e++) x[gg * 32 + e] = (g * 32 + e >= ca && g * 32 + e <= cb) ? x[gg * 32 + e] : -INFINITY;
+              }
+#pragma unroll
+              for (int e = 0; e < 16; e += 2) {
+                const int i0 = gg * 32 + 2 * e;
+                float t0, t1, t2, t3;
+                unpack2(fma2(pack2(x[i0], x[i0 + 1]), c2, nm2), t0, t1);
+                unpack2(fma2(pack2(x[i0 + 2], x[i0 + 3]), c2, nm2), t2, t3);
+                const float p0 = fast_exp2(t0), p1 = fast_exp2(t1), p2 = fast_exp2(t2), p3 = fast_exp2(t3);
+                sm2[0] = add2(sm2[0], pack2(p0, p1));
+                sm2[1] = add2(sm2[1], pack2(p2, p3));
+                pk[e] = pack_bf16(p0, p1);
+                pk[e + 1] = pack_bf16(p2, p3);
+              }
+            }
+            // keys g*32 .. g*32+31 as bf16: 16 columns starting at column g*16.  They overwrite S columns that this
+            // thread has already loaded (first half) or no longer needs.
+            tmem_st16(tS + g * 16, pk);
+          }
+        }
+        {
+          float s0, s1, s2, s3;
+          unpack2(sm2[0], s0, s1);
+          unpack2(sm2[1], s2, s3);
+          l += (s0 + s1) + (s2 + s3);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[X]);
+      }
+      if (!ok) break;
+      // ---- the item's O: out of tensor memory (then the next item's P V may start), scaled, to global memory ----
+      if (!mbar_wait(&pv_done[X], (tc - 1) & 1, abort_flag, a.status)) break;
+      tc_fence_after();
+      {
+        const float inv = 1.f / l;
+        bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          uint32_t rr[2][32];
+          tmem_ld32(tO + hf * 64, rr[0]);
+          tmem_ld32(tO + hf * 64 + 32, rr[1]);
+          tmem_ld_wait();
+          if (hf == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free[X]);
+          }
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 qv;
+              uint32_t* w = reinterpret_cast<uint32_t*>(&qv);
+#pragma unroll
+              for (int t = 0; t < 4; t++)
+                w[t] = pack_bf16(__uint_as_float(rr[u][e + 2 * t]) * inv, __uint_as_float(rr[u][e + 2 * t + 1]) * inv);
+              *reinterpret_cast<uint4*>(o + hf * 64 + u * 32 + e) = qv;
+            }
+          }
+        }
+      }
+      {
+        const long long si = ((long long)it.b * a.H + h) * a.T + q;
+        const float ln2 = 0.6931471805599453f;
+        if (a.lse) a.lse[si] = (m_used + log2f(l)) * ln2;
+        if (a.l) a.l[si] = l;
+        if (a.m) a.m[si] = m_used * ln2;
+      }
+      nX++;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace
 
 bool attention_tc_supported(const AttnArgs& a) {
@@ -657,12 +1068,22 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
   if (dev < 0 || !attr.done[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
     CUDA_TRY(cudaFuncSetAttribute(attn_fwd_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+    CUDA_TRY(cudaFuncSetAttribute(attn_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PP_SMEM));
     if (dev >= 0) attr.done[dev] = true;
   }
-  static int variant = -1;   // FEMTO_ATTN_FWD=1 in the environment selects the one-CTA-per-item kernel (measurement aid)
-  if (variant < 0) { const char* e = getenv("FEMTO_ATTN_FWD"); variant = (e && e[0] == '1') ? 1 : 2; }
-  // the persistent kernel assumes every query tile is full and starts on a 16-byte boundary of the document starts
-  if (variant == 2) {
+  // FEMTO_ATTN_FWD in the environment selects an older kernel (measurement aid): 1 = one CTA per (query tile, head),
+  // 3 = persistent, two query tiles in ping-pong (measured slower so far); default 2 = persistent, one query tile at a time
+  static int variant = -1;
+  if (variant < 0) { const char* e = getenv("FEMTO_ATTN_FWD"); variant = (e && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 2; }
+  // the persistent kernels assume every query tile is full and starts on a 16-byte boundary of the document starts
+  if (variant == 3) {
+    const int G = a.H / a.Hkv;
+    const bool gqa = (G % 2) == 0;
+    const int nqt = a.T / BQ;
+    const int nitems = gqa ? nqt * (a.H / 2) * a.B : ((nqt + 1) / 2) * a.H * a.B;
+    const int grid = std::min(nitems, device_sm_count());
+    attn_fwd_pair_kernel<<<grid, FWD_THREADS, PP_SMEM, s>>>(tmQ, tmK, tmV, p, nitems, gqa ? 1 : 0);
+  } else if (variant == 2) {
     const int nitems = (a.T / BQ) * a.H * a.B;
     const int grid = std::min(nitems, device_sm_count());
     attn_fwd_persistent_kernel<<<grid, FWD_THREADS, PF_SMEM, s>>>(tmQ, tmK, tmV, p, nitems);

@@ -214,6 +214,7 @@ struct XentArgs {
   int N = 0, D = 0, V = 0;
   float scale = 1.f; const float* scale_dev = nullptr;
   bool backward = false; void* dx = nullptr; float* dw = nullptr;
+  bool dw_overwrite = false;    // the first chunk's weight gradient overwrites dw instead of adding to it
   int chunk = 0;
   float* logits_f32 = nullptr;  // [chunk][ldw] fp32, SIMT path only
   float2* stats = nullptr; float* tz = nullptr; float* lse_rows = nullptr; float* loss_rows = nullptr;

@@ -363,15 +363,28 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     GemmArgs g = GA();
     if (two) g.ws = h->gemm_ws2;
     g.A = X; g.lda = in; g.a_kmajor = false; g.B = dY; g.ldb = ldy; g.b_kmajor = false;
-    g.C = dW; g.ldc = out; g.M = in; g.N = out; g.K = N; g.epi = EPI_F32; g.beta = 1.f;
+    g.C = dW; g.ldc = out; g.M = in; g.N = out; g.K = N; g.epi = EPI_F32; g.beta = accumulate ? 1.f : 0.f;
     return gemm<T>(g, s2);
   };
 
   FEMTO_TRY(S::prep_tokens(tokens, targets, positions, B, Tl, h->cfg.index_base, V, h->cfg.max_document_tokens,
                            h->tok0, h->tgt0, h->pos, h->doc_start, h->status, s));
-  if (backward && !accumulate) {   // off the chain: nothing reads or writes delta before the lm_head tail
+  // A step that does not accumulate overwrites the matrices' ranges of delta (their products run with beta = 0) and
+  // zero-fills only what is summed into: the embedding tables (row scatter), the gates and the scalars.  Off the
+  // chain: nothing reads or writes delta before the lm_head tail.
+  const bool lm_overwrite = V == Vp;   // padding columns of lm_head are written by nobody: keep the fill for them
+  if (backward && !accumulate) {
     FEMTO_TRY(fork());
-    FEMTO_TRY(fill_zero(delta, sizeof(float) * (size_t)h->nparams, s2));
+    auto zero = [&](long long off, long long n) { return n > 0 ? fill_zero(delta + off, sizeof(float) * (size_t)n, s2) : 0; };
+    FEMTO_TRY(zero(h->off_wte, (long long)Vp * d));
+    for (int i = 0; i < L; i++) {
+      const LayerP& p = h->lp[i];
+      if (p.ve) FEMTO_TRY(zero(p.ve_gate, 12ll * Hkv));
+      const long long from = p.ve ? p.ve_table : p.lam_b;
+      FEMTO_TRY(zero(from, p.lam_x0 + 1 - from));
+    }
+    if (!lm_overwrite) FEMTO_TRY(zero(h->off_lm, (long long)Vp * d));
+    FEMTO_TRY(zero(h->off_smear, h->nparams - h->off_smear));
     FEMTO_TRY(side_read(SL_FILL));
   }
   const int* docs = h->cfg.doc_mask ? h->doc_start : nullptr;
@@ -433,6 +446,7 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     x.x = h->xnf; x.W = h->sh_lm; x.ldw = Vp; x.targets0 = h->tgt0; x.N = N; x.D = d; x.V = V;
     x.scale_dev = mean ? h->inv_nvalid : nullptr; x.backward = backward; x.dx = dxnf;
     x.dw = backward ? delta + h->off_lm : nullptr; x.chunk = h->xchunk; x.logits_f32 = h->logits_f32;
+    x.dw_overwrite = backward && !accumulate && lm_overwrite;
     x.stats = h->xstats; x.tz = h->tz; x.lse_rows = h->lse_rows; x.loss_rows = h->loss_rows; x.dlogit = h->dlogit;
     x.ws = h->gemm_ws; x.ws_bytes = h->gemm_ws_bytes; x.status = h->status;
     if (two) {
@@ -465,23 +479,30 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   FEMTO_TRY(reduce_partials(h->partial, nb, 1, delta + h->off_lam_y, nullptr, 1.f, true, s));
   // The gradient of the residual stream rotates through three buffers, d(MLP pre-activation) and d(QKV) through
   // two each: a weight-gradient GEMM on the side stream may still be reading one while the chain writes the next.
+  // The last block reads its incoming gradient straight from dxf (nothing writes dxf again in this step).
   T* dxr[3] = {(T*)h->dx, (T*)h->dx_b, (T*)h->dx_c};
   T* dur[2] = {(T*)h->du, (T*)h->du_b};
   T* dqr[2] = {(T*)h->dqkv, (T*)h->dqkv_b};
-  int ci = 0;
-  CUDA_TRY(cudaMemcpyAsync(dxr[0], h->dxf, sizeof(T) * (size_t)N * d, cudaMemcpyDeviceToDevice, s));
+  T* dx = (T*)h->dxf;
+  int cs = -1, nf = 0;   // hazard slot of dx (-1: dxf, no slot) and the next free buffer of the rotation
   T* dxn = (T*)h->dxn;
   for (int i = L - 1; i >= 0; i--) {
     const LayerP& p = h->lp[i];
     LayerBuf& l = h->lb[i];
     const T* xin = i == 0 ? (const T*)h->x0 : (const T*)h->lb[i - 1].xout;
-    const int c1 = (ci + 1) % 3, c2 = (ci + 2) % 3, par = i & 1;
-    T *dx = dxr[ci], *dx1 = dxr[c1], *dx2 = dxr[c2], *du = dur[par], *dqkv = dqr[par];
-    if (i == h->backout) FEMTO_TRY(S::axpy(dx, (const T*)h->dxf, theta + h->off_lam_y, -1.f, (long long)N * d, s));
+    const int c1 = nf, c2 = (nf + 1) % 3, par = i & 1;
+    T *dx1 = dxr[c1], *dx2 = dxr[c2], *du = dur[par], *dqkv = dqr[par];
+    if (i == h->backout) {
+      if (cs < 0) {   // a model so shallow that the backout block is the last one: work on a copy, dxf is the operand
+        CUDA_TRY(cudaMemcpyAsync(dxr[2], h->dxf, sizeof(T) * (size_t)N * d, cudaMemcpyDeviceToDevice, s));
+        dx = dxr[2]; cs = 2;
+      }
+      FEMTO_TRY(S::axpy(dx, (const T*)h->dxf, theta + h->off_lam_y, -1.f, (long long)N * d, s));
+    }
     // MLP (ext/FemtoChatEnzymeExt.jl:121-134)
     FEMTO_TRY(fork());
     FEMTO_TRY(lin_dw(l.a, 4 * d, dx, d, d, delta + p.proj));
-    FEMTO_TRY(side_read(SL_DX + ci));
+    if (cs >= 0) FEMTO_TRY(side_read(SL_DX + cs));
     FEMTO_TRY(chain_write(SL_DU + par));
     FEMTO_TRY(lin_dx(dx, d, d, l.sh_proj, 4 * d, du, EPI_DRELU2, l.a));
     FEMTO_TRY(fork());
@@ -510,7 +531,7 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
       GemmArgs g = GA();  // fused dW of Q, K, V: three destinations in delta
       if (two) g.ws = h->gemm_ws2;
       g.A = l.xn1; g.lda = d; g.a_kmajor = false; g.B = dqkv; g.ldb = dq; g.b_kmajor = false;
-      g.M = d; g.N = dq; g.K = N; g.epi = EPI_F32; g.beta = 1.f; g.nseg = 3;
+      g.M = d; g.N = dq; g.K = N; g.epi = EPI_F32; g.beta = accumulate ? 1.f : 0.f; g.nseg = 3;
       g.seg_col0[0] = 0; g.seg_ncol[0] = d; g.seg_ptr[0] = delta + p.wq; g.seg_ld[0] = d;
       g.seg_col0[1] = d; g.seg_ncol[1] = kv; g.seg_ptr[1] = delta + p.wk; g.seg_ld[1] = kv;
       g.seg_col0[2] = d + kv; g.seg_ncol[2] = kv; g.seg_ptr[2] = delta + p.wv; g.seg_ld[2] = kv;
@@ -528,13 +549,12 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     FEMTO_TRY(S::mix_bwd(dx1, dx2, dxn, (const T*)l.xn1, l.r1, xin, (const T*)h->x0, theta + p.lam_b, theta + p.lam_x0,
                          (T*)h->dx0, i == L - 1, N, d, h->partial, &nb, s));
     FEMTO_TRY(reduce_partials(h->partial, nb, 2, delta + p.lam_b, nullptr, 1.f, true, s));
-    ci = c2;
+    dx = dx2; cs = c2; nf = (c2 + 1) % 3;
     if (ov) {
       FEMTO_TRY(join());
       FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + p.wq, p.lam_x0 + 1 - p.wq, s));   // the block's range is contiguous
     }
   }
-  T* dx = dxr[ci];
   FEMTO_TRY(S::add((T*)h->dx0, dx, (long long)N * d, s));
   FEMTO_TRY(S::smear_gate_bwd((const T*)h->dx0, (const T*)h->xe, h->sg, theta + h->off_lam_s, N, Tl, d, h->dpre_s,
                               h->partial, &nb, s));

@@ -58,7 +58,7 @@ template <typename T> int xent_tail(const XentArgs& x, cudaStream_t s) {
       GemmArgs gw;  // dW[d][ld] += x[cn][d]^T * dlogit[cn][V]   (the chunks' sums stay in order: one stream)
       gw.ws = two ? x.ws2 : x.ws; gw.ws_bytes = x.ws_bytes; gw.status = x.status; gw.ring = two ? 5 : 0;
       gw.A = xc; gw.lda = d; gw.a_kmajor = false; gw.B = dlogit; gw.ldb = ld; gw.b_kmajor = false;
-      gw.C = x.dw; gw.ldc = ld; gw.M = d; gw.N = V; gw.K = cn; gw.epi = EPI_F32; gw.beta = 1.f;
+      gw.C = x.dw; gw.ldc = ld; gw.M = d; gw.N = V; gw.K = cn; gw.epi = EPI_F32; gw.beta = (x.dw_overwrite && c0 == 0) ? 0.f : 1.f;
       FEMTO_TRY(gemm<T>(gw, sw));
       if (two) { CUDA_TRY(cudaEventRecord(x.ev_read[ci & 1], x.side)); armed[ci & 1] = true; }
     }

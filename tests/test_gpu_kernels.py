@@ -76,7 +76,9 @@ def _attn_inputs(dtype, B, T, H, Hkv, hd, seed, docs):
     (_lib.BF16, 2, 256, 4, 2, 128, 256, False), (_lib.BF16, 2, 512, 4, 2, 128, 100, True),
     (_lib.BF16, 1, 1024, 10, 5, 128, 300, True), (_lib.BF16, 2, 96, 2, 1, 64, 30, False),
     # one query head per kv head (the single-head forward kernel) and four per kv head (two CTAs per group)
-    (_lib.BF16, 2, 384, 3, 3, 128, 200, True), (_lib.BF16, 1, 512, 8, 2, 128, 512, False)])
+    (_lib.BF16, 2, 384, 3, 3, 128, 200, True), (_lib.BF16, 1, 512, 8, 2, 128, 512, False),
+    # three query heads per kv head: the forward pairs adjacent query tiles of one head instead of two heads
+    (_lib.BF16, 1, 512, 6, 2, 128, 150, True)])
 def test_attention_forward_and_reverse(dtype, B, T, H, Hkv, hd, left, docs):
     """attention! / Δattention! against naive_attention (src/kernels.jl:59-96) and the blockwise reverse."""
     Q, K, V, dO, ds = _attn_inputs(dtype, B, T, H, Hkv, hd, seed=T + hd, docs=docs)
