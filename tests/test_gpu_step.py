@@ -137,6 +137,45 @@ def test_accumulate_matches_two_micro_steps():
     assert float((params.delta - (ga + gb)).abs().max()) <= 1e-5 * float((ga + gb).abs().max())
 
 
+def test_side_streams_give_the_bits_of_one_stream(monkeypatch):
+    """A handle created with FEMTO_SIDE_STREAM=0 keeps every launch of the training step on the caller's stream; the
+    default runs the weight-gradient GEMMs, the zero fill of delta and the AdamW tables on a second internal stream.
+    Same kernels, same reduction orders: loss, delta, Theta and the moments must agree bit for bit over several
+    steps (a missing dependency between the two streams shows up here as a difference)."""
+    BIG = dict(sequence_len=512, max_document_tokens=512, vocab_size=2048, n_layer=6, n_head=4, n_kv_head=2, n_embed=512,
+               window_pattern="SSL")
+    cfg, ocfg = fb.GPTConfig(**BIG), fo.GPTConfig(**BIG)
+    lay = fb.parameter_layout(cfg)
+    th = torch.zeros(lay.nparams)
+    fo.initialize(th, ocfg, fo.parameter_layout(ocfg), 11, all_nonzero=True)
+    batches = [inputs(BIG, 4, seed) for seed in (1, 2, 3)]
+    results = []
+    for side in ("0", "1"):
+        monkeypatch.setenv("FEMTO_SIDE_STREAM", side)
+        params = fb.Params(th.clone().cuda())
+        st = fb.gradient_state(params, cfg, lay, *batches[0], compute_type="bfloat16", short_window=128, doc_mask=True)
+        opt = fb.MuonAdamW(params, lay, st, compute_type="bfloat16")
+        losses, deltas = [], []
+        for rep in range(2):          # two passes over the batches: the second one starts from updated weights
+            for i, b in enumerate(batches):
+                losses.append(fb.loss_and_gradient_(params, st, lay, *b, reduction="mean"))
+                # a second micro-step that accumulates, then the update
+                losses.append(fb.loss_and_gradient_(params, st, lay, *batches[(i + 1) % 3], reduction="mean", accumulate=True))
+                deltas.append(params.delta.clone())
+                opt.step(eta=0.5)
+        torch.cuda.synchronize()
+        assert st.status_word() == 0
+        results.append((losses, deltas, params.theta.clone(),
+                        [x.clone() for x in (opt.adam_m, opt.adam_v, opt.muon_m, opt.muon_v)]))
+    (l0, d0, t0, s0), (l1, d1, t1, s1) = results
+    assert l0 == l1
+    for a, b in zip(d0, d1):
+        assert torch.equal(a, b)
+    assert torch.equal(t0, t1)
+    for a, b in zip(s0, s1):
+        assert torch.equal(a, b)
+
+
 def test_bf16_small_simt_paths():
     r = run_both(MID, 3, "bfloat16", short_window=32)
     assert abs(r["l1"] - r["l0"]) <= 1e-2 * abs(r["l0"])
