@@ -218,6 +218,13 @@ __global__ void k_rope_tables(float* sin_t, float* cos_t, int n, int half, int h
 }  // namespace
 
 int model_alloc(femto_handle* h) {
+  {
+    // FEMTO_XENT_CHUNK in the environment overrides the lm_head tail's chunk of 16 384 tokens (256..32768; lets a
+    // small test shape run the chunk loop with a ragged last chunk).  Measured: a chunk of 18 944 tokens, which makes
+    // the dX product of a chunk a whole number of GEMM waves on 148 SMs, is no faster than 16 384.
+    const char* env = getenv("FEMTO_XENT_CHUNK");
+    if (env && atoi(env) >= 256 && atoi(env) <= 32768) h->xchunk = std::min(h->maxN, atoi(env) / 256 * 256);
+  }
   Bump dry;
   carve(h, dry);
   h->arena_bytes = dry.off + 256;

@@ -138,8 +138,11 @@ TC = dict(sequence_len=256, max_document_tokens=512, vocab_size=1000, n_layer=4,
 
 
 @pytest.mark.parametrize("doc_mask", [False, True])
-def test_small_tensor_core_step_every_tensor(doc_mask):
-    """The smallest shape that runs every tensor-core kernel, all fifteen tensor kinds checked one by one."""
+def test_small_tensor_core_step_every_tensor(doc_mask, monkeypatch):
+    """The smallest shape that runs every tensor-core kernel, all fifteen tensor kinds checked one by one.  The lm_head
+    tail is cut into chunks of 768 tokens here (1024 tokens: one full chunk and a short one, the second on the other
+    d-logit buffer and adding to the first one's weight gradient), as the full-size step cuts its 65 536."""
+    monkeypatch.setenv("FEMTO_XENT_CHUNK", "768")
     cfg, ocfg = fb.GPTConfig(**TC), fo.GPTConfig(**TC)
     lay, olay = fb.parameter_layout(cfg), fo.parameter_layout(ocfg)
     g = torch.Generator().manual_seed(4)
