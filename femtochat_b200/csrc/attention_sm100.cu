@@ -43,6 +43,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  grid_launch_dependents();   // the GEMM that follows may set itself up while this kernel runs (it still waits for our completion)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -328,6 +329,7 @@ __device__ __forceinline__ void pf_item(const AttnArgs& a, int item, int nqt, in
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                            const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems) {
+  grid_launch_dependents();   // the GEMM that follows may set itself up while this kernel runs (it still waits for our completion)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                    // 2 stages (items)
@@ -675,6 +677,7 @@ __device__ __forceinline__ PairItem pp_item(const AttnArgs& a, int item, int nqt
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems, const int gqa) {
+  grid_launch_dependents();   // the GEMM that follows may set itself up while this kernel runs (it still waits for our completion)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                    // Q_A, Q_B

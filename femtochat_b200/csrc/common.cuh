@@ -107,6 +107,14 @@ struct PerDevice {
     return dev;
   }
 };
+// Programmatic dependent launch, primary side: lets a dependent kernel that was launched with the programmatic
+// stream-serialisation attribute (the tensor-core GEMM) be scheduled and run its set-up (barriers, tensor memory,
+// descriptor prefetch) while this kernel is still running.  The dependent still waits for this kernel's completion
+// and memory flush before its first global access (griddepcontrol.wait), so calling this first thing is safe; it
+// has no effect when the next kernel is an ordinary launch.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 int device_sm_count();   // multiprocessors of the current device (cached per device)
 
 static inline int cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -28,10 +28,12 @@ struct ScatterPlan {
 namespace {
 
 __global__ void k_iota(int* p, int n) {
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = i;
 }
 __global__ void k_chunks(const int* counts, const int* num_runs, int n, int* nchunks, int* pchunks) {
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int c = i < num_runs[0] ? counts[i] : 0;
@@ -49,6 +51,7 @@ __global__ void __launch_bounds__(256) k_scatter_chunks(const int* __restrict__ 
                                                         const int* __restrict__ pstart, const int* __restrict__ order,
                                                         const T* __restrict__ dy, long long dy_stride, int D,
                                                         float* __restrict__ table, float* __restrict__ partial, int n) {
+  pdl_trigger();
   const int nr = num_runs[0];
   const int total = chunk_start[nr - 1] + nchunks[nr - 1];
   const int item = blockIdx.x;
@@ -84,6 +87,7 @@ __global__ void __launch_bounds__(256) k_scatter_combine(const int* __restrict__
                                                          const int* __restrict__ nchunks,
                                                          const int* __restrict__ pstart, int D,
                                                          float* __restrict__ table, const float* __restrict__ partial) {
+  pdl_trigger();
   const int nr = num_runs[0];
   for (int seg = blockIdx.x; seg < nr; seg += gridDim.x) {
     const int nc = nchunks[seg];

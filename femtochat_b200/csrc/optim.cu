@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const 
                                                float* __restrict__ m, float* __restrict__ v, long long n, float alpha,
                                                float b1, float b2, float eps, float lam, float c1, float c2,
                                                float inv_nt, S* __restrict__ shadow) {
+  pdl_trigger();
   // four elements per thread, a block apart: the sixteen loads are issued before the arithmetic, which is what
   // keeps enough bytes in flight (group offsets are arbitrary, so no wider-than-4-byte access is assumed)
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -93,6 +94,7 @@ struct SmallBatch { SmallAdam g[SMALL_BATCH]; };
 __global__ void __launch_bounds__(128) k_adamw_small(float* __restrict__ theta, const float* __restrict__ delta,
                                                      float* __restrict__ m, float* __restrict__ v,
                                                      const __grid_constant__ SmallBatch batch, float inv_nt) {
+  pdl_trigger();
   const SmallAdam& g = batch.g[blockIdx.x];
   for (int i = threadIdx.x; i < g.n; i += 128) {
     const float gg = delta[g.off + i] * inv_nt;
@@ -109,6 +111,7 @@ __global__ void __launch_bounds__(128) k_adamw_small(float* __restrict__ theta, 
 __global__ void __launch_bounds__(256) k_muon_momentum(const float* __restrict__ delta, const long long* __restrict__ offs,
                                                        float* __restrict__ mom, float* __restrict__ X, long long per,
                                                        float mu, float inv_nt) {
+  pdl_trigger();
   const int k = blockIdx.y;
   const float* g = delta + offs[k];
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
@@ -122,6 +125,7 @@ __global__ void __launch_bounds__(256) k_muon_momentum(const float* __restrict__
 // vec[k][o] = sum_i X[k][i][o]^2 (thread per column, rows in order)
 template <typename T>
 __global__ void __launch_bounds__(256) k_sumsq_cols(const T* __restrict__ X, int in, int out, float* __restrict__ vec) {
+  pdl_trigger();
   const int k = blockIdx.y;
   const int o = blockIdx.x * 256 + threadIdx.x;
   if (o >= out) return;
@@ -142,6 +146,7 @@ __global__ void __launch_bounds__(256) k_sumsq_cols(const T* __restrict__ X, int
 // vec[k][i] = sum_o X[k][i][o]^2 (warp per row)
 template <typename T>
 __global__ void __launch_bounds__(256) k_sumsq_rows(const T* __restrict__ X, int in, int out, float* __restrict__ vec) {
+  pdl_trigger();
   const int k = blockIdx.y;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (i >= in) return;
@@ -155,6 +160,7 @@ __global__ void __launch_bounds__(256) k_sumsq_rows(const T* __restrict__ X, int
 // MuonEq + Polar-Express normalisation factors (src/optim.jl:210-212,135-136), one block per matrix:
 // fac[k][o] = sqrt(old/m)/max(sqrt(row[o]),1e-6) / (1.01*sqrt(sum_o fac0^2*row[o]) + 1e-6)
 __global__ void __launch_bounds__(256) k_muoneq_factors(const float* __restrict__ vec, int out, float* __restrict__ fac) {
+  pdl_trigger();
   __shared__ float red[256];
   const int k = blockIdx.x;
   const float* row = vec + (long long)k * out;
@@ -181,6 +187,7 @@ __global__ void __launch_bounds__(256) k_muoneq_factors(const float* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(256) k_scale_cols_cast(const float* __restrict__ X, const float* __restrict__ fac,
                                                          T* __restrict__ Y, long long per, int out) {
+  pdl_trigger();
   const int k = blockIdx.y;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x)
     Y[k * per + i] = from_f<T>(X[k * per + i] * fac[(long long)k * out + (int)(i % out)]);
@@ -190,6 +197,7 @@ __global__ void __launch_bounds__(256) k_scale_cols_cast(const float* __restrict
 template <typename T>
 __global__ void __launch_bounds__(256) k_scale_cols_cast4(const float* __restrict__ X, const float* __restrict__ fac,
                                                           T* __restrict__ Y, int per4, int out4) {
+  pdl_trigger();
   const int k = blockIdx.y;
   const float4* x4 = reinterpret_cast<const float4*>(X) + (long long)k * per4;
   const float4* f4 = reinterpret_cast<const float4*>(fac) + (long long)k * out4;
@@ -212,6 +220,7 @@ __global__ void __launch_bounds__(256) k_scale_cols_cast4(const float* __restric
 // the reduced axis (length dim, each over dsize elements); v is the persistent second moment.
 __global__ void __launch_bounds__(256) k_normuon_factors(const float* __restrict__ vec, int dim, int dsize, int rmin,
                                                          float b2, float* __restrict__ v, float* __restrict__ fac) {
+  pdl_trigger();
   __shared__ float red[256];
   const int k = blockIdx.x;
   const float* S = vec + (long long)k * dim;
@@ -246,6 +255,7 @@ __global__ void __launch_bounds__(256) k_muon_update(float* __restrict__ theta, 
                                                      const T* __restrict__ X, const float* __restrict__ fac,
                                                      long long per, int out, int by_col, int dim, float eta, float lam,
                                                      void* const* __restrict__ shadow, const int* __restrict__ shadow_ld) {
+  pdl_trigger();
   const int k = blockIdx.y;
   float* th = theta + offs[k];
   S* sh = shadow ? reinterpret_cast<S*>(shadow[k]) : nullptr;
@@ -269,6 +279,7 @@ __global__ void __launch_bounds__(256) k_muon_update2(float* __restrict__ theta,
                                                       const T* __restrict__ X, const float* __restrict__ fac,
                                                       int per2, int out2, int by_col, int dim, float eta, float lam,
                                                       void* const* __restrict__ shadow, const int* __restrict__ shadow_ld) {
+  pdl_trigger();
   const int k = blockIdx.y;
   float2* th = reinterpret_cast<float2*>(theta + offs[k]);
   S* sh = shadow ? reinterpret_cast<S*>(shadow[k]) : nullptr;
@@ -334,6 +345,7 @@ int adamw_launch(float* theta, const float* delta, float* m, float* v, long long
 // tiles touching the upper triangle were computed.  64 x 64 tiles through shared memory, one block per tile pair.
 template <typename T>
 __global__ void __launch_bounds__(256) k_mirror_upper(T* __restrict__ C, int r, long long stride, int nb) {
+  pdl_trigger();
   __shared__ float tile[64][65];
   // blockIdx.x enumerates the tile pairs (bi >= bj) of the lower triangle, 64 x 64 elements each
   int bi = (int)((sqrtf(8.f * blockIdx.x + 1.f) - 1.f) * 0.5f);
@@ -505,6 +517,7 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(256) k_direction_out(const T* __restrict__ X, const float* __restrict__ fac,
                                                        float* __restrict__ out_, long long per, int out, int by_col, int dim) {
+  pdl_trigger();
   const int k = blockIdx.y;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
     const int j = by_col ? (int)(i % out) : (int)(i / out);
@@ -512,6 +525,7 @@ __global__ void __launch_bounds__(256) k_direction_out(const T* __restrict__ X, 
   }
 }
 __global__ void k_stack_offsets(long long* offs, int k, long long per) {
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < k) offs[i] = (long long)i * per;
 }

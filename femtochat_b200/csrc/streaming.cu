@@ -28,6 +28,7 @@ constexpr int WPB = 8;  // warps (rows) per block
 __global__ void k_prep_tokens(const int* tokens, const int* targets, const int* positions, int n, int Tlen,
                               int base, int vocab, int maxdoc, int* tok0, int* tgt0, int* pos, int* doc_start,
                               unsigned int* status) {
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int t = i % Tlen;
@@ -49,6 +50,7 @@ __global__ void k_prep_tokens(const int* tokens, const int* targets, const int* 
 template <typename T, int V>
 __global__ void __launch_bounds__(256) k_embed_norm(const T* __restrict__ table, const int* __restrict__ tok0,
                                                     T* __restrict__ xe, int N, int D, float eps) {
+  pdl_trigger();
   ROW_SETUP();
   const T* src = table + (long long)tok0[row] * D;
   float ss = 0.f;
@@ -74,6 +76,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256) k_smear(const T* __restrict__ xe, const float* __restrict__ w_s,
                                                const float* __restrict__ lam_s, int N, int Tlen, int D,
                                                float* __restrict__ sg, T* __restrict__ x0) {
+  pdl_trigger();
   ROW_SETUP();
   const int t = (int)(row % Tlen);
   const T* cur = xe + row * D;
@@ -108,6 +111,7 @@ __global__ void __launch_bounds__(256) k_mix_norm(const T* __restrict__ xin, con
                                                   const float* __restrict__ lam_b, const float* __restrict__ lam_x0,
                                                   T* __restrict__ xm, T* __restrict__ xn, float* __restrict__ r,
                                                   int N, int D, float eps) {
+  pdl_trigger();
   ROW_SETUP();
   const float lb = lam_b[0], l0 = lam_x0[0];
   const T* a = xin + row * D;
@@ -143,6 +147,7 @@ __global__ void __launch_bounds__(256) k_mix_norm(const T* __restrict__ xin, con
 template <typename T, int V>
 __global__ void __launch_bounds__(256) k_norm(const T* __restrict__ x, T* __restrict__ xn, float* __restrict__ r,
                                               int N, int D, float eps) {
+  pdl_trigger();
   ROW_SETUP();
   const T* a = x + row * D;
   float ss = 0.f;
@@ -171,6 +176,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256) k_backout_norm(const T* __restrict__ xl, const T* __restrict__ xb,
                                                       const float* __restrict__ lam_y, T* __restrict__ xnf,
                                                       float* __restrict__ rf, int N, int D, float eps) {
+  pdl_trigger();
   ROW_SETUP();
   const float ly = lam_y[0];
   const T* a = xl + row * D;
@@ -210,6 +216,7 @@ __global__ void __launch_bounds__(256) k_qkv_post(T* __restrict__ qkv, long long
                                                   const float* __restrict__ cos_t, long long N, int H, int Hkv,
                                                   int hd, float eps, float* __restrict__ rqk,
                                                   float* __restrict__ sv) {
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int nslot = H + 2 * Hkv;
   const long long w = (long long)blockIdx.x * WPB + (threadIdx.x >> 5);
@@ -260,6 +267,7 @@ __global__ void __launch_bounds__(256) k_qkv_post_bwd(T* __restrict__ dqkv, cons
                                                       int hd, const float* __restrict__ rqk,
                                                       const float* __restrict__ sv, T* __restrict__ dve,
                                                       float* __restrict__ dpre) {
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int nslot = H + 2 * Hkv;
   const long long w = (long long)blockIdx.x * WPB + (threadIdx.x >> 5);
@@ -342,6 +350,7 @@ __global__ void __launch_bounds__(256) k_qkv_post_128(T* __restrict__ qkv, long 
                                                       const float* __restrict__ sin_t, const float* __restrict__ cos_t,
                                                       long long N, int H, int Hkv, float eps, float* __restrict__ rqk,
                                                       float* __restrict__ sv) {
+  pdl_trigger();
   constexpr int hd = 128, half = 64;
   const int sub = threadIdx.x & 7;
   const int nslot = H + 2 * Hkv;
@@ -398,6 +407,7 @@ __global__ void __launch_bounds__(256) k_qkv_post_bwd_128(T* __restrict__ dqkv, 
                                                           const float* __restrict__ cos_t, long long N, int H, int Hkv,
                                                           const float* __restrict__ rqk, const float* __restrict__ sv,
                                                           T* __restrict__ dve, float* __restrict__ dpre) {
+  pdl_trigger();
   constexpr int hd = 128, half = 64;
   const int sub = threadIdx.x & 7;
   const int nslot = H + 2 * Hkv;
@@ -451,6 +461,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) k_ve_gate_bwd(const T* __restrict__ xn1, int D, const float* __restrict__ dpre,
                                                      const float* __restrict__ ve_gate, T* __restrict__ dxn, int N,
                                                      int Hkv, float* __restrict__ partial) {
+  pdl_trigger();
   constexpr int CH = 256;
   __shared__ float sx[CH][12];
   extern __shared__ float sd[];  // [CH][Hkv]
@@ -479,6 +490,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256) k_norm_bwd_resid(const T* __restrict__ dy, const T* __restrict__ y,
                                                         const float* __restrict__ r, const T* resid,
                                                         T* out, int N, int D) {
+  pdl_trigger();
   ROW_SETUP();
   const T* a = dy + row * D;
   const T* b = y + row * D;
@@ -513,6 +525,7 @@ __global__ void __launch_bounds__(256) k_mix_bwd(const T* dx_in, T* dx, const T*
                                                  const float* __restrict__ lam_b, const float* __restrict__ lam_x0,
                                                  T* __restrict__ dx0, int first, int N, int D,
                                                  float* __restrict__ partial) {
+  pdl_trigger();
   __shared__ float red[WPB][2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float lb = lam_b[0], l0 = lam_x0[0];
@@ -566,6 +579,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256) k_head_bwd(const T* __restrict__ dxnf, const T* __restrict__ xnf,
                                                   const float* __restrict__ rf, const T* __restrict__ xb,
                                                   T* __restrict__ dxf, int N, int D, float* __restrict__ partial) {
+  pdl_trigger();
   __shared__ float red[WPB];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float sb = 0.f;
@@ -607,6 +621,7 @@ __global__ void __launch_bounds__(256) k_head_bwd(const T* __restrict__ dxnf, co
 
 template <typename T>
 __global__ void k_axpy(T* __restrict__ y, const T* __restrict__ x, const float* a_dev, float a_mul, long long n) {
+  pdl_trigger();
   const float a = (a_dev ? a_dev[0] : 1.f) * a_mul;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     y[i] = from_f<T>(to_f<T>(y[i]) + a * to_f<T>(x[i]));
@@ -619,6 +634,7 @@ __global__ void __launch_bounds__(256) k_smear_gate_bwd(const T* __restrict__ dx
                                                         const float* __restrict__ sg, const float* __restrict__ lam_s,
                                                         int N, int Tlen, int D, float* __restrict__ dpre,
                                                         float* __restrict__ partial) {
+  pdl_trigger();
   __shared__ float red[WPB][25];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float ls = lam_s[0];
@@ -660,6 +676,7 @@ __global__ void __launch_bounds__(256) k_embed_bwd(const T* __restrict__ dx0, co
                                                    const float* __restrict__ sg, const float* __restrict__ dpre,
                                                    const float* __restrict__ w_s, const float* __restrict__ lam_s,
                                                    int N, int Tlen, int D, float eps, T* __restrict__ dE) {
+  pdl_trigger();
   ROW_SETUP();
   const int t = (int)(row % Tlen);
   const bool has_next = t + 1 < Tlen;
@@ -705,6 +722,7 @@ __global__ void __launch_bounds__(256) k_xent_rows(const float* __restrict__ log
                                                    const float* __restrict__ w_dev, T* __restrict__ dlogit,
                                                    long long lddl,
                                                    float* __restrict__ loss_rows) {
+  pdl_trigger();
   __shared__ float red[8];
   __shared__ float bc;
   const long long row = blockIdx.x;
@@ -740,6 +758,7 @@ __global__ void __launch_bounds__(256) k_xent_rows(const float* __restrict__ log
 }
 
 template <typename T> __global__ void k_cast(const float* __restrict__ src, T* __restrict__ dst, long long n) {
+  pdl_trigger();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     dst[i] = from_f<T>(src[i]);
 }
@@ -747,6 +766,7 @@ template <typename T> __global__ void k_cast(const float* __restrict__ src, T* _
 template <typename T>
 __global__ void k_pack_qkv(const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ wv,
                            T* __restrict__ dst, int D, int kv) {
+  pdl_trigger();
   const int W = D + 2 * kv;
   const long long n = (long long)D * W;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -759,6 +779,7 @@ __global__ void k_pack_qkv(const float* __restrict__ wq, const float* __restrict
 __global__ void __launch_bounds__(1024) k_sum_rows(const float* __restrict__ rows, int n, float* out,
                                                    const int* __restrict__ tgt0, int* n_valid_out,
                                                    float scale_by_valid) {
+  pdl_trigger();
   __shared__ float red[32];
   __shared__ int redc[32];
   float acc = 0.f;
@@ -782,21 +803,28 @@ __global__ void __launch_bounds__(1024) k_sum_rows(const float* __restrict__ row
   }
 }
 
+// One warp per column: the lanes take every 32nd row, then a fixed shuffle tree (repeatable).  A single thread per
+// column walking several hundred rows took 17 us per launch, 32 launches per step on the dependency chain.
 __global__ void __launch_bounds__(256) k_reduce_partials(const float* __restrict__ partial, int nrow, int ncol,
                                                          float* out, const float* scale_dev, float scale,
                                                          int accumulate) {
-  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_trigger();
+  const int j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (j >= ncol) return;
   float acc = 0.f;
-  for (int i = 0; i < nrow; i++) acc += partial[(long long)i * ncol + j];
-  acc *= scale * (scale_dev ? scale_dev[0] : 1.f);
-  out[j] = (accumulate ? out[j] : 0.f) + acc;
+  for (int i = lane; i < nrow; i += 32) acc += partial[(long long)i * ncol + j];
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    acc *= scale * (scale_dev ? scale_dev[0] : 1.f);
+    out[j] = (accumulate ? out[j] : 0.f) + acc;
+  }
 }
 
 // One warp per row: merge the row's (max, sum exp) partials into its logsumexp.
 __global__ void __launch_bounds__(256) k_xent_finalize(const float2* __restrict__ stats, int ntile,
                                                        const float* __restrict__ tz, const int* __restrict__ tgt0,
                                                        int n, float* __restrict__ lse, float* __restrict__ loss_rows) {
+  pdl_trigger();
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= n) return;
   const float2* st = stats + (long long)row * ntile;
@@ -825,6 +853,7 @@ __global__ void __launch_bounds__(256) k_xent_dlogit_inplace(bf16* __restrict__ 
                                                              const float* __restrict__ lse_rows,
                                                              const int* __restrict__ tgt0, int V, float w_host,
                                                              const float* __restrict__ w_dev) {
+  pdl_trigger();
   const long long row = blockIdx.y;
   const int col0 = blockIdx.x * 8192 + threadIdx.x * 8;
   const int tg = tgt0[row];
@@ -1023,7 +1052,7 @@ int sum_rows_to_scalar(const float* rows, int n, float* out, const int* tgt0, in
 }
 int reduce_partials(const float* partial, int nrow, int ncol, float* out, const float* scale_dev, float scale,
                     bool accumulate, cudaStream_t s) {
-  k_reduce_partials<<<cdiv(ncol, 256), 256, 0, s>>>(partial, nrow, ncol, out, scale_dev, scale, accumulate ? 1 : 0);
+  k_reduce_partials<<<cdiv(ncol, 8), 256, 0, s>>>(partial, nrow, ncol, out, scale_dev, scale, accumulate ? 1 : 0);
   KERNEL_CHECK();
   return 0;
 }
@@ -1043,6 +1072,7 @@ int xent_dlogit_inplace(void* logits_bf16, long long ld, const float* lse_rows, 
 namespace {
 // z = 15 tanh(x / 15) in place (src/gpt.jl:12)
 __global__ void __launch_bounds__(256) k_softcap(float* __restrict__ x, long long n) {
+  pdl_trigger();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     x[i] = 15.f * tanhf(x[i] * (1.f / 15.f));
 }

@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(256) k_ce_rows(const float* __restrict__ logit
                                                  const int* __restrict__ tgt0, int V, float* __restrict__ loss_rows,
                                                  float* __restrict__ delta, long long ldd, float scale_host,
                                                  const float* __restrict__ scale_rows, const int* __restrict__ n_valid) {
+  pdl_trigger();
   __shared__ float red[8];
   __shared__ float bc;
   const long long row = blockIdx.x;
@@ -157,6 +158,7 @@ __global__ void __launch_bounds__(256) k_ce_rows(const float* __restrict__ logit
   }
 }
 __global__ void __launch_bounds__(1024) k_count_valid(const int* tgt0, int n, int* out) {
+  pdl_trigger();
   __shared__ int red[32];
   int c = 0;
   for (int i = threadIdx.x; i < n; i += 1024) c += tgt0[i] >= 0 ? 1 : 0;
