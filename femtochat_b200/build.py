@@ -13,6 +13,8 @@ LIB = os.path.join(HERE, "libfemto_sm100a.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xcudafe", "--diag_suppress=177"]
+# extra compiler flags for a one-off build (e.g. FEMTO_NVCC_FLAGS=-DFEMTO_ATTN_CYCLES with -f, then -f again without)
+FLAGS += os.environ.get("FEMTO_NVCC_FLAGS", "").split()
 
 
 def sources():

@@ -12,6 +12,7 @@
 // each): they read S with tcgen05.ld, keep the running max / sum, rescale the TMEM-resident O only
 // when the max grew by more than 2^8, and write P with tcgen05.st.  S of tile j+1 is computed
 // while the softmax of tile j runs.
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <algorithm>
@@ -39,6 +40,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+
+// Optional cycle accounting of the roles of the persistent forward kernels (compiled in with -DFEMTO_ATTN_CYCLES,
+// printed by the launcher when FEMTO_ATTN_PROF is set in the environment): consecutive laps of clock64(), summed per
+// role in CTA 0.  In a normal build every member is empty.
+struct Cyc {
+#ifdef FEMTO_ATTN_CYCLES
+  long long t = 0, acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  __device__ __forceinline__ void start() { t = clock64(); }
+  __device__ __forceinline__ void lap(int i) { const long long n = clock64(); acc[i] += n - t; t = n; }
+  __device__ __forceinline__ void store(long long* prof, int slot, int tiles) const {
+    if (!prof || blockIdx.x != 0) return;
+    for (int i = 0; i < 10; i++) prof[slot * 16 + i] = acc[i];
+    prof[slot * 16 + 10] = tiles;
+  }
+#else
+  __device__ __forceinline__ void start() {}
+  __device__ __forceinline__ void lap(int) {}
+  __device__ __forceinline__ void store(long long*, int, int) const {}
+#endif
+};
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -328,7 +349,7 @@ __device__ __forceinline__ void pf_item(const AttnArgs& a, int item, int nqt, in
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                           const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems) {
+                           const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems, long long* prof) {
   grid_launch_dependents();   // the GEMM that follows may set itself up while this kernel runs (it still waits for our completion)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -426,6 +447,8 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // both operands K-major
       int tc = 0;
       bool ok = true;
+      Cyc cy;   // laps: 0 waiting (Q, K, free S buffer), 1 issuing
+      cy.start();
       for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
         int qt, h, b;
         pf_item(a, item, nqt, qt, h, b);
@@ -439,6 +462,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           // S overwrites the buffer that held P of tile tc-2: its P V must have been executed
           if (tc >= 2 && !mbar_wait(&pv_done[st], ((tc - 2) >> 1) & 1, abort_flag, a.status)) { ok = false; break; }
           tc_fence_after();
+          cy.lap(0);
           const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
 #pragma unroll
           for (int k = 0; k < HD / 16; k++) {
@@ -446,9 +470,11 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             mma_ss(tS[st], smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0);
           }
           tc_commit(&s_full[st]);
+          cy.lap(1);
         }
         if (ok) tc_commit(&q_free[qs]);   // the item's last S has been issued: its Q stage may be refilled once it completes
       }
+      cy.store(prof, 1, tc);
     }
   } else if (warp == 2) {
     if (lane == 0) {
@@ -456,6 +482,8 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // V is N-contiguous
       int tc = 0;
       bool ok = true;
+      Cyc cy;   // laps: 0 waiting (Q, P, V, free O), 1 issuing
+      cy.start();
       for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
         int qt, h, b;
         pf_item(a, item, nqt, qt, h, b);
@@ -471,13 +499,16 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           if (!mbar_wait(&p_ready[st], ph, abort_flag, a.status)) { ok = false; break; }
           if (!mbar_wait(&v_full[st], ph, abort_flag, a.status)) { ok = false; break; }
           tc_fence_after();
+          cy.lap(0);
           const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
           for (int k = 0; k < BKV / 16; k++)
             mma_ts(tO, tS[st] + k * 8, smem_desc_sw128(v_addr + k * 2048, TILE_BYTES / 2, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
           tc_commit(&pv_done[st]);
+          cy.lap(1);
         }
       }
+      cy.store(prof, 2, tc);
     }
   } else if (warp >= 4) {
     // ---------------- softmax: NS threads per query row, each owns CW = 128 / NS of the keys of a tile ----------------
@@ -488,6 +519,8 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     const float c = rsqrtf((float)HD) * LOG2E;
     int tc = 0;
     bool ok = true;
+    Cyc cy;   // laps: 0 waiting for S (and Q), 1 S load + masks + maximum, 2 exchange barrier, 3 rescale, 4 exponentials + P store, 5 arrive, 6 end of item
+    cy.start();
     for (int item = blockIdx.x, n = 0; item < nitems; item += gridDim.x, n++) {
       int qt, h, b;
       pf_item(a, item, nqt, qt, h, b);
@@ -514,6 +547,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         if (ok && !mbar_wait(&s_full[st], ph, abort_flag, a.status)) ok = false;
         if (!ok) { asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory"); continue; }
         tc_fence_after();
+        cy.lap(0);
         float x[CW];
 #pragma unroll
         for (int u = 0; u < CW / 32; u++)
@@ -535,7 +569,9 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         }
         float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;
         xmax[(tc & 1) * (NS * 128) + hs * 128 + r] = mt;
+        cy.lap(1);
         asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+        cy.lap(2);
 #pragma unroll
         for (int o = 1; o < NS; o++) mt = fmaxf(mt, xmax[(tc & 1) * (NS * 128) + ((hs + o) % NS) * 128 + r]);
         const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
@@ -560,6 +596,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             tmem_st_wait();
           }
         }
+        cy.lap(3);
         const float mm = (m_used == -INFINITY) ? 0.f : m_used;
         float sm[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -576,10 +613,12 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           tmem_st16(tS[st] + lane_off + hs * (CW / 2) + u * 16, pk);
         }
         l += (sm[0] + sm[1]) + (sm[2] + sm[3]);
+        cy.lap(4);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_ready[st]);
+        cy.lap(5);
       }
       // ---- the item's O: out of tensor memory first (so that the next item's products can start), then to global memory ----
       xl[hs * 128 + r] = l;
@@ -621,7 +660,9 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       }
       // the row's partner reads xl of this item before either thread may overwrite it for the next one
       asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
+      cy.lap(6);
     }
+    if (lane == 0) cy.store(prof, warp, tc);
   }
 
   tc_fence_before();
@@ -676,7 +717,7 @@ __device__ __forceinline__ PairItem pp_item(const AttnArgs& a, int item, int nqt
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems, const int gqa) {
+                     const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems, const int gqa, long long* prof) {
   grid_launch_dependents();   // the GEMM that follows may set itself up while this kernel runs (it still waits for our completion)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -783,6 +824,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // V is N-contiguous
       int tu = 0, tcx[2] = {0, 0}, nx[2] = {0, 0};
       bool ok = true;
+      Cyc cy;   // laps: 0 waiting (Q, K, V, P_A, P_B, free O), 1 issuing
+      cy.start();
       for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
         if (!mbar_wait(q_full, n & 1, abort_flag, a.status)) break;
         const int jlo[2] = {rng[0], rng[2]}, jhi[2] = {rng[1], rng[3]};
@@ -804,10 +847,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // first key tile of the item
         if (!mbar_wait(&k_full[tu & 1], (tu >> 1) & 1, abort_flag, a.status)) break;
         tc_fence_after();
+        cy.lap(0);
         if (in(0, 0)) issue_s(0, tu & 1);
         if (in(1, 0)) issue_s(1, tu & 1);
         tc_commit(&k_free[tu & 1]);
         if (nu == 1) tc_commit(q_free);
+        cy.lap(1);
         for (int u = 0; u < nu && ok; u++) {
           const int st = (tu + u) & 1, st1 = (tu + u + 1) & 1;
           const uint32_t ph = ((tu + u) >> 1) & 1, ph1 = ((tu + u + 1) >> 1) & 1;
@@ -821,6 +866,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               // O_X still holds the previous item's result until its warpgroup has read it
               if (first[X] && nx[X] >= 1 && !mbar_wait(&o_free[X], (nx[X] - 1) & 1, abort_flag, a.status)) { ok = false; break; }
               tc_fence_after();
+              cy.lap(0);
               const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
               for (int k = 0; k < BKV / 16; k++)
@@ -829,6 +875,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               tc_commit(&pv_done[X]);
               first[X] = false;
               tcx[X]++;
+              cy.lap(1);
             }
             if (X == 1) tc_commit(&v_free[st]);
             if (u + 1 < nu) {
@@ -836,7 +883,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 if (!k_seen && !mbar_wait(&k_full[st1], ph1, abort_flag, a.status)) { ok = false; break; }
                 k_seen = true;
                 tc_fence_after();
+                cy.lap(0);
                 issue_s(X, st1);
+                cy.lap(1);
               }
               if (X == 1) {
                 tc_commit(&k_free[st1]);
@@ -849,6 +898,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (has[0]) nx[0]++;
         if (has[1]) nx[1]++;
       }
+      cy.store(prof, 1, tu);
     }
   }
   } else {
@@ -862,6 +912,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint64_t c2 = pack2(c, c);
     int tc = 0, nX = 0;
     bool ok = true;
+    Cyc cy;   // laps: 0 waiting for S (and Q), 1 pass 1 (S load, masks, maximum), 3 rescale, 4 pass 2 (S load, exponentials, P store), 5 arrive, 6 end of item
+    cy.start();
     for (int item = blockIdx.x, n = 0; item < nitems && ok; item += gridDim.x, n++) {
       const PairItem it = pp_item(a, item, nqt, gqa != 0);
       if (!mbar_wait(q_full, n & 1, abort_flag, a.status)) break;
@@ -878,6 +930,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int k0 = j * BKV;
         if (!mbar_wait(&s_full[X], tc & 1, abort_flag, a.status)) { ok = false; break; }
         tc_fence_after();
+        cy.lap(0);
         // Masks.  The keys this row may see in the tile are the columns ca..cb.  Per group of 32 columns the warp
         // decides together: every lane sees all of it (no work), no lane sees any of it (P = 0, no exponentials), or
         // mixed (element-wise select).  On a diagonal tile one group of four is mixed and those right of it are empty.
@@ -918,6 +971,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;
+        cy.lap(1);
         const bool grow = mt > m_used + 8.f || (m_used == -INFINITY && mt > -INFINITY);
         if (__any_sync(0xffffffffu, grow)) {
           const float m_new = fmaxf(m_used, mt);
@@ -940,6 +994,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tmem_st_wait();
           }
         }
+        cy.lap(3);
         // ---- pass 2: P = 2^(c S - m) as bf16 over S, and the row sum; two elements per fma / add ----
         const float mm = (m_used == -INFINITY) ? 0.f : m_used;
         const uint64_t nm2 = pack2(-mm, -mm);
@@ -988,10 +1043,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           unpack2(sm2[1], s2, s3);
           l += (s0 + s1) + (s2 + s3);
         }
+        cy.lap(4);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_ready[X]);
+        cy.lap(5);
       }
       if (!ok) break;
       // ---- the item's O: out of tensor memory (then the next item's P V may start), scaled, to global memory ----
@@ -1033,7 +1090,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (a.m) a.m[si] = m_used * ln2;
       }
       nX++;
+      cy.lap(6);
     }
+    if (lane == 0) cy.store(prof, warp, tc);
   }
 
   tc_fence_before();
@@ -1055,6 +1114,37 @@ bool attention_tc_supported(const AttnArgs& a) {
   if (a.doc_start && !aligned16(a.doc_start)) return false;
   return true;
 }
+
+// Cycle accounting (see Cyc): a 16 x 16 table of counters, one row per warp, printed after the launch.
+#ifdef FEMTO_ATTN_CYCLES
+static long long* g_cycles = nullptr;
+static long long* cycles_buffer() {
+  static int want = -1;
+  if (want < 0) {
+    want = getenv("FEMTO_ATTN_PROF") ? 1 : 0;
+    if (want && cudaMalloc(&g_cycles, 16 * 16 * sizeof(long long)) != cudaSuccess) g_cycles = nullptr;
+  }
+  if (g_cycles) cudaMemset(g_cycles, 0, 16 * 16 * sizeof(long long));
+  return g_cycles;
+}
+static void cycles_report(const char* issuers, const char* softmax, int first_issuer, int last_issuer) {
+  if (!g_cycles) return;
+  cudaDeviceSynchronize();
+  long long h[16 * 16];
+  cudaMemcpy(h, g_cycles, sizeof(h), cudaMemcpyDeviceToHost);
+  printf("cycles of CTA 0 | %s | %s\n", issuers, softmax);
+  for (int w = 0; w < 12; w++) {
+    if (!((w >= first_issuer && w <= last_issuer) || w == 4 || w == 8)) continue;
+    printf("  warp %2d tiles %lld:", w, h[w * 16 + 10]);
+    for (int i = 0; i < 7; i++) printf(" %lld", h[w * 16 + i]);
+    printf("\n");
+  }
+  fflush(stdout);
+}
+#else
+static long long* cycles_buffer() { return nullptr; }
+static void cycles_report(const char*, const char*, int, int) {}
+#endif
 
 int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
   if (!attention_tc_supported(a)) return femto_fail(FEMTO_ERR_UNSUPPORTED, "attention_fwd_tc: unsupported shape");
@@ -1085,11 +1175,13 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
     const int nqt = a.T / BQ;
     const int nitems = gqa ? nqt * (a.H / 2) * a.B : ((nqt + 1) / 2) * a.H * a.B;
     const int grid = std::min(nitems, device_sm_count());
-    attn_fwd_pair_kernel<<<grid, FWD_THREADS, PP_SMEM, s>>>(tmQ, tmK, tmV, p, nitems, gqa ? 1 : 0);
+    attn_fwd_pair_kernel<<<grid, FWD_THREADS, PP_SMEM, s>>>(tmQ, tmK, tmV, p, nitems, gqa ? 1 : 0, cycles_buffer());
+    cycles_report("issuer: waiting / issuing", "softmax A, B: wait S / pass 1 / - / rescale / pass 2 / arrive / item end", 1, 1);
   } else if (variant == 2) {
     const int nitems = (a.T / BQ) * a.H * a.B;
     const int grid = std::min(nitems, device_sm_count());
-    attn_fwd_persistent_kernel<<<grid, FWD_THREADS, PF_SMEM, s>>>(tmQ, tmK, tmV, p, nitems);
+    attn_fwd_persistent_kernel<<<grid, FWD_THREADS, PF_SMEM, s>>>(tmQ, tmK, tmV, p, nitems, cycles_buffer());
+    cycles_report("S issuer, P V issuer: waiting / issuing", "softmax (keys 0-63, 64-127): wait S / load+max / barrier / rescale / exp / arrive / item end", 1, 2);
   } else {
     dim3 grid(a.T / BQ, a.H, a.B);
     attn_fwd_tc_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tmQ, tmK, tmV, p);
