@@ -77,6 +77,26 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnArgs a, float* D
   }
 }
 
+// A warp's 32 rows x 64 columns of a result (two tcgen05.ld chunks per thread, scaled) as bf16 into a 4 KB staging
+// area in the 128-byte-swizzled layout of a (64 columns x 32 rows) TMA box: one tiled store then writes whole
+// 128-byte lines, where sixteen-byte stores of one row per lane cost every store instruction 32 separate lines.
+__device__ __forceinline__ void stage_rows(uint8_t* stage, const uint32_t (&r0)[32], const uint32_t (&r1)[32], float scale, int lane) {
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      uint4 q;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint32_t a0 = u ? r1[8 * j + 2 * e] : r0[8 * j + 2 * e], a1 = u ? r1[8 * j + 2 * e + 1] : r0[8 * j + 2 * e + 1];
+        w[e] = pack2(__uint_as_float(a0) * scale, __uint_as_float(a1) * scale);
+      }
+      *reinterpret_cast<uint4*>(stage + lane * 128 + (((u * 4 + j) ^ (lane & 7)) << 4)) = q;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // dQ kernel.  Roles: warp 0 streams K (three stages: a K tile is held until dQ has used it) and V
 // (two stages) with TMA; warps 1, 3 and 2 issue dP = dO V^T, S = Q K^T and dQ += dS K (issue of
@@ -90,7 +110,7 @@ constexpr int DQ_SMEM = TILE_BYTES * 7 + 1024 + 256;
 __global__ void __launch_bounds__(384, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const BwdParams p) {
+                   const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -301,14 +321,31 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int last = ntile - 1;
     if (ok && mbar_wait(&dq_done[last & 1], (last >> 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
-      bf16* dq = reinterpret_cast<bf16*>(a.dQ) + (row0 + q) * a.dq_stride + (long long)h * HD;
-#pragma unroll
-      for (int cc = 2 * halfsel; cc < 2 * halfsel + 2; cc++) {
-        uint32_t rr[32];
-        tmem_ld32(tdQ + lane_off + cc * 32, rr);
+      if (!a.accumulate) {
+        // every product has been executed: the Q tile's shared memory is free and stages the result for a TMA store
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tdQ + lane_off + (2 * halfsel) * 32, r0);
+        tmem_ld32(tdQ + lane_off + (2 * halfsel + 1) * 32, r1);
         tmem_ld_wait();
+        uint8_t* stage = sQ + (warp - 4) * 4096;
+        stage_rows(stage, r0, r1, scale, lane);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&tmdQ, stage, h * HD + halfsel * 64, (int)(row0 + q0 + quad * 32), 0);
+          bulk_commit();
+          bulk_wait_read<0>();   // shared memory is released when the CTA leaves
+        }
+      } else {
+        bf16* dq = reinterpret_cast<bf16*>(a.dQ) + (row0 + q) * a.dq_stride + (long long)h * HD;
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) store8(dq + cc * 32 + j, rr + j, scale, a.accumulate);
+        for (int cc = 2 * halfsel; cc < 2 * halfsel + 2; cc++) {
+          uint32_t rr[32];
+          tmem_ld32(tdQ + lane_off + cc * 32, rr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) store8(dq + cc * 32 + j, rr + j, scale, true);
+        }
       }
     }
   }
@@ -328,6 +365,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 __global__ void __launch_bounds__(384, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
                     const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -555,18 +593,40 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int lasth = n2 - 1;   // the dV / dK issuer's last commit covers every earlier instruction
     if (ok && mbar_wait(&out_done[lasth & 1], (lasth >> 1) & 1, abort_flag, a.status)) {
       tc_fence_after();
-      bf16* dk = reinterpret_cast<bf16*>(a.dK) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
-      bf16* dv = reinterpret_cast<bf16*>(a.dV) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
+      if (!a.accumulate) {
+        // every product has been executed: the two Q stages are free and stage dK and dV for TMA stores
+        const int out_row = (int)(row0 + key) - lane;   // first of this warp's 32 key rows
 #pragma unroll
-      for (int cc = 2 * halfsel; cc < 2 * halfsel + 2; cc++) {
-        uint32_t rk[32], rv[32];
-        tmem_ld32(tdK + lane_off + cc * 32, rk);
-        tmem_ld32(tdV + lane_off + cc * 32, rv);
-        tmem_ld_wait();
+        for (int which = 0; which < 2; which++) {
+          uint32_t r0[32], r1[32];
+          const uint32_t src = (which ? tdV : tdK) + lane_off;
+          tmem_ld32(src + (2 * halfsel) * 32, r0);
+          tmem_ld32(src + (2 * halfsel + 1) * 32, r1);
+          tmem_ld_wait();
+          uint8_t* stage = sQ + which * TILE_BYTES + (warp - 4) * 4096;
+          stage_rows(stage, r0, r1, which ? 1.f : scale, lane);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(which ? &tmdV : &tmdK, stage, kvh * HD + halfsel * 64, out_row, 0);
+            bulk_commit();
+          }
+        }
+        if (lane == 0) bulk_wait_read<0>();   // shared memory is released when the CTA leaves
+      } else {
+        bf16* dk = reinterpret_cast<bf16*>(a.dK) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
+        bf16* dv = reinterpret_cast<bf16*>(a.dV) + (row0 + key) * a.dkv_stride + (long long)kvh * HD;
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          store8(dk + cc * 32 + j, rk + j, scale, a.accumulate);
-          store8(dv + cc * 32 + j, rv + j, 1.f, a.accumulate);
+        for (int cc = 2 * halfsel; cc < 2 * halfsel + 2; cc++) {
+          uint32_t rk[32], rv[32];
+          tmem_ld32(tdK + lane_off + cc * 32, rk);
+          tmem_ld32(tdV + lane_off + cc * 32, rv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            store8(dk + cc * 32 + j, rk + j, scale, true);
+            store8(dv + cc * 32 + j, rv + j, 1.f, true);
+          }
         }
       }
     }
@@ -607,10 +667,15 @@ int attention_bwd_tc(const AttnArgs& a, cudaStream_t s) {
     if (dev >= 0) attr.done[dev] = true;
   }
   dim3 gq(a.T / BT, a.H, a.B);
-  attn_bwd_dq_kernel<<<gq, 384, DQ_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  // result maps: 64-column x 32-row swizzled boxes, one per row-owning warp
+  CUtensorMap tmdQ, tmdK, tmdV;
+  FEMTO_TRY(make_tmap_3d_bf16_sw(&tmdQ, a.dQ, (uint64_t)a.H * HD, N, 1, a.dq_stride, 0, 64, 32, 3));
+  FEMTO_TRY(make_tmap_3d_bf16_sw(&tmdK, a.dK, (uint64_t)a.Hkv * HD, N, 1, a.dkv_stride, 0, 64, 32, 3));
+  FEMTO_TRY(make_tmap_3d_bf16_sw(&tmdV, a.dV, (uint64_t)a.Hkv * HD, N, 1, a.dkv_stride, 0, 64, 32, 3));
+  attn_bwd_dq_kernel<<<gq, 384, DQ_SMEM, s>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
   KERNEL_CHECK();
   dim3 gk(a.T / BT, a.Hkv, a.B);
-  attn_bwd_dkv_kernel<<<gk, 384, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, p);
+  attn_bwd_dkv_kernel<<<gk, 384, BWD_SMEM, s>>>(tmQ, tmK, tmV, tmdO, tmdK, tmdV, p);
   KERNEL_CHECK();
   return 0;
 }

@@ -349,7 +349,8 @@ __device__ __forceinline__ void pf_item(const AttnArgs& a, int item, int nqt, in
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                           const __grid_constant__ CUtensorMap tmV, const FwdParams p, const int nitems, long long* prof) {
+                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FwdParams p,
+                           const int nitems, long long* prof) {
   grid_launch_dependents();   // the GEMM that follows may set itself up while this kernel runs (it still waits for our completion)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -384,7 +385,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     mbar_init(o_free, NS * 4);
     *abort_flag = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -534,7 +535,9 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const int jlo = item_jlo[qs];
       const int ntile = min(max((q0 + BQ - 1) / BKV - jlo + 1, 0), nqt);
       __syncwarp();
-      if (ok && lane == 0) mbar_arrive(&q_free[qs]);
+      // The Q stage of the PREVIOUS item doubles as the staging area of that item's O (see the end of the item):
+      // it goes back to the producer once the store has read it.
+      if (ok && lane == 0 && n >= 1) { bulk_wait_read<0>(); mbar_arrive(&q_free[(n - 1) & 1]); }
       int lo = max(0, q - a.window_left);
       if (a.doc_start) lo = max(lo, a.doc_start[row0 + q]);
       float m_used = -INFINITY, l = 0.f;
@@ -636,19 +639,28 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(o_free);
         const float inv = 1.f / l;
-        bf16* o = reinterpret_cast<bf16*>(a.O) + (row0 + q) * a.o_stride + (long long)h * HD;
+        // This warp's 32 rows x 64 columns of O leave through shared memory and ONE tiled TMA store (whole 128-byte
+        // lines; sixteen-byte stores of one row per lane cost every store instruction 32 separate lines).  The
+        // staging area is the item's own Q stage: every S product of the item has been executed (the threads have
+        // consumed the last S), and the stage is handed back to the producer only after the store has read it.
+        uint8_t* stage = sQ + qs * TILE_BYTES + (warp - 4) * 4096;
 #pragma unroll
         for (int u = 0; u < CW / 32; u++) {
-          const int cc = hs * (CW / 32) + u;
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
+          for (int j = 0; j < 4; j++) {
             uint4 qv;
             uint32_t* w = reinterpret_cast<uint32_t*>(&qv);
 #pragma unroll
             for (int e = 0; e < 4; e++)
-              w[e] = pack_bf16(__uint_as_float(rr[u][j + 2 * e]) * inv, __uint_as_float(rr[u][j + 2 * e + 1]) * inv);
-            *reinterpret_cast<uint4*>(o + cc * 32 + j) = qv;
+              w[e] = pack_bf16(__uint_as_float(rr[u][8 * j + 2 * e]) * inv, __uint_as_float(rr[u][8 * j + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(stage + lane * 128 + (((u * 4 + j) ^ (lane & 7)) << 4)) = qv;
           }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&tmO, stage, h * HD + hs * CW, (int)(row0 + q0 + quad * 32), 0);
+          bulk_commit();
         }
         if (hs == 0) {
           const long long si = ((long long)b * a.H + h) * a.T + q;
@@ -662,7 +674,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       asm volatile("bar.sync %0, %1;" ::"r"(2 + quad), "n"(NS * 32) : "memory");
       cy.lap(6);
     }
-    if (lane == 0) cy.store(prof, warp, tc);
+    if (lane == 0) { bulk_wait_all(); cy.store(prof, warp, tc); }   // the last item's store has left shared memory
   }
 
   tc_fence_before();
@@ -1180,7 +1192,9 @@ int attention_fwd_tc(const AttnArgs& a, cudaStream_t s) {
   } else if (variant == 2) {
     const int nitems = (a.T / BQ) * a.H * a.B;
     const int grid = std::min(nitems, device_sm_count());
-    attn_fwd_persistent_kernel<<<grid, FWD_THREADS, PF_SMEM, s>>>(tmQ, tmK, tmV, p, nitems, cycles_buffer());
+    CUtensorMap tmO;   // O as [rows][H * 128] for 64-column x 32-row swizzled boxes (one per softmax warp)
+    FEMTO_TRY(make_tmap_3d_bf16_sw(&tmO, a.O, (uint64_t)a.H * HD, N, 1, a.o_stride, 0, 64, 32, 3));
+    attn_fwd_persistent_kernel<<<grid, FWD_THREADS, PF_SMEM, s>>>(tmQ, tmK, tmV, tmO, p, nitems, cycles_buffer());
     cycles_report("S issuer, P V issuer: waiting / issuing", "softmax (keys 0-63, 64-127): wait S / load+max / barrier / rescale / exp / arrive / item end", 1, 2);
   } else {
     dim3 grid(a.T / BQ, a.H, a.B);
