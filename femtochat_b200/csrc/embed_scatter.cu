@@ -42,6 +42,9 @@ __global__ void k_chunks(const int* counts, const int* num_runs, int n, int* nch
   pchunks[i] = nc > 1 ? nc : 0;
 }
 
+// One WARP per chunk (eight chunks per block): a chunk is at most CH rows of D columns, far too little for a block, and
+// with one block per possible chunk two thirds of the blocks found nothing to do.  The lanes cover the columns with
+// 16-byte loads; the chunk's row indices are read once (lane r holds row r) and passed round by shuffle.
 template <typename T, int V>
 __global__ void __launch_bounds__(256) k_scatter_chunks(const int* __restrict__ num_runs, const int* __restrict__ uniq,
                                                         const int* __restrict__ counts,
@@ -52,9 +55,10 @@ __global__ void __launch_bounds__(256) k_scatter_chunks(const int* __restrict__ 
                                                         const T* __restrict__ dy, long long dy_stride, int D,
                                                         float* __restrict__ table, float* __restrict__ partial, int n) {
   pdl_trigger();
+  const int lane = threadIdx.x & 31;
   const int nr = num_runs[0];
   const int total = chunk_start[nr - 1] + nchunks[nr - 1];
-  const int item = blockIdx.x;
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (item >= total) return;
   // binary search: last segment with chunk_start <= item
   int lo = 0, hi = nr - 1;
@@ -68,37 +72,83 @@ __global__ void __launch_bounds__(256) k_scatter_chunks(const int* __restrict__ 
   const int cnt = min(CH, counts[seg] - ck * CH);
   const bool direct = nchunks[seg] == 1;
   float* dst = direct ? table + (long long)uniq[seg] * D : partial + (long long)(pstart[seg] + ck) * D;
-  for (int c = threadIdx.x * V; c < D; c += 256 * V) {
+  static_assert(CH <= 32, "a lane holds one row index of the chunk");
+  const int my_row = lane < cnt ? order[first + lane] : 0;
+  for (int c0 = 0; c0 < D; c0 += 32 * V) {   // every lane walks every pass: the shuffles below need the whole warp
+    const int c = c0 + lane * V;
+    const bool live = c < D;
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; i++) acc[i] = 0.f;
-    for (int r = 0; r < cnt; r++) {
-      float f[V];
-      load_vec<T, V>(dy + (long long)order[first + r] * dy_stride + c, f);
+    for (int r = 0; r < cnt; r++) {   // in token order: the sum is repeatable
+      const int row = __shfl_sync(0xffffffffu, my_row, r);
+      if (live) {
+        float f[V];
+        load_vec<T, V>(dy + (long long)row * dy_stride + c, f);
 #pragma unroll
-      for (int i = 0; i < V; i++) acc[i] += f[i];
+        for (int i = 0; i < V; i++) acc[i] += f[i];
+      }
     }
+    if (live) {
 #pragma unroll
-    for (int i = 0; i < V; i++) dst[c + i] = direct ? dst[c + i] + acc[i] : acc[i];
+      for (int i = 0; i < V; i++) dst[c + i] = direct ? dst[c + i] + acc[i] : acc[i];
+    }
   }
 }
 
+// Segments with more than one chunk (BOS, the head of the token distribution): their partial rows are added up in
+// chunk order.  A block looks at 256 segments at once and handles the few that qualify one after the other.
 __global__ void __launch_bounds__(256) k_scatter_combine(const int* __restrict__ num_runs, const int* __restrict__ uniq,
                                                          const int* __restrict__ nchunks,
                                                          const int* __restrict__ pstart, int D,
                                                          float* __restrict__ table, const float* __restrict__ partial) {
   pdl_trigger();
+  __shared__ int s_list[256];
+  __shared__ int s_cnt;
   const int nr = num_runs[0];
-  for (int seg = blockIdx.x; seg < nr; seg += gridDim.x) {
-    const int nc = nchunks[seg];
-    if (nc <= 1) continue;
-    float* dst = table + (long long)uniq[seg] * D;
-    const float* src = partial + (long long)pstart[seg] * D;
-    for (int c = threadIdx.x; c < D; c += 256) {
-      float acc = 0.f;
-      for (int k = 0; k < nc; k++) acc += src[(long long)k * D + c];
-      dst[c] += acc;
+  // thread t of block b looks at segment t * gridDim.x + b (+ whole rounds): neighbouring segments, and the frequent
+  // tokens are neighbours, go to different blocks
+  for (int base = 0; base < nr; base += gridDim.x * 256) {
+    if (threadIdx.x == 0) s_cnt = 0;
+    __syncthreads();
+    const int mine = base + threadIdx.x * gridDim.x + blockIdx.x;
+    if (mine < nr && nchunks[mine] > 1) s_list[atomicAdd(&s_cnt, 1)] = mine;   // the order of the list does not matter:
+    __syncthreads();                                                           // every segment has its own row
+    const int cnt = s_cnt;
+    for (int k = 0; k < cnt; k++) {
+      const int seg = s_list[k];
+      const int nc = nchunks[seg];
+      float* dst = table + (long long)uniq[seg] * D;
+      const float* src = partial + (long long)pstart[seg] * D;
+      if ((D & 3) == 0) {
+        // four columns per thread and sixteen chunks in flight, added in chunk order: the head of the token
+        // distribution has hundreds of chunks, and one dependent load per chunk bounded the whole kernel
+        for (int c = threadIdx.x * 4; c < D; c += 1024) {
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          int j = 0;
+          for (; j + 16 <= nc; j += 16) {
+            float4 v[16];
+#pragma unroll
+            for (int u = 0; u < 16; u++) v[u] = *reinterpret_cast<const float4*>(src + (long long)(j + u) * D + c);
+#pragma unroll
+            for (int u = 0; u < 16; u++) { acc[0] += v[u].x; acc[1] += v[u].y; acc[2] += v[u].z; acc[3] += v[u].w; }
+          }
+          for (; j < nc; j++) {
+            const float4 v = *reinterpret_cast<const float4*>(src + (long long)j * D + c);
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; i++) dst[c + i] += acc[i];
+        }
+      } else {
+        for (int c = threadIdx.x; c < D; c += 256) {
+          float acc = 0.f;
+          for (int j = 0; j < nc; j++) acc += src[(long long)j * D + c];
+          dst[c] += acc;
+        }
+      }
     }
+    __syncthreads();
   }
 }
 
@@ -168,7 +218,7 @@ template <typename T>
 int scatter_rows(ScatterPlan* p, float* table, const T* dy, long long dy_stride, int D, cudaStream_t s) {
   if (D > p->max_cols) return femto_fail(FEMTO_ERR_SHAPE, "scatter: D=%d exceeds plan width %d", D, p->max_cols);
   const int N = p->cur;
-  const int grid = N / CH + N + 1;  // upper bound of chunk count; surplus blocks exit at once
+  const int grid = cdiv(N / CH + N + 1, 8);  // eight chunks per block; the count is an upper bound, surplus warps exit at once
   const bool vec = D % VecN<T>::n == 0 && dy_stride % VecN<T>::n == 0 && aligned16(dy);
   if (vec)
     k_scatter_chunks<T, VecN<T>::n><<<grid, 256, 0, s>>>(p->num_runs, p->uniq, p->counts, p->seg_start, p->chunk_start,
@@ -178,7 +228,7 @@ int scatter_rows(ScatterPlan* p, float* table, const T* dy, long long dy_stride,
     k_scatter_chunks<T, 1><<<grid, 256, 0, s>>>(p->num_runs, p->uniq, p->counts, p->seg_start, p->chunk_start,
                                               p->nchunks, p->pstart, p->order, dy, dy_stride, D, table, p->partial, N);
   KERNEL_CHECK();
-  k_scatter_combine<<<1184, 256, 0, s>>>(p->num_runs, p->uniq, p->nchunks, p->pstart, D, table, p->partial);
+  k_scatter_combine<<<std::min(cdiv(N, 256), 1184), 256, 0, s>>>(p->num_runs, p->uniq, p->nchunks, p->pstart, D, table, p->partial);
   KERNEL_CHECK();
   return 0;
 }
