@@ -55,7 +55,7 @@ namespace {
 template <typename S>
 __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const float* __restrict__ delta,
                                                float* __restrict__ m, float* __restrict__ v, long long n, float alpha,
-                                               float b1, float b2, float eps, float lam, float c1, float c2,
+                                               float b1, float b2, float eps, float lam, float inv_c1, float inv_c2,
                                                float inv_nt, S* __restrict__ shadow) {
   pdl_trigger();
   // four elements per thread, a block apart: the sixteen loads are issued before the arithmetic, which is what
@@ -78,7 +78,11 @@ __global__ void __launch_bounds__(256) k_adamw(float* __restrict__ theta, const 
       m[i] = mm;
       v[i] = vv;
       const float t = th[u] * (1.f - alpha * lam);
-      const float tn = t - alpha * (mm / c1) / (sqrtf(vv / c2) + eps);
+      // Bias corrections as multiplications and the quotient as a correctly rounded reciprocal times the numerator
+      // (within 2 ulp of the divisions): an IEEE division takes a slow path, about a hundred instructions, whenever
+      // its numerator is zero or tiny, which is the steady state of every embedding row whose token was not in the
+      // batch (measured 0.19 ms per 42 M-element table with O(1) gradients, 0.32 ms with zero gradients).
+      const float tn = t - alpha * ((mm * inv_c1) * __frcp_rn(sqrtf(vv * inv_c2) + eps));
       theta[i] = tn;
       // the model's compute-type copy of the weights is refreshed in the same pass (2 more bytes per parameter
       // instead of a separate read-and-cast pass over Theta)
@@ -331,8 +335,8 @@ static int adamw_launch_shadow(float* theta, const float* delta, float* m, float
                                float b2, float eps, float lam, int t, float n_tokens, void* shadow, bool shadow_bf16,
                                cudaStream_t s) {
   const float c1 = 1.f - powf(b1, (float)t), c2 = 1.f - powf(b2, (float)t);
-  if (shadow_bf16) k_adamw<bf16><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (bf16*)shadow);
-  else k_adamw<float><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, c1, c2, 1.f / n_tokens, (float*)shadow);
+  if (shadow_bf16) k_adamw<bf16><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, 1.f / c1, 1.f / c2, 1.f / n_tokens, (bf16*)shadow);
+  else k_adamw<float><<<egrid(n), 256, 0, s>>>(theta, delta, m, v, n, alpha, b1, b2, eps, lam, 1.f / c1, 1.f / c2, 1.f / n_tokens, (float*)shadow);
   KERNEL_CHECK();
   return 0;
 }
