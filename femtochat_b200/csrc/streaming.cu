@@ -626,6 +626,21 @@ __global__ void k_axpy(T* __restrict__ y, const T* __restrict__ x, const float* 
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     y[i] = from_f<T>(to_f<T>(y[i]) + a * to_f<T>(x[i]));
 }
+// the same on 16-byte vectors (n a multiple of V, both pointers 16-byte aligned)
+template <typename T, int V>
+__global__ void __launch_bounds__(256) k_axpy_vec(T* __restrict__ y, const T* __restrict__ x, const float* a_dev, float a_mul,
+                                                  long long nvec) {
+  pdl_trigger();
+  const float a = (a_dev ? a_dev[0] : 1.f) * a_mul;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float f[V], g[V];
+    load_vec<T, V>(y + i * V, f);
+    load_vec<T, V>(x + i * V, g);
+#pragma unroll
+    for (int e = 0; e < V; e++) f[e] = round_to<T>(f[e] + a * g[e]);
+    store_vec<T, V>(y + i * V, f);
+  }
+}
 
 // Row n (t >= 1): dgate = dot(dx0[n], xe[n-1]); dpre[n] = dgate*lam_s*sg*(1-sg);
 // partial[block][j] = sum xe[n][j]*dpre[n] (j<24, smear gate weights), partial[block][24] = sum dgate*sg (lam_s).
@@ -994,8 +1009,14 @@ int Stream<T>::head_bwd(const T* dxnf, const T* xnf, const float* rf, const T* x
   return 0;
 }
 template <typename T> int Stream<T>::axpy(T* y, const T* x, const float* a_dev, float a_mul, long long n, cudaStream_t s) {
-  int nb = (int)std::min<long long>(cdiv(n, 256), 148 * 16);
-  k_axpy<T><<<nb, 256, 0, s>>>(y, x, a_dev, a_mul, n);
+  constexpr int V = VecN<T>::n;
+  if (n % V == 0 && aligned16(y) && aligned16(x)) {
+    const int nb = (int)std::min<long long>(cdiv(n / V, 256), 148 * 8);
+    k_axpy_vec<T, V><<<nb, 256, 0, s>>>(y, x, a_dev, a_mul, n / V);
+  } else {
+    const int nb = (int)std::min<long long>(cdiv(n, 256), 148 * 16);
+    k_axpy<T><<<nb, 256, 0, s>>>(y, x, a_dev, a_mul, n);
+  }
   KERNEL_CHECK();
   return 0;
 }
