@@ -337,7 +337,7 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   // about to overwrite that buffer and waits for that reader.
   cudaStream_t s2 = (backward && side) ? side : s;
   const bool two = s2 != s;
-  enum { SL_DX = 0, SL_DU = 3, SL_DQKV = 5, SL_FILL = 7 };
+  enum { SL_DX = 0, SL_DU = 3, SL_DQKV = 5, SL_FILL = 7, SL_DVE = 10 };   // 8, 9: the lm_head tail's two d-logit buffers
   auto fork = [&]() -> int {
     if (!two) return 0;
     cudaEvent_t e = h->ev_fork[h->ev_next++ % femto_handle::N_FORK];
@@ -531,6 +531,7 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     a.B = B; a.T = Tl; a.H = H; a.Hkv = Hkv; a.hd = hd; a.window_left = p.window; a.doc_start = docs;
     a.ws = h->attn_ws; a.ws_bytes = h->attn_ws_bytes; a.status = h->status;
     FEMTO_TRY(attention_bwd<T>(a, s));
+    if (p.ve) FEMTO_TRY(chain_write(SL_DVE));   // the previous value-embedding scatter has read dve
     FEMTO_TRY(S::qkv_post_bwd(dqkv, (const T*)l.qkv, dq, p.ve ? (const T*)l.sh_ve : nullptr, h->tok0, h->pos,
                               h->sin_t, h->cos_t, N, H, Hkv, hd, l.rqk, l.sv, (T*)h->dve, h->dpre, s));
     FEMTO_TRY(fork());
@@ -550,7 +551,10 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
     if (p.ve) {
       FEMTO_TRY(S::ve_gate_bwd((const T*)l.xn1, d, h->dpre, theta + p.ve_gate, dxn, N, Hkv, h->partial, &nb, s));
       FEMTO_TRY(reduce_partials(h->partial, nb, 12 * Hkv, delta + p.ve_gate, nullptr, 1.f, true, s));
-      FEMTO_TRY(scatter_rows<T>(h->plan, delta + p.ve_table, (const T*)h->dve, kv, kv, s));
+      // the row scatter into the value-embedding table's gradient: nothing on the chain waits for it
+      FEMTO_TRY(fork());
+      FEMTO_TRY(scatter_rows<T>(h->plan, delta + p.ve_table, (const T*)h->dve, kv, kv, s2));
+      FEMTO_TRY(side_read(SL_DVE));
     }
     FEMTO_TRY(chain_write(SL_DX + c2));
     FEMTO_TRY(S::mix_bwd(dx1, dx2, dxn, (const T*)l.xn1, l.r1, xin, (const T*)h->x0, theta + p.lam_b, theta + p.lam_x0,
@@ -568,7 +572,8 @@ static int step_t(femto_handle* h, const float* theta, float* delta, const int* 
   FEMTO_TRY(reduce_partials(h->partial, nb, 25, delta + h->off_smear, nullptr, 1.f, true, s));
   FEMTO_TRY(S::embed_bwd((const T*)h->dx0, (const T*)h->sh_wte, h->tok0, (const T*)h->xe, h->sg, h->dpre_s,
                          theta + h->off_smear, theta + h->off_lam_s, N, Tl, d, eps, dxn, s));
-  FEMTO_TRY(scatter_rows<T>(h->plan, delta + h->off_wte, dxn, d, d, s));
+  FEMTO_TRY(fork());
+  FEMTO_TRY(scatter_rows<T>(h->plan, delta + h->off_wte, dxn, d, d, s2));
   FEMTO_TRY(join());
   if (ov) {
     FEMTO_TRY(dp_bucket_allreduce(h->dp, delta + h->off_wte, (long long)Vp * d, s));

@@ -60,7 +60,7 @@ struct femto_handle {
   // AdamW tables of the update.  Nothing on the chain waits for that work within a block, so it fills the tensor
   // pipe while the chain runs its HBM-streaming kernels.  The caller's stream is joined on both sides of a call.
   cudaStream_t hi = nullptr, lo = nullptr;
-  static constexpr int N_FORK = 16, N_SIDE = 10;
+  static constexpr int N_FORK = 16, N_SIDE = 12;
   cudaEvent_t ev_fork[N_FORK] = {};   // chain -> side, used round-robin (a wait keeps the record it was given)
   int ev_next = 0;
   cudaEvent_t ev_side[N_SIDE] = {};   // side -> chain: the last side reader of a gradient buffer has finished
